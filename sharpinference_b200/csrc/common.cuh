@@ -1,0 +1,92 @@
+// Shared helpers of the sm_100a kernel library.
+//
+// Every kernel file is a translation unit of its own with a C ABI: plain pointers, sizes
+// and a cudaStream_t come in, an int status comes back (0 = launched, otherwise a code of
+// SharpiStatus).  No file allocates device memory; scratch is passed in by the caller.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum SharpiStatus : int {
+    SHARPI_OK = 0,
+    SHARPI_BAD_ARGUMENT = 1,     // a size or option the kernel does not take
+    SHARPI_LAUNCH_FAILED = 2,    // cudaGetLastError() after the launch was not cudaSuccess
+    SHARPI_UNALIGNED = 3,        // a pointer or stride that breaks an alignment rule
+};
+
+enum SharpiDtype : int {
+    SHARPI_F32 = 0,
+    SHARPI_BF16 = 1,
+};
+
+#define SHARPI_API extern "C" __attribute__((visibility("default")))
+
+#define SHARPI_CHECK_LAUNCH()                                       \
+    do {                                                            \
+        cudaError_t err__ = cudaGetLastError();                     \
+        if (err__ != cudaSuccess) return SHARPI_LAUNCH_FAILED;      \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads.  `scratch` holds 32 floats of shared memory.
+// Every thread receives the total.  The order of the additions is fixed by the block
+// size alone, so a row gives the same sum whatever else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = (lane < nwarps) ? scratch[lane] : 0.0f;
+    total = warp_sum(total);
+    return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    total = warp_max(total);
+    return total;
+}
+
+// How much of the past a query at position `pos` may see (the lowest visible position;
+// the highest is `pos` itself).  The same three rules name the cache manager's groups.
+enum SharpiMask : int {
+    SHARPI_MASK_FULL = 0,    // every earlier position
+    SHARPI_MASK_CHUNK = 1,   // positions of the same chunk of `span` positions
+    SHARPI_MASK_WINDOW = 2,  // the last `span` positions, the query's own included
+};
+
+__host__ __device__ __forceinline__ int visible_lo(int pos, int mask_kind, int span) {
+    if (mask_kind == SHARPI_MASK_CHUNK) return (pos / span) * span;
+    if (mask_kind == SHARPI_MASK_WINDOW) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+    return 0;
+}

@@ -1,0 +1,147 @@
+// Embedding lookup, residual-add + RMSNorm, SwiGLU and dtype casts.
+//
+// The residual stream is fp32 in both precisions; sums of squares, the rsqrt and the
+// scaling are fp32.  Counterparts in the reference: llm_embed_lookup_f32
+// (src/SharpInference.Cuda/CudaTextKernels.cs:944), llm_rmsnorm / llm_rmsnorm_batched
+// (:199, :5819), add_inplace (src/SharpInference.Cuda/CudaKernels.cs:89) and llm_silu_mul
+// (CudaTextKernels.cs:331); here the residual add is fused into the norm that follows it.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// out[t, :] = table[ids[t], :]           (fp32 residual stream)
+// ---------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
+                                    float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    const bool valid = (id >= 0 && id < V);
+    const TT* row = table + (size_t)(valid ? id : 0) * H;
+    float* dst = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = valid ? to_float(row[i]) : 0.0f;
+}
+
+SHARPI_API int sharpi_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
+                                   int T, int H, int V, cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (H <= 0 || V <= 0) return SHARPI_BAD_ARGUMENT;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == SHARPI_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+    else if (table_dtype == SHARPI_BF16)
+        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
+    else
+        return SHARPI_BAD_ARGUMENT;
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Residual add + RMSNorm.
+//   rows == nullptr:  x[t] += delta[t] (written back); out[t] = x[t] * rsqrt(mean(x[t]^2)+eps) * w
+//   rows != nullptr:  r = rows[t]; v = x[r] + delta[r] (x untouched); out[t] = norm(v)
+// `out` has dtype out_dtype; `out32` (optional) receives the same values in fp32, for
+// consumers that must not see them rounded (the expert router).
+// One block of NORM_THREADS threads per row whatever the batch, so the order of the
+// additions in the sum of squares never depends on what else is in the step.
+// ---------------------------------------------------------------------------------------
+constexpr int NORM_THREADS = 256;
+
+template <typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                   const float* __restrict__ w, float eps, const int* __restrict__ rows,
+                                   int H, TO* __restrict__ out, float* __restrict__ out32) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[t] : t) * H;
+    float* xr = x + src;
+    const float* dr = delta ? delta + src : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        float v = xr[i];
+        if (dr) {
+            v += dr[i];
+            if (!rows) xr[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)t * H;
+    float* o32 = out32 ? out32 + (size_t)t * H : nullptr;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        float v = xr[i];
+        if (dr && rows) v += dr[i];
+        const float y = v * scale * w[i];
+        orow[i] = from_float<TO>(y);
+        if (o32) o32[i] = y;
+    }
+}
+
+SHARPI_API int sharpi_add_rmsnorm(float* x, const float* delta, const float* w, float eps, const int* rows,
+                                  int T, int H, void* out, int out_dtype, float* out32, cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (H <= 0) return SHARPI_BAD_ARGUMENT;
+    if (out_dtype == SHARPI_F32)
+        add_rmsnorm_kernel<float><<<T, NORM_THREADS, 0, stream>>>(x, delta, w, eps, rows, H, (float*)out, out32);
+    else if (out_dtype == SHARPI_BF16)
+        add_rmsnorm_kernel<bf16><<<T, NORM_THREADS, 0, stream>>>(x, delta, w, eps, rows, H, (bf16*)out, out32);
+    else
+        return SHARPI_BAD_ARGUMENT;
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU over a fused [M, 2I] gate|up product:  out[m, i] = silu(s*g) * (s*u),
+// g = gate_up[m, i], u = gate_up[m, I + i], s = row_scale[scale_rows ? scale_rows[m] : m] or 1.
+// The routed expert's router weight multiplies gate and up BEFORE the nonlinearity, which
+// equals scaling the expert's input (src/SharpInference.Engine/ForwardPass.cs:2082-2088).
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gate_up, const float* __restrict__ row_scale,
+                              const int* __restrict__ scale_rows, TO* __restrict__ out, int I) {
+    const int m = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float s = row_scale ? row_scale[scale_rows ? scale_rows[m] : m] : 1.0f;
+    const float g = gate_up[(size_t)m * 2 * I + i] * s;
+    const float u = gate_up[(size_t)m * 2 * I + I + i] * s;
+    const float act = g / (1.0f + expf(-g));
+    out[(size_t)m * I + i] = from_float<TO>(act * u);
+}
+
+SHARPI_API int sharpi_swiglu(const float* gate_up, const float* row_scale, const int* scale_rows, void* out,
+                             int out_dtype, int M, int I, cudaStream_t stream) {
+    if (M <= 0) return SHARPI_OK;
+    if (I <= 0 || (I + 255) / 256 > 65535) return SHARPI_BAD_ARGUMENT;
+    dim3 grid(M, (I + 255) / 256);
+    if (out_dtype == SHARPI_F32)
+        swiglu_kernel<float><<<grid, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (float*)out, I);
+    else if (out_dtype == SHARPI_BF16)
+        swiglu_kernel<bf16><<<grid, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (bf16*)out, I);
+    else
+        return SHARPI_BAD_ARGUMENT;
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// y[i] = a[i] + b[i] (fp32), used to combine a shared and a routed feed-forward output
+// where no fused epilogue does it.
+// ---------------------------------------------------------------------------------------
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y,
+                           size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) y[i] = a[i] + b[i];
+}
+
+SHARPI_API int sharpi_add(const float* a, const float* b, float* y, long long n, cudaStream_t stream) {
+    if (n <= 0) return SHARPI_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    add_kernel<<<(int)blocks, 256, 0, stream>>>(a, b, y, (size_t)n);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}

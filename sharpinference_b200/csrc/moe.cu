@@ -1,0 +1,125 @@
+// Expert routing on the device: router logits, gate, top-1 choice, and the sort of the
+// step's rows by expert.  Nothing comes back to the host; the reference downloads the
+// router output and picks the expert on the CPU after a synchronize, once per layer and
+// token (src/SharpInference.Engine/CudaForwardPass.cs:5532-5541).
+//
+// Formula (src/SharpInference.Engine/ForwardPass.cs:2027-2040, :2132-2163): r = h . Wr^T,
+// p = sigmoid(r) elementwise, e* = the first index of the largest p (strict >), w = p[e*],
+// no renormalisation for one expert per token.  The logits are fp32 dot products of the
+// fp32 normalised activations with fp32 router weights, each summed in an order that the
+// width alone fixes, so a token picks the same expert in every batch.
+#include "common.cuh"
+
+enum RouterGate : int {
+    ROUTER_GATE_SIGMOID = 0,
+};
+
+constexpr int ROUTER_THREADS = 256;
+
+__global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int H, int E,
+                                   int* __restrict__ expert_id, float* __restrict__ expert_weight,
+                                   float* __restrict__ logits_out) {
+    extern __shared__ float smem[];
+    float* h_s = smem;          // [H]
+    float* r_s = smem + H;      // [E]
+    const int t = blockIdx.x;
+    const float* hr = h + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += ROUTER_THREADS) h_s[i] = hr[i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
+        const float* w = wr + (size_t)e * H;
+        float acc = 0.0f;
+        for (int i = lane; i < H; i += 32) acc = fmaf(h_s[i], w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) r_s[e] = acc;
+    }
+    __syncthreads();
+    if (logits_out)
+        for (int e = threadIdx.x; e < E; e += ROUTER_THREADS) logits_out[(size_t)t * E + e] = r_s[e];
+    if (threadIdx.x == 0) {
+        int best = 0;
+        float best_p = 1.0f / (1.0f + expf(-r_s[0]));
+        for (int e = 1; e < E; ++e) {
+            const float p = 1.0f / (1.0f + expf(-r_s[e]));
+            if (p > best_p) {
+                best_p = p;
+                best = e;
+            }
+        }
+        expert_id[t] = best;
+        expert_weight[t] = best_p;
+    }
+}
+
+SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H, int E, int gate, int* expert_id,
+                                  float* expert_weight, float* logits_out, cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (H <= 0 || E <= 0 || gate != ROUTER_GATE_SIGMOID) return SHARPI_BAD_ARGUMENT;
+    const size_t smem = (size_t)(H + E) * sizeof(float);
+    if (smem > 200 * 1024) return SHARPI_BAD_ARGUMENT;
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(router_top1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem);
+        if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
+    }
+    router_top1_kernel<<<T, ROUTER_THREADS, smem, stream>>>(h, wr, H, E, expert_id, expert_weight, logits_out);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Stable counting sort of the rows by expert, in one block: offsets[e] = first sorted row of
+// expert e (offsets[E] = T), sorted_rows[r] = the row that stands at sorted position r.  Rows
+// of one expert keep their order.  Warp w owns experts w, w + 32, ...: it walks all rows with
+// ballots, once to count and once to place.
+// ---------------------------------------------------------------------------------------
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_MAX_E = 1024;
+
+__global__ void moe_sort_kernel(const int* __restrict__ expert_id, int T, int E, int* __restrict__ offsets,
+                                int* __restrict__ sorted_rows) {
+    __shared__ int cnt_s[SORT_MAX_E + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int e = warp; e < E; e += SORT_THREADS / 32) {
+        int n = 0;
+        for (int base = 0; base < T; base += 32) {
+            const int t = base + lane;
+            const bool mine = (t < T) && (expert_id[t] == e);
+            n += __popc(__ballot_sync(0xffffffffu, mine));
+        }
+        if (lane == 0) cnt_s[e] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int n = cnt_s[e];
+            cnt_s[e] = run;
+            offsets[e] = run;
+            run += n;
+        }
+        cnt_s[E] = run;
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += SORT_THREADS / 32) {
+        int cursor = cnt_s[e];
+        for (int base = 0; base < T; base += 32) {
+            const int t = base + lane;
+            const bool mine = (t < T) && (expert_id[t] == e);
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) sorted_rows[cursor + __popc(mask & lt)] = t;
+            cursor += __popc(mask);
+        }
+    }
+}
+
+SHARPI_API int sharpi_moe_sort(const int* expert_id, int T, int E, int* offsets, int* sorted_rows,
+                               cudaStream_t stream) {
+    if (E <= 0 || E > SORT_MAX_E || T < 0) return SHARPI_BAD_ARGUMENT;
+    moe_sort_kernel<<<1, SORT_THREADS, 0, stream>>>(expert_id, T, E, offsets, sorted_rows);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}

@@ -1,0 +1,253 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.  It decides; the step function runs what it decided.
+
+Reference: ``ContinuousBatchingEngine.BatcherLoop`` (src/SharpInference.Engine/ContinuousBatchingEngine.cs:257-502):
+FIFO admission under a batch-slot limit and a reservation of ``prompt + max_new`` cache tokens
+(:511-580), a prefill budget split over the prompts being prefilled (:588-684), then one decode
+step for every active sequence (:314-347), retirement on a stop token, ``MaxNewTokens`` or
+cancellation (:394-407).  Differences, because pages are taken as needed instead of reserved up
+front: one step mixes decodes and prompt portions; and pages can run out mid-flight, which is
+decided as follows.
+
+**When pages run out.**  Decodes come first.  If the running requests' next tokens do not all
+fit, the most recently admitted running request is *preempted*: its pages and state slot are
+given back, it returns to the FRONT of the waiting queue, and when it is admitted again it is
+recomputed from its prompt and the tokens it had generated (its sampler stream and its output
+continue where they were).  This repeats until the rest fits.  A request that does not fit even
+when it is the only one running can never finish: it ends with ``finish_reason="cache_full"``
+and the others go on.  Prompt portions only take pages that decodes left over; a portion shrinks
+to what fits, and a waiting request is admitted only when at least one of its tokens fits.
+"""
+from __future__ import annotations
+
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import SamplerState
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    request_id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    stop_set: Tuple[int, ...] = ()
+    generated: List[int] = field(default_factory=list)
+    status: str = WAITING
+    computed: int = 0                   # tokens of prompt + generated whose keys and values are cached
+    finish_reason: Optional[str] = None
+    stop_token: Optional[int] = None
+    admitted_order: int = -1
+    preemptions: int = 0
+    sampler: Optional[SamplerState] = None
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.generated
+
+    @property
+    def pending(self) -> int:
+        """Tokens not yet run: the rest of the prompt, or the one token sampled last."""
+        return len(self.prompt) + len(self.generated) - self.computed
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    start: int          # index into request.tokens of the first token of the portion
+    count: int
+    want_last: bool     # the portion reaches the request's last token: sample from its last row
+
+
+@dataclass
+class StepPlan:
+    entries: List[PlannedEntry] = field(default_factory=list)
+    preempted: List[Request] = field(default_factory=list)
+    failed: List[Request] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(e.count for e in self.entries)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, *, max_batch: int, max_tokens_per_step: int):
+        if max_batch <= 0 or max_tokens_per_step <= 0:
+            raise ValueError("max_batch and max_tokens_per_step must be positive")
+        self.cache = cache
+        self.max_batch = min(max_batch, cache.max_requests)
+        self.max_tokens_per_step = max_tokens_per_step
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []            # in admission order
+        self._order = itertools.count()
+        # counters
+        self.num_preemptions = 0
+        self.num_finished = 0
+        self.num_steps = 0
+
+    # -- intake --------------------------------------------------------------------------
+    def add(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError(f"request {request.request_id!r}: the prompt is empty")
+        request.status = WAITING
+        self.waiting.append(request)
+
+    def abort(self, request_id: Hashable) -> Optional[Request]:
+        for req in list(self.running):
+            if req.request_id == request_id:
+                self._finish(req, "abort")
+                return req
+        for req in list(self.waiting):
+            if req.request_id == request_id:
+                self.waiting.remove(req)
+                req.status, req.finish_reason = FINISHED, "abort"
+                return req
+        return None
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # -- planning ------------------------------------------------------------------------
+    def _fits(self, req: Request, n: int, left: Dict[int, int]) -> bool:
+        need = self.cache.pages_needed(req.request_id, n)
+        return all(need[g] <= left[g] for g in need)
+
+    def _take(self, req: Request, n: int, left: Dict[int, int]) -> None:
+        for g, k in self.cache.pages_needed(req.request_id, n).items():
+            left[g] -= k
+
+    def _largest_fit(self, req: Request, n_max: int, left: Dict[int, int]) -> int:
+        if n_max <= 0 or self._fits(req, n_max, left):
+            return max(n_max, 0)
+        lo, hi = 0, n_max            # fits(lo) holds (0 tokens need nothing), fits(hi) does not
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if self._fits(req, mid, left):
+                lo = mid
+            else:
+                hi = mid
+        return lo
+
+    def _preempt(self, req: Request, plan: StepPlan) -> None:
+        self.cache.free_request(req.request_id)
+        self.running.remove(req)
+        req.status, req.computed = WAITING, 0
+        req.preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(req)
+        plan.preempted.append(req)
+
+    def _finish(self, req: Request, reason: str) -> None:
+        if req.status == RUNNING:
+            self.cache.free_request(req.request_id)
+            self.running.remove(req)
+        req.status, req.finish_reason = FINISHED, reason
+        self.num_finished += 1
+
+    def plan(self) -> StepPlan:
+        plan = StepPlan()
+        budget = self.max_tokens_per_step
+
+        # 1. decodes: every running request whose prompt is done brings its one pending token.
+        while True:
+            left = dict(self.cache.free_pages())
+            decodes = [r for r in self.running if r.pending == 1 and r.computed >= len(r.prompt)]
+            ok = True
+            for req in decodes:
+                if self._fits(req, 1, left):
+                    self._take(req, 1, left)
+                else:
+                    ok = False
+                    break
+            if ok:
+                break
+            victim = self.running[-1]
+            if len(self.running) == 1:
+                self._finish(victim, "cache_full")
+                plan.failed.append(victim)
+            else:
+                self._preempt(victim, plan)
+        for req in decodes[:budget]:
+            plan.entries.append(PlannedEntry(req, req.computed, 1, True))
+        budget -= len(plan.entries)
+        planned = {e.request.request_id for e in plan.entries}
+
+        # 2. portions of prompts already admitted, oldest first.
+        for req in self.running:
+            if budget <= 0:
+                break
+            if req.request_id in planned or req.pending <= 0:
+                continue
+            n = self._largest_fit(req, min(req.pending, budget), left)
+            if n <= 0:
+                continue
+            self._take(req, n, left)
+            plan.entries.append(PlannedEntry(req, req.computed, n, n == req.pending))
+            planned.add(req.request_id)
+            budget -= n
+
+        # 3. admission, first come first served; a request enters only if a token of it fits.
+        while self.waiting and budget > 0 and len(self.running) < self.max_batch \
+                and self.cache.state_slots.free_count > 0:
+            req = self.waiting[0]
+            self.cache.add_request(req.request_id)
+            n = self._largest_fit(req, min(req.pending, budget), left)
+            if n <= 0:
+                self.cache.free_request(req.request_id)
+                if not self.running:
+                    # alone and still no room for one token: it can never run
+                    self.waiting.popleft()
+                    req.status, req.finish_reason = FINISHED, "cache_full"
+                    self.num_finished += 1
+                    plan.failed.append(req)
+                    continue
+                break
+            self.waiting.popleft()
+            req.status = RUNNING
+            req.admitted_order = next(self._order)
+            self.running.append(req)
+            self._take(req, n, left)
+            plan.entries.append(PlannedEntry(req, req.computed, n, n == req.pending))
+            budget -= n
+
+        # A running request that holds pages but could not move while nothing else moves either
+        # would wait for ever: the cache is too small for it.
+        if not plan.entries and self.running and not plan.preempted:
+            victim = self.running[-1]
+            if len(self.running) == 1:
+                self._finish(victim, "cache_full")
+                plan.failed.append(victim)
+            else:
+                self._preempt(victim, plan)
+        return plan
+
+    # -- after the step --------------------------------------------------------------------
+    def complete(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """Record the step: ``sampled`` holds one token for every planned entry with ``want_last``,
+        in plan order.  Returns the requests that finished."""
+        finished = []
+        it = iter(sampled)
+        self.num_steps += 1
+        for e in plan.entries:
+            req = e.request
+            req.computed += e.count
+            if not e.want_last:
+                continue
+            token = int(next(it))
+            if token in req.stop_set:
+                req.stop_token = token
+                self._finish(req, "stop")
+                finished.append(req)
+                continue
+            req.generated.append(token)
+            if len(req.generated) >= req.params.max_new_tokens:
+                self._finish(req, "length")
+                finished.append(req)
+        return finished

@@ -1,0 +1,286 @@
+"""Tensor-level wrappers of the kernel entry points.
+
+Each function checks what the kernel cannot check itself (device, dtype, contiguity, shapes),
+launches on torch's current CUDA stream and raises :class:`KernelError` on a refusal.  There
+is no CPU path: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .library import KernelError, check, kernel
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+MASK_FULL, MASK_CHUNK, MASK_WINDOW = 0, 1, 2
+ROPE_NONE, ROPE_INTERLEAVED, ROPE_HALVES = 0, 1, 2
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported by the kernels (float32 and bfloat16 are)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the engine has no CPU path); found device {t.device}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must have dtype {dtype}, found {t.dtype}")
+
+
+# ---------------------------------------------------------------------------------------
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` as fp32.  ``ids`` int32 [T], ``table`` [V, H] fp32 or bf16."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    T, (V, H) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32)
+    check(kernel("sharpi_embed_gather")(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), out.data_ptr(),
+                                        T, H, V, _stream()), "sharpi_embed_gather")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, *, rows: Optional[torch.Tensor] = None, want_fp32: bool = False,
+                out: Optional[torch.Tensor] = None, out32: Optional[torch.Tensor] = None):
+    """Residual add fused with RMSNorm.
+
+    Without ``rows``: ``x += delta`` in place (when ``delta`` is given) and the norm of every
+    row is returned.  With ``rows`` (int32 indices): the norm of ``x[rows] + delta[rows]``, and
+    ``x`` stays as it is.  Returns ``(out, out32)``; ``out32`` is the unrounded fp32 copy when
+    ``want_fp32`` (or ``out32``) is given, else ``None``.
+    """
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    H = x.shape[-1]
+    if delta is not None:
+        _need(delta, "delta", torch.float32)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta shape {tuple(delta.shape)} differs from x shape {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        T = rows.numel()
+    else:
+        T = x.numel() // H
+    if out is None:
+        out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    if want_fp32 and out32 is None:
+        out32 = out if out_dtype == torch.float32 else torch.empty((T, H), dtype=torch.float32, device=x.device)
+    alias = out32 is not None and out32.data_ptr() == out.data_ptr()
+    check(kernel("sharpi_add_rmsnorm")(x.data_ptr(), _ptr(delta), weight.data_ptr(), float(eps), _ptr(rows), T, H,
+                                       out.data_ptr(), dtype_code(out.dtype), None if alias else _ptr(out32),
+                                       _stream()), "sharpi_add_rmsnorm")
+    return out, out32
+
+
+def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, *, row_scale: Optional[torch.Tensor] = None,
+           scale_rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(s g) * (s u)`` over a fused ``[M, 2I]`` gate|up product (fp32 in)."""
+    _need(gate_up, "gate_up", torch.float32)
+    M, I2 = gate_up.shape
+    I = I2 // 2
+    if out is None:
+        out = torch.empty((M, I), dtype=out_dtype, device=gate_up.device)
+    check(kernel("sharpi_swiglu")(gate_up.data_ptr(), _ptr(row_scale), _ptr(scale_rows), out.data_ptr(),
+                                  dtype_code(out.dtype), M, I, _stream()), "sharpi_swiglu")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(a, "a", torch.float32)
+    _need(b, "b", torch.float32)
+    if out is None:
+        out = torch.empty_like(a)
+    check(kernel("sharpi_add")(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "sharpi_add")
+    return out
+
+
+def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
+             inv_freq: Optional[torch.Tensor], q_out: torch.Tensor, kv_layer: torch.Tensor, *, nq: int, nkv: int,
+             d: int, page_size: int, pairing: int, l2_eps: float, temp_attn_scale: float, temp_floor_scale: float,
+             write_kv: bool) -> None:
+    """RoPE, per-head L2 norm, temperature factor, q store and K/V scatter into pages.
+
+    ``qkv`` fp32 [T, (nq + 2 nkv) d]; ``kv_layer`` is one layer's pages
+    ``[pages, 2, nkv, page_size, d]`` in the dtype of ``q_out``; ``l2_eps < 0`` and
+    ``temp_floor_scale <= 0`` switch the norm and the temperature factor off.
+    """
+    _need(qkv, "qkv", torch.float32)
+    _need(positions, "positions", torch.int32)
+    _need(row_req, "row_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    _need(q_out, "q_out")
+    _need(kv_layer, "kv_layer", q_out.dtype)
+    T = positions.numel()
+    if qkv.shape != (T, (nq + 2 * nkv) * d):
+        raise KernelError(f"qkv shape {tuple(qkv.shape)} is not [T={T}, (nq + 2 nkv) d = {(nq + 2 * nkv) * d}]")
+    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"kv_layer shape {tuple(kv_layer.shape)} is not [pages, 2, {nkv}, {page_size}, {d}]")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != d // 2:
+            raise KernelError(f"inv_freq has {inv_freq.numel()} entries, head size {d} needs {d // 2}")
+    check(kernel("sharpi_qkv_post")(qkv.data_ptr(), positions.data_ptr(), row_req.data_ptr(),
+                                    block_table.data_ptr(), _ptr(inv_freq), q_out.data_ptr(), kv_layer.data_ptr(),
+                                    dtype_code(q_out.dtype), T, nq, nkv, d, block_table.shape[-1], page_size,
+                                    pairing, float(l2_eps), float(temp_attn_scale), float(temp_floor_scale),
+                                    int(write_kv), _stream()), "sharpi_qkv_post")
+
+
+def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
+                            row_req: torch.Tensor, positions: torch.Tensor, *, nq: int, nkv: int, d: int,
+                            page_size: int, mask_kind: int, mask_span: int, scale: float,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of every row over the keys it may see in its request's pages; [T, nq d]."""
+    _need(q, "q")
+    _need(kv_layer, "kv_layer", q.dtype)
+    _need(block_table, "block_table", torch.int32)
+    _need(row_req, "row_req", torch.int32)
+    _need(positions, "positions", torch.int32)
+    T = positions.numel()
+    if out is None:
+        out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+    check(kernel("sharpi_paged_attention_generic")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
+                                                   row_req.data_ptr(), positions.data_ptr(), out.data_ptr(),
+                                                   dtype_code(q.dtype), T, nq, nkv, d, block_table.shape[-1],
+                                                   page_size, mask_kind, mask_span, float(scale), _stream()),
+          "sharpi_paged_attention_generic")
+    return out
+
+
+def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+            group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
+            out_rows: Optional[torch.Tensor] = None, rows: Optional[int] = None, accumulate: bool = False
+            ) -> torch.Tensor:
+    """``C = A . W^T`` with fp32 accumulation on the CUDA cores.
+
+    Dense: ``w`` is [N, K].  Grouped: ``w`` is [E, N, K] and ``group_offsets`` (int32 [E+1])
+    gives the first sorted row of every expert.  ``a_rows`` / ``out_rows`` (int32 [rows]) make
+    sorted row r read ``A[a_rows[r]]`` and write ``C[out_rows[r]]``.
+    """
+    _need(a, "a")
+    _need(w, "w")
+    K = a.shape[-1]
+    if w.shape[-1] != K:
+        raise KernelError(f"inner sizes differ: a [..., {K}] against w [..., {w.shape[-1]}]")
+    if group_offsets is not None:
+        _need(group_offsets, "group_offsets", torch.int32)
+        if w.dim() != 3 or group_offsets.numel() != w.shape[0] + 1:
+            raise KernelError("a grouped product needs w [E, N, K] and group_offsets [E + 1]")
+        E, N = w.shape[0], w.shape[1]
+    else:
+        if w.dim() != 2:
+            raise KernelError("a dense product needs w [N, K]")
+        E, N = 1, w.shape[0]
+    M = rows if rows is not None else (a_rows.numel() if a_rows is not None else a.shape[0])
+    if out is None:
+        if accumulate:
+            raise KernelError("accumulate=True needs an output tensor to add to")
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _need(out, "out", torch.float32)
+    if a_rows is not None:
+        _need(a_rows, "a_rows", torch.int32)
+    if out_rows is not None:
+        _need(out_rows, "out_rows", torch.int32)
+    check(kernel("sharpi_gemm_nt")(a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype),
+                                   out.data_ptr(), _ptr(group_offsets), _ptr(a_rows), _ptr(out_rows), M, N, K, E,
+                                   int(accumulate), _stream()), "sharpi_gemm_nt")
+    return out
+
+
+def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False):
+    """Top-1 sigmoid routing.  Returns ``(expert_id int32 [T], weight fp32 [T], logits or None)``."""
+    _need(h32, "h32", torch.float32)
+    _need(router_weight, "router_weight", torch.float32)
+    T, H = h32.shape
+    E = router_weight.shape[0]
+    if router_weight.shape[1] != H:
+        raise KernelError(f"router weight is {tuple(router_weight.shape)}, activations have width {H}")
+    expert = torch.empty((T,), dtype=torch.int32, device=h32.device)
+    weight = torch.empty((T,), dtype=torch.float32, device=h32.device)
+    logits = torch.empty((T, E), dtype=torch.float32, device=h32.device) if want_logits else None
+    check(kernel("sharpi_router_top1")(h32.data_ptr(), router_weight.data_ptr(), T, H, E, 0, expert.data_ptr(),
+                                       weight.data_ptr(), _ptr(logits), _stream()), "sharpi_router_top1")
+    return expert, weight, logits
+
+
+def moe_sort(expert_id: torch.Tensor, num_experts: int):
+    """Stable sort of rows by expert: ``(offsets int32 [E+1], sorted_rows int32 [T])``."""
+    _need(expert_id, "expert_id", torch.int32)
+    T = expert_id.numel()
+    offsets = torch.empty((num_experts + 1,), dtype=torch.int32, device=expert_id.device)
+    sorted_rows = torch.empty((T,), dtype=torch.int32, device=expert_id.device)
+    check(kernel("sharpi_moe_sort")(expert_id.data_ptr(), T, num_experts, offsets.data_ptr(),
+                                    sorted_rows.data_ptr(), _stream()), "sharpi_moe_sort")
+    return offsets, sorted_rows
+
+
+def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "logits", torch.float32)
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    check(kernel("sharpi_argmax_rows")(logits.data_ptr(), R, V, out.data_ptr(), _stream()), "sharpi_argmax_rows")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, entry_row: torch.Tensor, entry_token: torch.Tensor,
+                    entry_count: torch.Tensor, rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32)
+    for name, t in (("entry_row", entry_row), ("entry_token", entry_token), ("entry_count", entry_count)):
+        _need(t, name, torch.int32)
+    for name, t in (("rep", rep), ("freq", freq), ("pres", pres)):
+        _need(t, name, torch.float32)
+    check(kernel("sharpi_apply_penalties")(logits.data_ptr(), logits.shape[1], entry_row.data_ptr(),
+                                           entry_token.data_ptr(), entry_count.data_ptr(), rep.data_ptr(),
+                                           freq.data_ptr(), pres.data_ptr(), entry_row.numel(), _stream()),
+          "sharpi_apply_penalties")
+
+
+def add_logit_bias(logits: torch.Tensor, entry_row: torch.Tensor, entry_token: torch.Tensor,
+                   entry_bias: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32)
+    _need(entry_row, "entry_row", torch.int32)
+    _need(entry_token, "entry_token", torch.int32)
+    _need(entry_bias, "entry_bias", torch.float32)
+    check(kernel("sharpi_add_logit_bias")(logits.data_ptr(), logits.shape[1], entry_row.data_ptr(),
+                                          entry_token.data_ptr(), entry_bias.data_ptr(), entry_row.numel(),
+                                          _stream()), "sharpi_add_logit_bias")
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                min_p: torch.Tensor, uniform: torch.Tensor, *, probs: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row: greedy where ``temperature <= 0``, else filtered temperature sampling."""
+    _need(logits, "logits", torch.float32)
+    R, V = logits.shape
+    _need(temperature, "temperature", torch.float32)
+    _need(top_k, "top_k", torch.int32)
+    _need(top_p, "top_p", torch.float32)
+    _need(min_p, "min_p", torch.float32)
+    _need(uniform, "uniform", torch.float32)
+    if probs is None:
+        probs = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    check(kernel("sharpi_sample_rows")(logits.data_ptr(), R, V, temperature.data_ptr(), top_k.data_ptr(),
+                                       top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(), probs.data_ptr(),
+                                       out.data_ptr(), _stream()), "sharpi_sample_rows")
+    return out

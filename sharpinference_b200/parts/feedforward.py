@@ -1,0 +1,68 @@
+"""Feed-forward parts: dense SwiGLU, and a top-1 sigmoid-routed mixture of experts with an
+always-on shared expert.
+
+Dense (src/SharpInference.Engine/ForwardPass.cs:2006-2015): ``y = (silu(h Wg^T) * (h Wu^T)) Wd^T``.
+
+Mixture (src/SharpInference.Engine/ForwardPass.cs:2021-2098): router logits ``r = h Wr^T``,
+``p = sigmoid(r)``, the expert with the largest ``p`` (first wins), ``w = p[e]``; the routed
+expert computes ``(silu(w g) * (w u)) Wd[e]^T`` with ``g = h Wg[e]^T``, ``u = h Wu[e]^T`` (the
+weight scales gate and up, which is scaling the expert's input); the shared expert is a dense
+SwiGLU on the unscaled ``h``; the two are summed.  Routing stays on the device: the step's rows
+are sorted by expert and each expert multiplies its rows in one grouped product.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, StepContext, register_part
+from .linear import GroupedLinear, Linear
+
+
+@register_part("feed_forward", "dense_swiglu")
+class DenseSwiGLU(FeedForward):
+    def __init__(self, *, gate_up: Linear, down: Linear, act_dtype: torch.dtype = torch.bfloat16):
+        if gate_up.out_features != 2 * down.in_features:
+            raise ValueError(f"fused gate|up weight has {gate_up.out_features} rows, expected 2 * {down.in_features}")
+        self.gate_up, self.down, self.act_dtype = gate_up, down, act_dtype
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        act = ops.swiglu(self.gate_up(h), self.act_dtype)
+        return self.down(act)
+
+
+@register_part("feed_forward", "moe_sigmoid_top1")
+class MoESigmoidTop1(FeedForward):
+    wants_fp32_input = True
+
+    def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
+                 shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):
+        E = experts_gate_up.num_groups
+        if router.shape != (E, experts_gate_up.in_features):
+            raise ValueError(f"router weight is {tuple(router.shape)}, expected [{E}, {experts_gate_up.in_features}]")
+        if experts_down.num_groups != E or experts_gate_up.out_features != 2 * experts_down.in_features:
+            raise ValueError("expert gate|up and down weights disagree on the number or width of the experts")
+        self.router = router
+        self.experts_gate_up, self.experts_down = experts_gate_up, experts_down
+        self.shared = shared
+        self.num_experts = E
+        self.act_dtype = act_dtype
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = h.shape[0]
+        if h32 is None:
+            h32 = h.to(torch.float32)
+        expert, weight, _ = ops.router_top1(h32, self.router)
+        offsets, sorted_rows = ops.moe_sort(expert, self.num_experts)
+        if "router_choices" in ctx.extras:          # tracing: which expert every row went to
+            ctx.extras["router_choices"].append(expert)
+        if self.shared is not None:
+            y = self.shared.forward(ctx, h)
+        else:
+            y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        gu = self.experts_gate_up(h, offsets, rows=T, a_rows=sorted_rows)          # sorted order
+        act = ops.swiglu(gu, self.act_dtype, row_scale=weight, scale_rows=sorted_rows)
+        self.experts_down(act, offsets, rows=T, out_rows=sorted_rows, out=y, accumulate=True)
+        return y

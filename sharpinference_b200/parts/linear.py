@@ -1,0 +1,65 @@
+"""Matrix products of the parts: ``y = a . W^T`` with the weight stored ``[out, in]``.
+
+Which routine runs is decided by the weight's dtype, not by a global mode:
+
+* float32 weight: the CUDA-core kernel with float32 accumulation (``gemm_generic.cu``), the
+  product of the true 32-bit path; no tensor cores and no reduced-precision mode are involved.
+* bfloat16 weight: a tensor-core product with float32 accumulation and float32 output.  The
+  dense ones go to the vendor library through ``torch.mm``, which is where the reference uses a
+  library too (cublasGemmEx for batched projections,
+  src/SharpInference.Cuda/CudaBackend.cs:2083-2117); sizes the library path does not take
+  (an inner size that is no multiple of 8) use the CUDA-core kernel.
+
+The grouped (per-expert) product has no library counterpart and always runs our own kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    """A weight ``[out, in]`` and the product with it.  Output is float32 ``[M, out]``."""
+
+    def __init__(self, weight: torch.Tensor, name: str = ""):
+        if weight.dim() != 2:
+            raise ValueError(f"linear weight '{name}' must be 2-D, found shape {tuple(weight.shape)}")
+        self.weight = weight
+        self.name = name
+        self.out_features, self.in_features = weight.shape
+        self._use_library = (weight.dtype == torch.bfloat16 and self.in_features % 8 == 0)
+        self._wt = weight.t() if self._use_library else None
+
+    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w = self.weight
+        if w.dtype == torch.float32:
+            if a.dtype != torch.float32:
+                a = a.to(torch.float32)
+            return ops.gemm_nt(a, w, out=out)
+        if self._use_library and a.dtype == torch.bfloat16:
+            if out is not None:
+                return torch.mm(a, self._wt, out_dtype=torch.float32, out=out)
+            return torch.mm(a, self._wt, out_dtype=torch.float32)
+        return ops.gemm_nt(a, w, out=out)
+
+
+class GroupedLinear:
+    """Per-expert weights ``[E, out, in]``; rows arrive sorted by expert."""
+
+    def __init__(self, weight: torch.Tensor, name: str = ""):
+        if weight.dim() != 3:
+            raise ValueError(f"grouped weight '{name}' must be [E, out, in], found shape {tuple(weight.shape)}")
+        self.weight = weight
+        self.name = name
+        self.num_groups, self.out_features, self.in_features = weight.shape
+
+    def __call__(self, a: torch.Tensor, group_offsets: torch.Tensor, *, rows: int,
+                 a_rows: Optional[torch.Tensor] = None, out_rows: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+        if self.weight.dtype == torch.float32 and a.dtype != torch.float32:
+            a = a.to(torch.float32)
+        return ops.gemm_nt(a, self.weight, out=out, group_offsets=group_offsets, a_rows=a_rows, out_rows=out_rows,
+                           rows=rows, accumulate=accumulate)

@@ -1,0 +1,36 @@
+"""Norm parts: RMSNorm with a weight, and the weightless L2 norm used on q and k per head.
+
+RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` (src/SharpInference.Cpu/SimdKernels.cs:4209-4246);
+the weightless form drops ``w`` (src/SharpInference.Cpu/SimdKernels.cs:4252-4283).  The sum of
+squares, the rsqrt and the scaling are float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import Norm, register_part
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Norm):
+    def __init__(self, weight: torch.Tensor, eps: float):
+        self.weight = weight
+        self.eps = float(eps)
+
+    def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
+        return ops.add_rmsnorm(x, delta, self.weight, self.eps, out_dtype, rows=rows, want_fp32=want_fp32)
+
+
+@register_part("norm", "l2")
+class L2Norm(Norm):
+    """``x * rsqrt(mean(x^2) + eps)`` over the last axis, no weight.  The attention mixer runs it
+    fused with the rotation and the cache write; it has no launch of its own."""
+
+    def __init__(self, eps: float):
+        self.eps = float(eps)
+
+    def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
+        raise NotImplementedError("L2Norm is applied inside the attention mixer's fused kernel")

@@ -1,0 +1,85 @@
+"""Shared fixtures: the tiny configurations, model folders with random weights, GPU marker."""
+from __future__ import annotations
+
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# Two tiny configurations that differ in every size and option.
+TINY_A = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 256, "hidden_size": 64, "num_hidden_layers": 4, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 128, "intermediate_size_mlp": 256,
+    "num_local_experts": 4, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1,
+    "rope_theta": 10000.0, "rope_scaling": None, "no_rope_layers": [3], "attention_chunk_size": 16,
+    "use_qk_norm": True, "qk_norm_eps": 1e-6, "attn_temperature_tuning": True, "floor_scale": 8,
+    "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+TINY_A_INIT = {"seed": 0, "std": 0.02, "norm_std": 0.1}
+
+TINY_B = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 384, "hidden_size": 96, "num_hidden_layers": 6, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 64, "intermediate_size_mlp": 192,
+    "num_local_experts": 8, "num_experts_per_tok": 1, "interleave_moe_layer_step": 2,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 16},
+    "no_rope_layers": [2, 5], "attention_chunk_size": 32, "use_qk_norm": False,
+    "attn_temperature_tuning": False, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+TINY_B_INIT = {"seed": 1, "std": 0.05, "norm_std": 0.0}
+
+# A third one with sizes that are no power of two anywhere, tied embeddings and the flag form of
+# no_rope_layers: hidden 88, 6 heads in 3 groups, head size 48, vocabulary 301.
+TINY_C = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 301, "hidden_size": 88, "num_hidden_layers": 3, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 40, "intermediate_size_mlp": 104,
+    "num_local_experts": 3, "num_experts_per_tok": 1, "moe_layers": [0, 2], "interleave_moe_layer_step": 1,
+    "rope_theta": 1000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
+                     "original_max_position_embeddings": 24},
+    "no_rope_layers": [1, 0, 1], "attention_chunk_size": 24, "use_qk_norm": True, "qk_norm_eps": 1e-5,
+    "attn_temperature_tuning": True, "floor_scale": 5, "attn_scale": 0.25, "rms_norm_eps": 1e-4,
+    "tie_word_embeddings": True,
+}
+TINY_C_INIT = {"seed": 2, "std": 0.08, "norm_std": 0.2}
+
+TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+
+
+def make_model_dir(tmp_path_factory, name: str, store_dtype: str = "bfloat16") -> str:
+    from sharpinference_b200.weights import write_random_model
+    cfg, init = TINY[name]
+    out = str(tmp_path_factory.mktemp(f"tiny_{name}_{store_dtype}"))
+    write_random_model(dict(cfg), out, init["seed"], std=init["std"], norm_std=init["norm_std"],
+                       store_dtype=store_dtype)
+    return out
+
+
+@pytest.fixture(scope="session")
+def model_dirs(tmp_path_factory):
+    """Model folders (bfloat16 weights) of the tiny configurations, made once per session."""
+    return {name: make_model_dir(tmp_path_factory, name) for name in TINY}

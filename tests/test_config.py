@@ -1,0 +1,105 @@
+"""Configuration and registry (no GPU)."""
+import copy
+
+import pytest
+
+from conftest import TINY_A, TINY_B, TINY_C
+from sharpinference_b200.config import ConfigError, Llama4TextConfig
+from sharpinference_b200.registry import (get_architecture, known_architectures, register_architecture, resolve,
+                                           unregister_architecture)
+
+
+def test_tiny_a_fields():
+    c = Llama4TextConfig.from_dict(TINY_A)
+    assert (c.vocab_size, c.hidden_size, c.num_hidden_layers) == (256, 64, 4)
+    assert (c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (4, 2, 16)
+    assert c.no_rope_layers == (3,) and c.moe_layers == (0, 1, 2, 3)
+    assert c.rope_scaling is None and c.attention_chunk_size == 16
+    assert c.use_qk_norm and c.qk_norm_eps == 1e-6 and c.attn_temperature_tuning
+    assert c.floor_scale == 8.0 and c.attn_scale == 0.1 and c.rms_norm_eps == 1e-5
+    assert [c.layer_uses_rope(i) for i in range(4)] == [True, True, True, False]
+
+
+def test_tiny_b_fields():
+    c = Llama4TextConfig.from_dict(TINY_B)
+    assert c.moe_layers == (1, 3, 5) and c.no_rope_layers == (2, 5)
+    assert c.rope_scaling.factor == 8.0 and c.rope_scaling.original_max_position_embeddings == 16
+    assert not c.use_qk_norm and not c.attn_temperature_tuning
+    assert [c.layer_is_moe(i) for i in range(6)] == [False, True, False, True, False, True]
+
+
+def test_no_rope_layers_both_forms():
+    flags = dict(TINY_A, no_rope_layers=[1, 1, 1, 0])
+    index = dict(TINY_A, no_rope_layers=[3])
+    assert Llama4TextConfig.from_dict(flags).no_rope_layers == Llama4TextConfig.from_dict(index).no_rope_layers == (3,)
+    absent = dict(TINY_A)
+    absent.pop("no_rope_layers")
+    assert Llama4TextConfig.from_dict(absent).no_rope_layers == (3,)          # every 4th layer
+    c = Llama4TextConfig.from_dict(TINY_C)
+    assert c.no_rope_layers == (1,) and c.moe_layers == (0, 2) and c.tie_word_embeddings
+
+
+def test_explicit_moe_layers_wins():
+    c = Llama4TextConfig.from_dict(dict(TINY_B, moe_layers=[0, 4]))
+    assert c.moe_layers == (0, 4)
+
+
+def test_text_config_member_and_round_trip():
+    nested = {"architectures": ["Llama4ForConditionalGeneration"], "text_config": dict(TINY_B)}
+    arch, c = resolve(nested)
+    assert arch.name == "Llama4ForCausalLM"
+    assert c == Llama4TextConfig.from_dict(TINY_B)
+    assert Llama4TextConfig.from_dict(c.to_dict()) == c
+
+
+def test_all_problems_in_one_error():
+    bad = dict(TINY_A, num_attention_heads=5, num_experts_per_tok=2, head_dim=15)
+    bad.pop("vocab_size")
+    with pytest.raises(ConfigError) as exc:
+        Llama4TextConfig.from_dict(bad)
+    text = str(exc.value)
+    assert "vocab_size" in text
+    bad2 = dict(TINY_A, num_attention_heads=5, num_experts_per_tok=2, head_dim=15)
+    with pytest.raises(ConfigError) as exc:
+        Llama4TextConfig.from_dict(bad2)
+    text = str(exc.value)
+    assert "multiple of num_key_value_heads" in text and "num_experts_per_tok" in text and "head_dim" in text
+
+
+@pytest.mark.parametrize("key,value", [("hidden_size", "64"), ("use_qk_norm", 1), ("rope_theta", "x"),
+                                       ("no_rope_layers", [9]), ("moe_layers", [7]), ("attention_chunk_size", 0),
+                                       ("hidden_act", "gelu"), ("attention_bias", True)])
+def test_bad_values(key, value):
+    with pytest.raises(ConfigError):
+        Llama4TextConfig.from_dict(dict(TINY_A, **{key: value}))
+
+
+def test_unsupported_rope_type():
+    bad = copy.deepcopy(TINY_B)
+    bad["rope_scaling"]["rope_type"] = "yarn"
+    with pytest.raises(ConfigError, match="yarn"):
+        Llama4TextConfig.from_dict(bad)
+
+
+def test_registry_unknown_lists_known():
+    assert "Llama4ForCausalLM" in known_architectures()
+    with pytest.raises(ConfigError, match="Llama4ForCausalLM"):
+        get_architecture("NoSuchModel")
+    with pytest.raises(ConfigError, match="architectures"):
+        resolve({"vocab_size": 3})
+
+
+def test_registry_accepts_new_architecture():
+    class Cfg:
+        architecture = "ToyArch"
+
+        @classmethod
+        def from_dict(cls, obj, where="config.json"):
+            return cls()
+
+    register_architecture("ToyArch", Cfg, lambda config, weights: None)
+    try:
+        arch, cfg = resolve({"architectures": ["ToyArch"]})
+        assert arch.name == "ToyArch" and isinstance(cfg, Cfg)
+    finally:
+        unregister_architecture("ToyArch")
