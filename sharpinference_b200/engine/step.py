@@ -44,6 +44,12 @@ class StepRunner:
         self._slots = cache.layer_slots()
         self.steps_run = 0
         self.rows_run = 0
+        # Tracing, for hunting the first difference: when `trace_router` is set, every routed
+        # feed-forward of a step leaves the expert it chose per row in `last_router_choices`
+        # (one int32 [T] tensor per routed schedule entry, in schedule order).  The reference
+        # prints the same with SHARPI_TRACE_ROUTERS (src/SharpInference.Engine/ForwardPass.cs:2042-2056).
+        self.trace_router = False
+        self.last_router_choices: List[torch.Tensor] = []
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         """Refuse, before any page is taken, a step that cannot run as given."""
@@ -143,7 +149,10 @@ class StepRunner:
         self.validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
         ctx = self.build_context(entries)
+        if self.trace_router:
+            ctx.extras["router_choices"] = []
         logits = self.model.forward(ctx)
+        self.last_router_choices = ctx.extras.get("router_choices", [])
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

@@ -89,7 +89,12 @@ def kernel(symbol: str):
     return fn
 
 
+launch_count = 0      # entry-point calls since the process started; each launches one or more kernels
+
+
 def check(status: int, symbol: str) -> None:
+    global launch_count
+    launch_count += 1
     if status != 0:
         raise KernelError(f"{symbol} failed: {STATUS_TEXT.get(status, f'status {status}')}")
 

@@ -41,6 +41,12 @@ class DecoderModel:
         self.config = config
         self._validate_schedule()
 
+    def set_schedule(self, schedule: Sequence[ScheduleEntry]) -> "DecoderModel":
+        """Replace the order in which blocks run (before a cache manager is made for the model)."""
+        self.schedule = list(schedule)
+        self._validate_schedule()
+        return self
+
     def _validate_schedule(self) -> None:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):

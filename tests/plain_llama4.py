@@ -204,14 +204,20 @@ def dense_ffn(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch
     return (silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def moe_ffn(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tensor, choices: Optional[list] = None):
+def moe_ffn(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tensor, choices: Optional[list] = None,
+            forced: Optional[Sequence[int]] = None, margins: Optional[list] = None):
     """The mixture, token by token as the reference runs it
     (src/SharpInference.Engine/ForwardPass.cs:2021-2098): router logits, sigmoid, the first index
     of the largest value (SelectTopK with k = 1, :2132-2163), the chosen expert's gate and up
     products scaled by the router weight before SiLU (:2082-2088), its down product accumulated
     with weight 1, then the shared expert on the unscaled input added (:2058-2066, :2095-2097).
     Expert tensors: ``gate_up_proj [E, H, 2I]`` multiplies from the right (``h @ W``), its first I
-    columns are the gate; ``down_proj [E, I, H]``."""
+    columns are the gate; ``down_proj [E, I, H]``.
+
+    ``forced`` (one expert per token) replaces the choice, for comparing an implementation whose
+    rounding let a near-tie fall the other way: the weight is then the sigmoid of the forced
+    expert, and ``margins`` receives, per token, how far below the largest sigmoid the forced
+    expert's lies (0 where the choice agrees)."""
     p = f"model.layers.{i}.feed_forward."
     router, gate_up, down = w[p + "router.weight"], w[p + "experts.gate_up_proj"], w[p + "experts.down_proj"]
     I = down.shape[1]
@@ -224,6 +230,10 @@ def moe_ffn(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tensor, choi
         for j in range(1, prob.shape[0]):
             if prob[j] > best:
                 e, best = j, prob[j]
+        if forced is not None:
+            if margins is not None:
+                margins.append(float(best - prob[forced[t]]))
+            e, best = int(forced[t]), prob[forced[t]]
         picked.append(e)
         gu = x @ gate_up[e]
         g, u = gu[:I] * best, gu[I:] * best
@@ -239,12 +249,14 @@ def moe_ffn(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tensor, choi
 # whole model
 # ---------------------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], schedule=None,
-            choices: Optional[list] = None) -> torch.Tensor:
+            choices: Optional[list] = None, forced: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
     """Logits [S, V] of a whole sequence: embedding (src/SharpInference.Engine/ForwardPass.cs:2230-2244),
     then per layer ``x += attn(norm(x))`` and ``x += ffn(norm(x))`` (:1557-1714), the final norm and
     the output product (:1740-1747; the embedding serves as output matrix when tied, :411-413).
     ``schedule`` is a list of ``(layer, borrow)``: run that layer's block, reading the keys and
-    values that schedule entry ``borrow`` produced if it is not None; default: every layer once."""
+    values that schedule entry ``borrow`` produced if it is not None; default: every layer once.
+    ``forced``: per routed schedule entry, in order, the expert of every token (see ``moe_ffn``)."""
     dtype = w["model.embed_tokens.weight"].dtype
     eps = cfg.get("rms_norm_eps", 1e-5)
     x = w["model.embed_tokens.weight"][torch.as_tensor(list(tokens), dtype=torch.long)]
@@ -253,6 +265,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], schedu
     moe = set(moe_layers(cfg))
     schedule = schedule if schedule is not None else [(i, None) for i in range(cfg["num_hidden_layers"])]
     produced = []
+    routed = 0
     for i, borrow in schedule:
         p = f"model.layers.{i}."
         h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
@@ -261,7 +274,11 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], schedu
         x = x + a
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
         if i in moe:
-            x = x + moe_ffn(cfg, w, i, h, choices)
+            m = [] if margins is not None else None
+            x = x + moe_ffn(cfg, w, i, h, choices, None if forced is None else forced[routed], m)
+            if margins is not None:
+                margins.append(m)
+            routed += 1
         else:
             x = x + dense_ffn(h, w[p + "feed_forward.gate_proj.weight"], w[p + "feed_forward.up_proj.weight"],
                               w[p + "feed_forward.down_proj.weight"])

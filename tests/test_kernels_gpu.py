@@ -1,0 +1,378 @@
+"""Each kernel alone against a plain float32 torch statement of the same operation, at sizes the
+engine's tiny models do not use (needs a GPU)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from sharpinference_b200.kernels import ops as _ops
+    return _ops
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(ops, dtype):
+    table = rnd(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32, device=DEV)
+    out = ops.embed_gather(ids, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("H", [8, 1000, 5120])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(ops, H, out_dtype):
+    T, eps = 37, 1e-5
+    x, delta, w = rnd(T, H, seed=1), rnd(T, H, seed=2), 1 + 0.1 * rnd(H, seed=3)
+    ref_x = x + delta
+    ref = ref_x * torch.rsqrt((ref_x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+    x1 = x.clone()
+    out, out32 = ops.add_rmsnorm(x1, delta, w, eps, out_dtype, want_fp32=True)
+    assert torch.equal(x1, ref_x)                                            # the residual stream got the sum
+    assert torch.allclose(out32, ref, rtol=2e-6, atol=1e-6)
+    assert torch.allclose(out.float(), ref.to(out_dtype).float(), rtol=1e-2 if out_dtype == torch.bfloat16 else 2e-6, atol=1e-6)
+    # no delta; and the gathered form leaves x alone
+    x2 = x.clone()
+    out_nd, _ = ops.add_rmsnorm(x2, None, w, eps, torch.float32)
+    assert torch.equal(x2, x)
+    assert torch.allclose(out_nd, x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w, rtol=2e-6, atol=1e-6)
+    rows = torch.tensor([36, 0, 7], dtype=torch.int32, device=DEV)
+    x3 = x.clone()
+    out_rows, _ = ops.add_rmsnorm(x3, delta, w, eps, torch.float32, rows=rows)
+    assert torch.equal(x3, x) and torch.allclose(out_rows, ref[rows.long()], rtol=2e-6, atol=1e-6)
+
+
+def test_rmsnorm_rows_do_not_depend_on_the_batch(ops):
+    x, w = rnd(64, 777, seed=4), 1 + 0.1 * rnd(777, seed=5)
+    full, _ = ops.add_rmsnorm(x.clone(), None, w, 1e-6, torch.float32)
+    one, _ = ops.add_rmsnorm(x[13:14].clone(), None, w, 1e-6, torch.float32)
+    assert torch.equal(full[13:14], one)
+
+
+def test_swiglu_scales_before_the_nonlinearity(ops):
+    M, I = 9, 300
+    gu = rnd(M, 2 * I, seed=6)
+    scale = torch.rand(20, device=DEV) + 0.1
+    rows = torch.randint(0, 20, (M,), device=DEV, dtype=torch.int32)
+    out = ops.swiglu(gu, torch.float32, row_scale=scale, scale_rows=rows)
+    s = scale[rows.long()][:, None]
+    g, u = gu[:, :I] * s, gu[:, I:] * s
+    assert torch.allclose(out, g / (1 + torch.exp(-g)) * u, rtol=1e-5, atol=1e-6)
+    plain_out = ops.swiglu(gu, torch.bfloat16)
+    g, u = gu[:, :I], gu[:, I:]
+    assert torch.allclose(plain_out.float(), (g / (1 + torch.exp(-g)) * u), rtol=1e-2, atol=1e-3)
+
+
+# ---------------------------------------------------------------------------------------
+def rope_ref(x, pos, inv_freq, pairing):
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    cos, sin = torch.cos(ang.double())[:, None, :], torch.sin(ang.double())[:, None, :]
+    x = x.double()
+    out = torch.empty_like(x)
+    if pairing == "interleaved":
+        a, b = x[..., 0::2], x[..., 1::2]
+        out[..., 0::2], out[..., 1::2] = a * cos - b * sin, a * sin + b * cos
+    else:
+        h = x.shape[-1] // 2
+        a, b = x[..., :h], x[..., h:]
+        out[..., :h], out[..., h:] = a * cos - b * sin, a * sin + b * cos
+    return out
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(6, 2, 48), (5, 5, 16), (8, 1, 128), (2, 1, 272)])
+@pytest.mark.parametrize("variant", ["rope+l2", "halves", "nope+temp", "bare"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qkv_post(ops, nq, nkv, d, variant, dtype):
+    ps, pages, B = 8, 12, 2
+    lens = [11, 5]
+    starts = [3, 40]
+    T = sum(lens)
+    positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    table = torch.full((B, 8), -1, dtype=torch.int32, device=DEV)
+    table[0, 0], table[0, 1] = 7, 2                    # positions 3..13 -> blocks 0, 1
+    table[1, 5] = 9                                     # positions 40..44 -> block 5
+    qkv = rnd(T, (nq + 2 * nkv) * d, seed=8)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))).to(DEV)
+    kv = torch.full((pages, 2, nkv, ps, d), 99.0, dtype=dtype, device=DEV)
+    q_out = torch.empty(T, nq, d, dtype=dtype, device=DEV)
+    use_rope = variant in ("rope+l2", "halves")
+    pairing = {"rope+l2": ops.ROPE_INTERLEAVED, "halves": ops.ROPE_HALVES}.get(variant, ops.ROPE_NONE)
+    l2 = 1e-6 if variant == "rope+l2" else -1.0
+    temp = (0.1, 8.0) if variant == "nope+temp" else (0.0, 0.0)
+    ops.qkv_post(qkv, positions, row_req, table, inv_freq if use_rope else None, q_out, kv, nq=nq, nkv=nkv, d=d,
+                 page_size=ps, pairing=pairing, l2_eps=l2, temp_attn_scale=temp[0], temp_floor_scale=temp[1],
+                 write_kv=True)
+    q = qkv[:, :nq * d].view(T, nq, d).double()
+    k = qkv[:, nq * d:(nq + nkv) * d].view(T, nkv, d).double()
+    v = qkv[:, (nq + nkv) * d:].view(T, nkv, d).double()
+    if use_rope:
+        name = "interleaved" if variant == "rope+l2" else "halves"
+        q, k = rope_ref(q, positions, inv_freq, name), rope_ref(k, positions, inv_freq, name)
+    if l2 >= 0:
+        q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + l2)
+        k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + l2)
+    if temp[1] > 0:
+        q = q * (1 + temp[0] * torch.log1p(torch.floor((positions.double() + 1) / temp[1])))[:, None, None]
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    assert torch.allclose(q_out.double(), q, **tol)
+    for t in range(T):
+        b, pos = int(row_req[t]), int(positions[t])
+        page = int(table[b, pos // ps])
+        assert torch.allclose(kv[page, 0, :, pos % ps, :].double(), k[t], **tol)
+        assert torch.allclose(kv[page, 1, :, pos % ps, :].double(), v[t], **tol)
+    written = {(int(table[int(row_req[t]), int(positions[t]) // ps]), int(positions[t]) % ps) for t in range(T)}
+    untouched = [(p, o) for p in range(pages) for o in range(ps) if (p, o) not in written]
+    p_idx = torch.tensor([p for p, _ in untouched], device=DEV)
+    o_idx = torch.tensor([o for _, o in untouched], device=DEV)
+    assert bool((kv[p_idx, :, :, o_idx, :] == 99.0).all())      # nothing else was written
+    # a layer that borrows a cache writes q only
+    kv2 = torch.full_like(kv, 5.0)
+    ops.qkv_post(qkv, positions, row_req, table, None, q_out, kv2, nq=nq, nkv=nkv, d=d, page_size=ps,
+                 pairing=ops.ROPE_NONE, l2_eps=-1.0, temp_attn_scale=0.0, temp_floor_scale=0.0, write_kv=False)
+    assert bool((kv2 == 5.0).all())
+
+
+# ---------------------------------------------------------------------------------------
+def attention_ref(q, k_all, v_all, positions, row_req, lo_of, scale, nq, nkv):
+    """q [T, nq, d]; k_all/v_all: per request [S, nkv, d] float64."""
+    T, _, d = q.shape
+    out = torch.zeros(T, nq, d, dtype=torch.float64)
+    for t in range(T):
+        b, pos = int(row_req[t]), int(positions[t])
+        lo = lo_of(pos)
+        for h in range(nq):
+            kh = k_all[b][lo:pos + 1, h // (nq // nkv)]
+            vh = v_all[b][lo:pos + 1, h // (nq // nkv)]
+            p = torch.softmax((kh @ q[t, h].double()) * scale, dim=0)
+            out[t, h] = p @ vh
+    return out.reshape(T, nq * d)
+
+
+def paged_setup(lens, nkv, d, ps, dtype, seed, shuffle=True):
+    """Random K/V for requests of the given lengths, scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [(n + ps - 1) // ps for n in lens]
+    pages = sum(blocks) + 3
+    perm = torch.randperm(pages, generator=g).tolist() if shuffle else list(range(pages))
+    table = torch.full((len(lens), max(blocks) + 1), -1, dtype=torch.int32)
+    kv = torch.zeros(pages, 2, nkv, ps, d, dtype=dtype)
+    ks, vs, at = [], [], 0
+    for b, n in enumerate(lens):
+        k = torch.randn(n, nkv, d, generator=g).to(dtype)
+        v = torch.randn(n, nkv, d, generator=g).to(dtype)
+        ks.append(k.double()); vs.append(v.double())
+        for blk in range(blocks[b]):
+            page = perm[at]; at += 1
+            table[b, blk] = page
+            n_in = min(ps, n - blk * ps)
+            kv[page, 0, :, :n_in] = k[blk * ps: blk * ps + n_in].transpose(0, 1)
+            kv[page, 1, :, :n_in] = v[blk * ps: blk * ps + n_in].transpose(0, 1)
+    return kv.to(DEV), table.to(DEV), ks, vs
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 4), (6, 3, 48, 16), (5, 1, 128, 64), (2, 2, 256, 8), (40, 8, 128, 64)])
+@pytest.mark.parametrize("mask", [("full", 0), ("chunk", 24), ("window", 9)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_paged_attention_generic(ops, nq, nkv, d, ps, mask, dtype):
+    lens = [150, 37, 1]
+    kv, table, ks, vs = paged_setup(lens, nkv, d, ps, dtype, seed=d + ps)
+    # rows: a prompt portion of request 0 (positions 100..149), the last token of request 1, request 2's only token
+    rows = [(0, p) for p in range(100, 150)] + [(1, 36), (2, 0)]
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([b for b, _ in rows], dtype=torch.int32, device=DEV)
+    q = rnd(len(rows), nq, d, dtype=dtype, seed=11)
+    kind, span = mask
+    code = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK, "window": ops.MASK_WINDOW}[kind]
+    lo_of = {"full": lambda p: 0, "chunk": lambda p: p // span * span, "window": lambda p: max(0, p - span + 1)}[kind]
+    scale = 1.0 / math.sqrt(d)
+    out = ops.paged_attention_generic(q, kv, table, row_req, positions, nq=nq, nkv=nkv, d=d, page_size=ps,
+                                      mask_kind=code, mask_span=max(span, 1), scale=scale)
+    ref = attention_ref(q.cpu(), ks, vs, positions.cpu(), row_req.cpu(), lo_of, scale, nq, nkv)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+    assert torch.allclose(out.double().cpu(), ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """One key far back is made to match the query; its value must dominate the output.  A kernel
+    that loses a tile, a page or the first key of a chunk shows here where random data would hide it."""
+    nq, nkv, d, ps = 4, 2, 32, 16
+    n = 700
+    for far in (0, 1, 15, 16, 127, 128, 129, 383, 384, 698, 699):
+        kv, table, ks, vs = paged_setup([n], nkv, d, ps, dtype, seed=far)
+        q = rnd(1, nq, d, dtype=dtype, seed=far + 1)
+        page, off = int(table[0, far // ps]), far % ps
+        for h in range(nkv):
+            kv[page, 0, h, off] = (q[0, h * 2].float() * 8.0).to(dtype)          # q.k / sqrt(d) is far above the rest
+        positions = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        row_req = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = ops.paged_attention_generic(q, kv, table, row_req, positions, nq=nq, nkv=nkv, d=d, page_size=ps,
+                                          mask_kind=ops.MASK_FULL, mask_span=1, scale=1 / math.sqrt(d))
+        out = out.view(nq, d).float()
+        for h in range(nkv):
+            target = kv[page, 1, h, off].float()
+            assert torch.allclose(out[h * 2], target, atol=5e-2), (far, h)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_chunk_and_window_edges(ops, dtype):
+    """The key just outside a chunk or window is made overwhelmingly attractive: it must not be seen.
+    The key just inside is made attractive next: it must be."""
+    nq, nkv, d, ps, n = 2, 1, 16, 8, 100
+    for kind, span, pos, outside, inside in (("chunk", 24, 50, 47, 48), ("chunk", 24, 48, 47, 48),
+                                             ("window", 9, 60, 51, 52), ("window", 9, 8, None, 0)):
+        code = {"chunk": 1, "window": 2}[kind]
+        for which, key in (("outside", outside), ("inside", inside)):
+            if key is None:
+                continue
+            kv, table, ks, vs = paged_setup([n], nkv, d, ps, dtype, seed=pos)
+            q = rnd(1, nq, d, dtype=dtype, seed=3)
+            page, off = int(table[0, key // ps]), key % ps
+            kv[page, 0, 0, off] = (q[0, 0].float() * 10.0).to(dtype)
+            kv[page, 1, 0, off] = 50.0
+            positions = torch.tensor([pos], dtype=torch.int32, device=DEV)
+            out = ops.paged_attention_generic(q, kv, table, torch.zeros(1, dtype=torch.int32, device=DEV), positions,
+                                              nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=code, mask_span=span,
+                                              scale=1 / math.sqrt(d)).float()
+            if which == "outside":
+                assert float(out[0, :d].abs().max()) < 10.0, (kind, pos, key)
+            else:
+                assert float(out[0, :d].min()) > 40.0, (kind, pos, key)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (37, 53, 71), (64, 64, 16), (130, 300, 257), (3, 2000, 96)])
+@pytest.mark.parametrize("dt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                (torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_gemm_nt_dense(ops, M, N, K, dt):
+    a, w = rnd(M, K, dtype=dt[0], seed=1), rnd(N, K, dtype=dt[1], seed=2)
+    out = ops.gemm_nt(a, w)
+    ref = (a.double() @ w.double().T)
+    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4)
+
+
+def test_gemm_nt_rows_do_not_depend_on_the_batch(ops):
+    a, w = rnd(200, 300, seed=3), rnd(77, 300, seed=4)
+    full = ops.gemm_nt(a, w)
+    assert torch.equal(full[131:132], ops.gemm_nt(a[131:132].contiguous(), w))
+    assert torch.equal(full[:70], ops.gemm_nt(a[:70].contiguous(), w))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_nt_grouped_gather_scatter_accumulate(ops, dtype):
+    E, N, K, T = 5, 70, 90, 200
+    w = rnd(E, N, K, dtype=dtype, seed=5)
+    a = rnd(T, K, dtype=dtype, seed=6)
+    expert = torch.randint(0, E, (T,), generator=torch.Generator().manual_seed(7))
+    expert[expert == 3] = 1                                  # expert 3 gets no rows
+    order = torch.argsort(expert, stable=True)
+    counts = torch.bincount(expert, minlength=E)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(counts, 0)]).to(torch.int32).to(DEV)
+    sorted_rows = order.to(torch.int32).to(DEV)
+    ref = torch.stack([a[t].double() @ w[int(expert[t])].double().T for t in range(T)])
+    gathered = ops.gemm_nt(a, w, group_offsets=offsets, a_rows=sorted_rows, rows=T)
+    assert torch.allclose(gathered.double(), ref[order.to(DEV)], rtol=1e-5, atol=1e-4)
+    base = rnd(T, N, seed=8)
+    acc = base.clone()
+    ops.gemm_nt(a[order.to(DEV)].contiguous(), w, group_offsets=offsets, out_rows=sorted_rows, rows=T, out=acc,
+                accumulate=True)
+    assert torch.allclose(acc.double(), base.double() + ref, rtol=1e-5, atol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,H,E", [(1, 77, 5), (50, 5120, 16), (9, 5120, 128), (3, 20000, 7)])
+def test_router_top1(ops, T, H, E):
+    h, wr = rnd(T, H, seed=9), rnd(E, H, scale=0.05, seed=10)
+    expert, weight, logits = ops.router_top1(h, wr, want_logits=True)
+    ref = h.double() @ wr.double().T
+    assert torch.allclose(logits.double(), ref, rtol=1e-4, atol=1e-4)
+    p = torch.sigmoid(logits)
+    assert torch.equal(expert.long(), torch.argmax(p, dim=1))
+    assert torch.allclose(weight, p.max(dim=1).values, rtol=1e-6)
+
+
+def test_router_first_of_equal_experts_wins(ops):
+    h = torch.ones(2, 16, device=DEV)
+    wr = torch.zeros(6, 16, device=DEV)
+    wr[2], wr[4] = 0.25, 0.25
+    expert, weight, _ = ops.router_top1(h, wr)
+    assert expert.tolist() == [2, 2] and float(weight[0]) == pytest.approx(1 / (1 + math.exp(-4.0)))
+
+
+@pytest.mark.parametrize("T,E", [(0, 4), (1, 1), (33, 4), (1000, 16), (5000, 128), (77, 1000)])
+def test_moe_sort_is_a_stable_counting_sort(ops, T, E):
+    ids = torch.randint(0, E, (T,), generator=torch.Generator().manual_seed(T + E)).to(torch.int32).to(DEV)
+    offsets, rows = ops.moe_sort(ids, E)
+    counts = torch.bincount(ids.long().cpu(), minlength=E)
+    assert offsets.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+    assert rows.cpu().tolist() == torch.argsort(ids.long().cpu(), stable=True).tolist()
+
+
+# ---------------------------------------------------------------------------------------
+def test_argmax_lowest_index_wins(ops):
+    logits = rnd(5, 202048, seed=12)
+    logits[0, 7] = logits[0, 150000] = 50.0
+    logits[1, :] = 0.0
+    logits[2, 202047] = 60.0
+    logits[3, 0] = 60.0
+    out = ops.argmax_rows(logits).tolist()
+    assert out[:4] == [7, 0, 202047, 0] and out[4] == int(torch.argmax(logits[4]))
+
+
+def test_sampling_follows_the_filtered_distribution(ops):
+    import plain_llama4 as plain
+    V, R = 1000, 256
+    row = rnd(V, scale=2.0, seed=13)
+    u = ((torch.arange(R, dtype=torch.float32) + 0.5) / R).to(DEV)
+    for temp, k, p, mp in ((0.8, 0, 1.0, 0.0), (1.0, 40, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
+                           (0.7, 40, 0.95, 0.05)):
+        dist = plain.sample_distribution(row.cpu(), temp, top_k=k, top_p=p, min_p=mp)
+        got = ops.sample_rows(row.expand(R, V).contiguous(), torch.full((R,), temp, device=DEV),
+                              torch.full((R,), k, dtype=torch.int32, device=DEV), torch.full((R,), p, device=DEV),
+                              torch.full((R,), mp, device=DEV), u).tolist()
+        want = [plain.draw(dist, float(x)) for x in u.tolist()]
+        differ = sum(a != b for a, b in zip(got, want))
+        assert differ <= 2, (temp, k, p, mp, differ)          # a draw may sit on a boundary of the cumulative sum
+        assert all(dist[t] > 0 for t in got)                   # never a token outside the kept set
+    greedy = ops.sample_rows(row.expand(3, V).contiguous(), torch.zeros(3, device=DEV),
+                             torch.zeros(3, dtype=torch.int32, device=DEV), torch.ones(3, device=DEV),
+                             torch.zeros(3, device=DEV), torch.rand(3, device=DEV)).tolist()
+    assert greedy == [int(torch.argmax(row))] * 3
+
+
+def test_penalties_and_bias(ops):
+    logits = torch.tensor([[2.0, -1.0, 0.5, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
+    ops.add_logit_bias(logits, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                       torch.tensor([2, 3], dtype=torch.int32, device=DEV), torch.tensor([1.5, -4.0], device=DEV))
+    assert logits.tolist() == [[2.0, -1.0, 2.0, 3.0], [1.0, 1.0, 1.0, -3.0]]
+    ops.apply_penalties(logits, torch.tensor([0, 0, 1], dtype=torch.int32, device=DEV),
+                        torch.tensor([0, 1, 3], dtype=torch.int32, device=DEV),
+                        torch.tensor([1, 3, 2], dtype=torch.int32, device=DEV),
+                        torch.tensor([2.0, 1.0], device=DEV), torch.tensor([0.0, 0.5], device=DEV),
+                        torch.tensor([0.0, 0.25], device=DEV))
+    # row 0: repetition 2 -> positive halves, negative doubles; row 1: -(2 * 0.5 + 0.25)
+    assert logits.tolist() == [[1.0, -2.0, 2.0, 3.0], [1.0, 1.0, 1.0, -4.25]]
+
+
+def test_no_cpu_path(ops):
+    from sharpinference_b200.kernels.library import KernelError
+    with pytest.raises(KernelError, match="CUDA"):
+        ops.embed_gather(torch.zeros(2, dtype=torch.int32), torch.zeros(4, 4))
+    with pytest.raises(KernelError):
+        ops.paged_attention_generic(torch.zeros(1, 3, 16, device=DEV), torch.zeros(1, 2, 2, 4, 16, device=DEV),
+                                    torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV), nq=3, nkv=2, d=16, page_size=4,
+                                    mask_kind=0, mask_span=1, scale=1.0)

@@ -1,0 +1,225 @@
+"""Generality of the parts: a toy mixer with state of its own, defined here, is registered, built
+into a toy architecture and stepped through the unchanged framework; and a schedule that names a
+layer twice and lets a layer read another's cache (needs a GPU).  Nothing here is a model of
+anyone's: the toy parts exist to exercise the interfaces."""
+import json
+import os
+from dataclasses import asdict, dataclass
+
+import pytest
+import torch
+
+import plain_llama4 as plain
+import traces
+from conftest import TINY_A, TINY_A_INIT
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+# ---------------------------------------------------------------------------------------
+# a mixer with state: s <- decay * s + h_t ; out_t = W s
+# ---------------------------------------------------------------------------------------
+def define_toy():
+    from sharpinference_b200.models.model import DecoderModel
+    from sharpinference_b200.parts import (DenseSwiGLU, Linear, PagedAttention, PreNormBlock, RMSNorm,
+                                           RotaryEncoding, rotary_inv_freq)
+    from sharpinference_b200.parts.base import Mixer, StateSpec, make_part, register_part
+    from sharpinference_b200.registry import register_architecture
+
+    @register_part("mixer", "toy_decay")
+    class DecayMixer(Mixer):
+        def __init__(self, *, weight, decay, act_dtype):
+            self.weight, self.decay, self.act_dtype = weight, float(decay), act_dtype
+            self.state_spec = StateSpec((weight.shape[1],), torch.float32)
+            self.cache_spec = None
+
+        def forward(self, ctx, slot, h):
+            out = torch.empty((ctx.num_tokens, self.weight.shape[0]), dtype=torch.float32, device=h.device)
+            row = 0
+            for b in range(ctx.num_requests):
+                s = slot.state[ctx.host_state_slots[b]]
+                for _ in range(ctx.host_lengths[b]):
+                    s.mul_(self.decay).add_(h[row].float())
+                    out[row] = self.weight.float() @ s
+                    row += 1
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int = 50
+        hidden_size: int = 40
+        intermediate_size: int = 56
+        num_heads: int = 5
+        head_dim: int = 16
+        window: int = 6
+        decay: float = 0.75
+        eps: float = 1e-5
+        architecture = "ToyDecayForCausalLM"
+
+        @classmethod
+        def from_dict(cls, obj, where="config.json"):
+            return cls(**{k: obj[k] for k in cls.__dataclass_fields__ if k in obj})
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], **asdict(self)}
+
+    def build(c, weights):
+        act, H, I = weights.compute_dtype, c.hidden_size, c.intermediate_size
+
+        def ffn(p):
+            return DenseSwiGLU(gate_up=Linear(weights.matrix(p + "gate_up.weight", (2 * I, H))),
+                               down=Linear(weights.matrix(p + "down.weight", (H, I))), act_dtype=act)
+
+        def norm(name):
+            return RMSNorm(weights.vector(name, (H,)), c.eps)
+
+        inv = rotary_inv_freq(c.head_dim, 100.0, None)
+        inv = inv if weights.device.type == "meta" else inv.to(weights.device)
+        blocks = [
+            PreNormBlock(mixer_norm=norm("l0.n1"), ffn_norm=norm("l0.n2"), ffn=ffn("l0."), act_dtype=act,
+                         mixer=make_part("mixer", "toy_decay", weight=weights.matrix("l0.mix.weight", (H, H)),
+                                         decay=c.decay, act_dtype=act)),
+            PreNormBlock(mixer_norm=norm("l1.n1"), ffn_norm=norm("l1.n2"), ffn=ffn("l1."), act_dtype=act,
+                         mixer=PagedAttention(qkv=Linear(weights.matrix("l1.qkv.weight", (3 * c.num_heads * c.head_dim, H))),
+                                              out=Linear(weights.matrix("l1.o.weight", (H, c.num_heads * c.head_dim))),
+                                              num_heads=c.num_heads, num_kv_heads=c.num_heads, head_dim=c.head_dim,
+                                              mask="window", span=c.window, position=RotaryEncoding(inv, "halves"),
+                                              act_dtype=act)),
+        ]
+        return DecoderModel(embedding=weights.matrix("embed.weight", (c.vocab_size, H)), blocks=blocks,
+                            final_norm=norm("final.weight"), head=Linear(weights.matrix("head.weight", (c.vocab_size, H))),
+                            act_dtype=act, config=c)
+
+    register_architecture("ToyDecayForCausalLM", ToyConfig, build)
+    return ToyConfig
+
+
+def toy_plain(folder, toks):
+    """Whole-sequence statement of the toy model in float64."""
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as fh:
+        c = json.load(fh)
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    H, nh, d, S = c["hidden_size"], c["num_heads"], c["head_dim"], len(toks)
+    x = w["embed.weight"][torch.tensor(toks)]
+    h = plain.rms_norm(x, w["l0.n1"], c["eps"])
+    s, mixed = torch.zeros(H, dtype=torch.float64), []
+    for t in range(S):
+        s = c["decay"] * s + h[t]
+        mixed.append(w["l0.mix.weight"] @ s)
+    x = x + torch.stack(mixed)
+    def ffn(p, h):
+        gu = h @ w[p + "gate_up.weight"].T
+        return (plain.silu(gu[:, :c["intermediate_size"]]) * gu[:, c["intermediate_size"]:]) @ w[p + "down.weight"].T
+    x = x + ffn("l0.", plain.rms_norm(x, w["l0.n2"], c["eps"]))
+    h = plain.rms_norm(x, w["l1.n1"], c["eps"])
+    qkv = (h @ w["l1.qkv.weight"].T)
+    q, k, v = (qkv[:, i * nh * d:(i + 1) * nh * d].reshape(S, nh, d) for i in range(3))
+    inv = 1.0 / torch.pow(torch.tensor(100.0), torch.arange(d // 2, dtype=torch.float32) * 2.0 / d)
+    ang = (torch.arange(S).float()[:, None] * inv[None, :]).double()
+    cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    rot = lambda z: torch.cat([z[..., :d // 2] * cs - z[..., d // 2:] * sn, z[..., :d // 2] * sn + z[..., d // 2:] * cs], -1)
+    x = x + plain.attention_scores(rot(q), rot(k), v, plain.visible("window", c["window"], S)) @ w["l1.o.weight"].T
+    x = x + ffn("l1.", plain.rms_norm(x, w["l1.n2"], c["eps"]))
+    return plain.rms_norm(x, w["final.weight"], c["eps"]) @ w["head.weight"].T
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    from sharpinference_b200 import write_random_model
+    ToyConfig = define_toy()
+    out = str(tmp_path_factory.mktemp("toy"))
+    write_random_model(ToyConfig(), out, seed=11, std=0.15, norm_std=0.1)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_built_and_stepped(toy_folder, dtype):
+    from sharpinference_b200 import Engine, EngineOptions
+    reqs = {f"t{i}": traces.random_tokens(50, n, seed=n) for i, n in enumerate([30, 9, 41, 17, 25])}
+    ref = {rid: toy_plain(toy_folder, toks) for rid, toks in reqs.items()}
+    for cut in (traces.whole, traces.portions, lambda r: traces.mixed(r, max_live=2)):
+        steps = cut(reqs)
+        eng = Engine(toy_folder, dtype=dtype, device=DEV,
+                     options=EngineOptions(page_size=4, max_cache_tokens=traces.max_tokens(steps), max_batch=2))
+        assert [g.spec.kind for g in eng.cache.groups] == ["window"]
+        state = eng.cache.layer_slots()[0].state
+        assert state is not None and state.shape == (2, 40)
+        got = traces.replay(eng, steps)
+        err, where = traces.worst_error(got, ref)
+        assert err < (2e-5 if dtype == "float32" else 3e-2), (err, where)
+        # with two state slots and five requests, slots were reused: a stale state would have shown
+        assert not eng.cache.requests and eng.cache.state_slots.free_count == 2
+
+
+def test_toy_generation_through_the_scheduler(toy_folder):
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams
+    prompts = [traces.random_tokens(50, n, seed=n + 1) for n in (12, 3, 20)]
+    eng = Engine(toy_folder, dtype="float32", device=DEV,
+                 options=EngineOptions(page_size=4, max_cache_tokens=256, max_batch=3, max_tokens_per_step=7))
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=5))
+    for p, g in zip(prompts, got):
+        seq = list(p)
+        for tok in g:
+            assert plain.greedy(toy_plain(toy_folder, seq)[-1]) == tok
+            seq.append(tok)
+
+
+# ---------------------------------------------------------------------------------------
+# the schedule as data
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_named_twice_and_a_borrowed_cache(tmp_path, dtype):
+    from sharpinference_b200 import Engine, EngineOptions, write_random_model
+    from sharpinference_b200.config import Llama4TextConfig
+    from sharpinference_b200.models.llama4 import build_llama4
+    from sharpinference_b200.models.model import ScheduleEntry
+    from sharpinference_b200.registry import register_architecture, unregister_architecture
+
+    order = [(0, None), (1, None), (2, None), (1, None), (3, None), (2, 2), (3, 4)]
+
+    def build(config, weights):
+        return build_llama4(config, weights).set_schedule([ScheduleEntry(layer, borrow) for layer, borrow in order])
+
+    class Cfg(Llama4TextConfig):
+        architecture = "Llama4TwiceForCausalLM"
+
+        def to_dict(self):
+            return dict(super().to_dict(), architectures=[self.architecture])
+
+    register_architecture("Llama4TwiceForCausalLM", Cfg, build)
+    try:
+        folder = str(tmp_path / "m")
+        write_random_model(dict(TINY_A, architectures=["Llama4TwiceForCausalLM"]), folder, 3, std=0.05, norm_std=0.1)
+        cfg, w = plain.load_folder(folder)
+        reqs = {f"r{i}": traces.random_tokens(cfg["vocab_size"], n, seed=n) for i, n in enumerate([37, 50, 8])}
+        steps = traces.mixed(reqs, max_live=2)
+        eng = Engine(folder, dtype=dtype, device=DEV,
+                     options=EngineOptions(page_size=8, max_cache_tokens=traces.max_tokens(steps), max_batch=2))
+        # seven schedule entries; two of them borrow, so five caches in two groups
+        assert sorted(len(g.entries) for g in eng.cache.groups) == [1, 4]
+        routing = {} if dtype == "bfloat16" else None
+        got = traces.replay(eng, steps, routing)
+        ref = {rid: plain.forward(cfg, w, toks, schedule=order, forced=None if routing is None else routing[rid])
+               for rid, toks in reqs.items()}
+        err, where = traces.worst_error(got, ref)
+        assert err < (2e-5 if dtype == "float32" else 3e-2), (err, where)
+    finally:
+        unregister_architecture("Llama4TwiceForCausalLM")
+
+
+def test_schedule_is_validated():
+    from sharpinference_b200.models.model import DecoderModel, ScheduleEntry
+    from sharpinference_b200.weights import DeclaringWeights
+    from sharpinference_b200.config import Llama4TextConfig
+    from sharpinference_b200.models.llama4 import build_llama4
+    model = build_llama4(Llama4TextConfig.from_dict(TINY_A), DeclaringWeights())
+    with pytest.raises(ValueError, match="names block 9"):
+        model.set_schedule([ScheduleEntry(9)])
+    with pytest.raises(ValueError, match="must come earlier"):
+        model.set_schedule([ScheduleEntry(0, cache_from=0)])
+    with pytest.raises(ValueError, match="cache needs differ"):
+        model.set_schedule([ScheduleEntry(0), ScheduleEntry(3, cache_from=0)])      # chunked against full
+    with pytest.raises(ValueError, match="itself borrows"):
+        model.set_schedule([ScheduleEntry(0), ScheduleEntry(1, cache_from=0), ScheduleEntry(2, cache_from=1)])
