@@ -103,3 +103,17 @@ def test_registry_accepts_new_architecture():
         assert arch.name == "ToyArch" and isinstance(cfg, Cfg)
     finally:
         unregister_architecture("ToyArch")
+
+
+def test_command_line_keeps_the_reference_option_names():
+    from sharpinference_b200.cli import build_parser, parse_prompts
+    ns = build_parser().parse_args(["-m", "dir", "-p", "5 17 3; 9,9", "-n", "8", "--temp", "0", "--top-k", "5",
+                                    "--top-p", "0.5", "--min-p", "0.1", "-s", "7", "-c", "256", "--rep-penalty", "1.3",
+                                    "--repeat-last-n", "32", "--verbose-prompt", "--no-display-prompt"])
+    assert (ns.model, ns.n_predict, ns.temp, ns.top_k, ns.top_p, ns.min_p) == ("dir", 8, 0.0, 5, 0.5, 0.1)
+    assert (ns.seed, ns.ctx_size, ns.repeat_penalty, ns.repeat_last_n) == (7, 256, 1.3, 32)
+    assert ns.verbose_prompt and ns.no_display_prompt
+    defaults = build_parser().parse_args([])
+    assert (defaults.n_predict, defaults.temp, defaults.top_k, defaults.top_p, defaults.min_p, defaults.seed) == \
+        (512, 0.7, 40, 0.95, 0.05, -1)
+    assert parse_prompts("5 17 3; 9,9") == [[5, 17, 3], [9, 9]]
