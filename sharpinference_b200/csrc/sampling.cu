@@ -280,3 +280,55 @@ SHARPI_API int sharpi_sample_rows(const float* logits, int R, int V, const float
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// The same sampler for callers that cannot allocate device memory: the [rows, vocab] work area is
+// a file-scope device array of this library.  See sampling_no_alloc.h for who needs it and for the
+// rules (size limit, first call per device, shared contents, no overlapping calls).
+// ---------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "sampling_no_alloc.h"
+
+static __device__ __align__(256) float g_no_alloc_probs[SHARPI_NO_ALLOC_MAX_FLOATS];
+
+// In host code `g_no_alloc_probs` is only a handle for the runtime, not a device address: handing it
+// to a kernel would make the kernel read host memory or fault.  The address the kernel needs comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static float* no_alloc_work_area(int* status) {
+    constexpr int MAX_DEVICES = 64;
+    static float* per_device[MAX_DEVICES] = {};
+    static std::mutex guard;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+        *status = SHARPI_NO_ALLOC_SETUP_FAILED;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> hold(guard);
+    if (per_device[device] == nullptr) {
+        float* address = nullptr;
+        if (cudaGetSymbolAddress((void**)&address, g_no_alloc_probs) != cudaSuccess || address == nullptr) {
+            cudaGetLastError();  // leave no sticky error behind for the caller's next launch check
+            *status = SHARPI_NO_ALLOC_SETUP_FAILED;
+            return nullptr;
+        }
+        per_device[device] = address;
+    }
+    return per_device[device];
+}
+
+int sharpi_sample_rows_no_alloc(const float* logits, int rows, int vocab, const float* temperature,
+                                const int* top_k, const float* top_p, const float* min_p, const float* uniform,
+                                int* out, cudaStream_t stream) {
+    if (rows <= 0) return SHARPI_OK;
+    if (vocab <= 0 || vocab > (1 << 24)) return SHARPI_BAD_ARGUMENT;
+    if ((unsigned long long)rows * (unsigned long long)vocab > (unsigned long long)SHARPI_NO_ALLOC_MAX_FLOATS)
+        return SHARPI_NO_ALLOC_TOO_LARGE;
+    int status = SHARPI_OK;
+    float* probs = no_alloc_work_area(&status);
+    if (probs == nullptr) return status;
+    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
+                                                            uniform, probs, out);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}

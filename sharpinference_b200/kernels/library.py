@@ -41,6 +41,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_apply_penalties": ("sampling", [P, I, P, P, P, P, P, P, I, P]),
     "sharpi_add_logit_bias": ("sampling", [P, I, P, P, P, I, P]),
     "sharpi_sample_rows": ("sampling", [P, I, I, P, P, P, P, P, P, P, P]),
+    "sharpi_sample_rows_no_alloc": ("sampling", [P, I, I, P, P, P, P, P, P, P]),
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}
