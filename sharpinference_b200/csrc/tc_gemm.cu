@@ -1,0 +1,314 @@
+// Grouped (per-expert) bf16 matrix products on the 5th-generation tensor cores: tcgen05.mma with
+// the accumulator in tensor memory, operands staged in shared memory by TMA, one elected thread
+// issuing the MMAs.  The reference runs each routed expert as per-token matvecs after choosing
+// the expert on the host (src/SharpInference.Engine/CudaForwardPass.cs:5554-5578); here all of a
+// step's rows, sorted by expert, go through one launch.
+//
+// Shape of the problem: rows sorted by expert (`group_offsets[e]` .. `group_offsets[e+1]`),
+// activations A [rows, K] bf16, weights W [E, N, K] bf16, both K-major.  A routed expert sees few
+// rows (1 .. a few hundred) and the work is streaming W once, so the MMA is laid out "swapped":
+// the 128-row M side of the instruction holds 128 weight rows, the N side holds a tile of
+// NT rows of activations (16 .. 256), and D[weight row, activation row] lives in tensor memory with
+// the weight rows on the 128 lanes.  One CTA computes one (expert, 128 weight rows, NT activation
+// rows) tile over all of K in steps of 64 elements.
+//
+// Two epilogues:
+//   MODE_STORE   C[out_row, n] = (or +=) D            fp32, out_row = out_rows[sorted row] or the sorted row
+//   MODE_SWIGLU  W holds gate rows [0, I) and up rows [I, 2I); the CTA accumulates the gate tile
+//                and the matching up tile side by side and writes
+//                act[sorted row, i] = silu(s g) * (s u) as bf16, s = row_scale[scale_rows[sorted row]]
+//                (the router weight scales gate and up before the nonlinearity,
+//                src/SharpInference.Engine/ForwardPass.cs:2082-2088).
+//
+// Warps: 0-3 read the accumulator (warp w owns TMEM lanes 32w .. 32w+31) and write the output;
+// warp 4 issues the TMA loads; warp 5 allocates tensor memory and issues the MMAs.  Every
+// mbarrier wait is bounded; on a timeout the kernel sets *status and winds down.
+//
+// Each output element is one fp32 accumulation over K in a fixed order inside the tensor core,
+// independent of which tile or batch the row fell into.
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+enum TcMode : int { MODE_STORE = 0, MODE_SWIGLU = 1 };
+
+constexpr int TC_BM = 128;   // weight rows per tile (MMA M)
+constexpr int TC_BK = 64;    // K elements per stage: 128 bytes, one swizzle row
+constexpr int TC_THREADS = 192;
+
+struct TcGemmParams {
+    const int* group_offsets;   // [E + 1]
+    const int* out_rows;        // MODE_STORE: nullable
+    const float* row_scale;     // MODE_SWIGLU: nullable
+    const int* scale_rows;      // MODE_SWIGLU: nullable
+    void* out;                  // MODE_STORE: float [*, N]; MODE_SWIGLU: bf16 [rows, I]
+    int* status;                // device word: 0 ok, else the code of the wait that gave up
+    int rows, N, K, E;          // N: weight rows per expert (MODE_SWIGLU: 2 I)
+    int accumulate;
+};
+
+template <int MODE, int NT>
+struct TcConfig {
+    static constexpr int W_TILES = (MODE == MODE_SWIGLU) ? 2 : 1;
+    static constexpr int W_BYTES = TC_BM * TC_BK * 2;
+    static constexpr int A_BYTES = NT * TC_BK * 2;
+    static constexpr int STAGE_BYTES = W_TILES * W_BYTES + A_BYTES;
+    // stages: what fits 108 KB (so that two CTAs share an SM) for small tiles, 200 KB otherwise
+    static constexpr int BUDGET = (STAGE_BYTES <= 36 * 1024) ? 108 * 1024 : 200 * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+    static_assert(STAGES >= 3, "a tile configuration must leave room for three stages");
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS_NEEDED = W_TILES * NT;
+    static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
+};
+
+template <int MODE, int NT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                       const TcGemmParams p) {
+    using Cfg = TcConfig<MODE, NT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + Cfg::STAGES;
+    uint64_t* accum_bar = empty_bar + Cfg::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);   // [0] expert, [1] first sorted row, [2] end row
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which tile is this CTA's ----------------------------------------------------------
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.y, e = 0, start = 0, end = 0;
+        for (; e < p.E; ++e) {
+            start = p.group_offsets[e];
+            end = p.group_offsets[e + 1];
+            const int tiles = (end - start + NT - 1) / NT;
+            if (tile < tiles) break;
+            tile -= tiles;
+        }
+        tile_info[0] = (e < p.E) ? e : -1;
+        tile_info[1] = start + tile * NT;
+        tile_info[2] = end;
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(accum_bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const int expert = tile_info[0];
+    if (expert < 0) return;                       // uniform: nothing allocated yet
+    const int row0 = tile_info[1], row_end = tile_info[2];
+    const int n0 = blockIdx.x * TC_BM;            // MODE_SWIGLU: index into [0, I)
+    const int I = p.N / 2;                        // MODE_SWIGLU only
+    const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ---- TMA producer ------------------------------------------------------------------
+        if (lane == 0) {
+            prefetch_tensormap(&map_w);
+            prefetch_tensormap(&map_a);
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                if (kb >= Cfg::STAGES) ok = mbar_wait(&empty_bar[s], ((kb / Cfg::STAGES) - 1) & 1);
+                if (!ok) { atomicExch(p.status, 1); break; }
+                uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                tma_load_3d(stage, &map_w, &full_bar[s], kb * TC_BK, n0, expert);
+                if (MODE == MODE_SWIGLU)
+                    tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kb * TC_BK, I + n0, expert);
+                tma_load_2d(stage + Cfg::W_TILES * Cfg::W_BYTES, &map_a, &full_bar[s], kb * TC_BK, row0);
+                issued = kb + 1;
+            }
+            if (!ok) {
+                // let the copies that were started land before the block goes away
+                for (int kb = max(0, issued - Cfg::STAGES); kb < issued; ++kb)
+                    mbar_wait(&full_bar[kb % Cfg::STAGES], (kb / Cfg::STAGES) & 1, 1u << 16);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer --------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc_bf16(TC_BM, NT);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                ok = mbar_wait(&full_bar[s], (kb / Cfg::STAGES) & 1);
+                if (!ok) { atomicExch(p.status, 2); break; }
+                tcgen05_fence_after();
+                const uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
+                const uint8_t* a_tile = stage + Cfg::W_TILES * Cfg::W_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    const uint32_t acc = (kb | k) != 0;
+                    const uint64_t db = smem_desc_k_sw128(a_tile, k * 32);
+                    mma_bf16_ss(tmem_base, smem_desc_k_sw128(stage, k * 32), db, idesc, acc);
+                    if (MODE == MODE_SWIGLU)
+                        mma_bf16_ss(tmem_base + NT, smem_desc_k_sw128(stage + Cfg::W_BYTES, k * 32), db, idesc, acc);
+                }
+                mma_commit(&empty_bar[s]);      // the stage is free when these MMAs have read it
+            }
+            if (ok) mma_commit(accum_bar);       // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: warps 0..3, thread = TMEM lane = weight row ---------------------------
+        const bool ok = mbar_wait(accum_bar, 0);
+        if (!ok) {
+            if (lane == 0) atomicExch(p.status, 3);
+        } else {
+            tcgen05_fence_after();
+            const int n = n0 + warp * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+            const int valid = min(NT, row_end - row0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                if (c0 >= valid) break;               // uniform over the warp
+                float g[16];
+                tmem_ld_16(lane_addr + c0, g);
+                if (MODE == MODE_SWIGLU) {
+                    float u[16];
+                    tmem_ld_16(lane_addr + NT + c0, u);
+                    if (n < I) {
+                        bf16* act = reinterpret_cast<bf16*>(p.out);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int r = row0 + c0 + j;
+                            if (c0 + j < valid) {
+                                const float s = p.row_scale ? p.row_scale[p.scale_rows ? p.scale_rows[r] : r] : 1.0f;
+                                const float gv = g[j] * s, uv = u[j] * s;
+                                act[(size_t)r * I + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                            }
+                        }
+                    }
+                } else if (n < p.N) {
+                    float* C = reinterpret_cast<float*>(p.out);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int r = row0 + c0 + j;
+                        if (c0 + j < valid) {
+                            float* dst = C + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
+                            *dst = p.accumulate ? *dst + g[j] : g[j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// bf16 tensor [d2, d1, d0] (d0 innermost, contiguous), box [1, box1, 64], 128-byte swizzle, zero fill.
+static bool make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box1) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const bool three = d2 > 0;
+    cuuint64_t dims[3] = {d0, d1, three ? d2 : 1};
+    cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+    cuuint32_t box[3] = {TC_BK, box1, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, three ? 3 : 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE, int NT>
+static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmParams& p, int n_tiles, int row_tiles,
+                  cudaStream_t stream) {
+    using Cfg = TcConfig<MODE, NT>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(tc_grouped_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::SMEM_BYTES) != cudaSuccess)
+            return SHARPI_LAUNCH_FAILED;
+        configured = true;
+    }
+    dim3 grid(n_tiles, row_tiles);
+    tc_grouped_gemm_kernel<MODE, NT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, p);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
+// `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes.
+SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
+                                      const int* out_rows, const float* row_scale, const int* scale_rows,
+                                      int* status, int rows, int N, int K, int E, int mode, int row_tile,
+                                      int accumulate, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return SHARPI_OK;
+    if (K <= 0 || E <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;          // TMA: rows 16-byte aligned
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return SHARPI_UNALIGNED;
+    if (mode == MODE_SWIGLU && (N % 2 != 0)) return SHARPI_BAD_ARGUMENT;
+    if (!status || !group_offsets) return SHARPI_BAD_ARGUMENT;
+    CUtensorMap mw, ma;
+    if (!make_map(&mw, W, (uint64_t)K, (uint64_t)N, (uint64_t)E, TC_BM)) return SHARPI_LAUNCH_FAILED;
+    if (!make_map(&ma, A, (uint64_t)K, (uint64_t)rows, 0, (uint32_t)row_tile)) return SHARPI_LAUNCH_FAILED;
+    TcGemmParams p;
+    p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
+    p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
+    const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
+    const int n_tiles = (n_out + TC_BM - 1) / TC_BM;
+    const long long row_tiles = (rows + row_tile - 1) / row_tile + E;
+    if (row_tiles > 65535) return SHARPI_BAD_ARGUMENT;
+#define TC_CASE(M, T) if (mode == M && row_tile == T) return launch<M, T>(mw, ma, p, n_tiles, (int)row_tiles, stream);
+    TC_CASE(MODE_STORE, 16) TC_CASE(MODE_STORE, 32) TC_CASE(MODE_STORE, 64) TC_CASE(MODE_STORE, 128) TC_CASE(MODE_STORE, 256)
+    TC_CASE(MODE_SWIGLU, 16) TC_CASE(MODE_SWIGLU, 32) TC_CASE(MODE_SWIGLU, 64) TC_CASE(MODE_SWIGLU, 128) TC_CASE(MODE_SWIGLU, 256)
+#undef TC_CASE
+    return SHARPI_BAD_ARGUMENT;
+}
+
+// out[r, :] = in[rows[r], :] for bf16 rows of width K (a multiple of 8): the activations sorted by
+// expert, so that TMA can fetch an expert's rows as one tile.
+__global__ void gather_rows_bf16_kernel(const uint4* __restrict__ in, const int* __restrict__ rows,
+                                        uint4* __restrict__ out, int vec_per_row) {
+    const int r = blockIdx.x;
+    const uint4* src = in + (size_t)rows[r] * vec_per_row;
+    uint4* dst = out + (size_t)r * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
+}
+
+SHARPI_API int sharpi_gather_rows_bf16(const void* in, const int* rows, void* out, int R, int K, cudaStream_t stream) {
+    if (R <= 0) return SHARPI_OK;
+    if (K <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return SHARPI_UNALIGNED;
+    gather_rows_bf16_kernel<<<R, 128, 0, stream>>>((const uint4*)in, rows, (uint4*)out, K / 8);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}

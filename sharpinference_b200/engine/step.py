@@ -22,6 +22,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..kernels import ops
 from ..parts.base import StepContext
 
 
@@ -49,6 +50,9 @@ class StepRunner:
         # (one int32 [T] tensor per routed schedule entry, in schedule order).  The reference
         # prints the same with SHARPI_TRACE_ROUTERS (src/SharpInference.Engine/ForwardPass.cs:2042-2056).
         self.trace_router = False
+        # after every step, read the word in which a tensor-core kernel records a wait that gave up
+        # (a 4-byte copy; the step's result is read by the host right after anyway)
+        self.check_kernel_status = True
         self.last_router_choices: List[torch.Tensor] = []
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -152,6 +156,8 @@ class StepRunner:
         if self.trace_router:
             ctx.extras["router_choices"] = []
         logits = self.model.forward(ctx)
+        if self.check_kernel_status:
+            ops.check_status(self.device)
         self.last_router_choices = ctx.extras.get("router_choices", [])
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))

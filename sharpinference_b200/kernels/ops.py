@@ -205,6 +205,93 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
     return out
 
 
+# ---------------------------------------------------------------------------------------
+# tensor-core kernels (tcgen05 / TMEM / TMA)
+# ---------------------------------------------------------------------------------------
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device word in which a tensor-core kernel records a wait that gave up (0 = none)."""
+    device = torch.device(device)
+    w = _status_words.get(device)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device] = w
+    return w
+
+
+def check_status(device) -> None:
+    """Raise if a tensor-core kernel gave up on a wait since the last check (synchronises)."""
+    w = _status_words.get(torch.device(device))
+    if w is not None:
+        code = int(w.item())
+        if code != 0:
+            w.zero_()
+            raise KernelError(f"a tensor-core kernel gave up waiting (code {code}: 1 = free stage, 2 = loaded stage, "
+                              f"3 = finished accumulator); its output is incomplete")
+
+
+TC_MODE_STORE, TC_MODE_SWIGLU = 0, 1
+
+
+def tc_row_tile(rows: int) -> int:
+    """Activation rows per CTA for a grouped product over `rows` rows in all."""
+    if rows <= 128:
+        return 16
+    if rows <= 256:
+        return 32
+    if rows <= 512:
+        return 64
+    return 128
+
+
+def gather_rows_bf16(x: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[r] = x[rows[r]]`` for bfloat16 rows whose width is a multiple of 8."""
+    _need(x, "x", torch.bfloat16)
+    _need(rows, "rows", torch.int32)
+    R, K = rows.numel(), x.shape[-1]
+    if out is None:
+        out = torch.empty((R, K), dtype=torch.bfloat16, device=x.device)
+    check(kernel("sharpi_gather_rows_bf16")(x.data_ptr(), rows.data_ptr(), out.data_ptr(), R, K, _stream()),
+          "sharpi_gather_rows_bf16")
+    return out
+
+
+def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, *, mode: int,
+                    out: Optional[torch.Tensor] = None, out_rows: Optional[torch.Tensor] = None,
+                    row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
+                    accumulate: bool = False, row_tile: Optional[int] = None) -> torch.Tensor:
+    """Per-expert products on the tensor cores.  ``a`` bfloat16 [rows, K] sorted by expert,
+    ``w`` bfloat16 [E, N, K], ``group_offsets`` int32 [E + 1].
+
+    ``mode=TC_MODE_STORE``: float32 ``out[out_rows[r] or r] (+)= a[r] . w[e(r)]^T``, shape [*, N].
+    ``mode=TC_MODE_SWIGLU``: ``w`` holds gate rows then up rows (N = 2 I); bfloat16
+    ``out[r] = silu(s g) * (s u)``, shape [rows, I], ``s = row_scale[scale_rows[r]]``.
+    """
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    _need(group_offsets, "group_offsets", torch.int32)
+    rows, K = a.shape
+    E, N, Kw = w.shape
+    if Kw != K or group_offsets.numel() != E + 1:
+        raise KernelError(f"shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, offsets {group_offsets.numel()}")
+    if K % 8 != 0:
+        raise KernelError(f"the tensor-core product needs an inner size that is a multiple of 8, found {K}")
+    if out is None:
+        if accumulate:
+            raise KernelError("accumulate=True needs an output tensor to add to")
+        out = (torch.empty((rows, N // 2), dtype=torch.bfloat16, device=a.device) if mode == TC_MODE_SWIGLU
+               else torch.empty((rows, N), dtype=torch.float32, device=a.device))
+    _need(out, "out", torch.bfloat16 if mode == TC_MODE_SWIGLU else torch.float32)
+    status = status_word(a.device)
+    check(kernel("sharpi_tc_grouped_gemm")(a.data_ptr(), w.data_ptr(), group_offsets.data_ptr(), out.data_ptr(),
+                                           _ptr(out_rows), _ptr(row_scale), _ptr(scale_rows), status.data_ptr(),
+                                           rows, N, K, E, mode, row_tile or tc_row_tile(rows), int(accumulate),
+                                           _stream()), "sharpi_tc_grouped_gemm")
+    return out
+
+
 def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False):
     """Top-1 sigmoid routing.  Returns ``(expert_id int32 [T], weight fp32 [T], logits or None)``."""
     _need(h32, "h32", torch.float32)

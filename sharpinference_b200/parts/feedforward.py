@@ -49,6 +49,11 @@ class MoESigmoidTop1(FeedForward):
         self.shared = shared
         self.num_experts = E
         self.act_dtype = act_dtype
+        # the tensor-core path takes bfloat16 weights whose inner sizes are multiples of 8 (TMA rows
+        # must start on 16 bytes); everything else runs the CUDA-core kernels
+        self._tensor_core = (experts_gate_up.weight.dtype == torch.bfloat16
+                             and experts_down.weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
+                             and experts_gate_up.in_features % 8 == 0 and experts_down.in_features % 8 == 0)
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None) -> torch.Tensor:
         T = h.shape[0]
@@ -62,6 +67,13 @@ class MoESigmoidTop1(FeedForward):
             y = self.shared.forward(ctx, h)
         else:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        if self._tensor_core and h.dtype == torch.bfloat16:
+            h_sorted = ops.gather_rows_bf16(h, sorted_rows)
+            act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
+                                      row_scale=weight, scale_rows=sorted_rows)
+            ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
+                                out_rows=sorted_rows, accumulate=True)
+            return y
         gu = self.experts_gate_up(h, offsets, rows=T, a_rows=sorted_rows)          # sorted order
         act = ops.swiglu(gu, self.act_dtype, row_scale=weight, scale_rows=sorted_rows)
         self.experts_down(act, offsets, rows=T, out_rows=sorted_rows, out=y, accumulate=True)

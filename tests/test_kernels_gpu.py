@@ -376,3 +376,75 @@ def test_no_cpu_path(ops):
                                     torch.zeros(1, dtype=torch.int32, device=DEV),
                                     torch.zeros(1, dtype=torch.int32, device=DEV), nq=3, nkv=2, d=16, page_size=4,
                                     mask_kind=0, mask_span=1, scale=1.0)
+
+
+# ---------------------------------------------------------------------------------------
+# tensor-core grouped product (tcgen05 / TMEM / TMA)
+# ---------------------------------------------------------------------------------------
+def grouped_case(T, E, K, seed, empty=()):
+    g = torch.Generator().manual_seed(seed)
+    expert = torch.randint(0, E, (T,), generator=g)
+    for e in empty:
+        expert[expert == e] = (e + 1) % E
+    order = torch.argsort(expert, stable=True)
+    counts = torch.bincount(expert, minlength=E)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(counts, 0)]).to(torch.int32).to(DEV)
+    a = (torch.randn(T, K, generator=g)).to(torch.bfloat16)
+    return expert, order, offsets, a
+
+
+@pytest.mark.parametrize("T,E,N,K,row_tile", [(8, 4, 256, 128, 16), (5, 3, 200, 72, 16), (64, 16, 384, 512, 16),
+                                              (300, 5, 136, 264, 64), (700, 3, 520, 128, 128), (70, 2, 128, 64, 32),
+                                              (1500, 4, 256, 192, 256)])
+def test_tc_grouped_gemm_store(ops, T, E, N, K, row_tile):
+    expert, order, offsets, a = grouped_case(T, E, K, seed=T + N, empty=(1,) if E > 2 else ())
+    w = rnd(E, N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
+    a_sorted = a[order].contiguous().to(DEV)
+    ref = torch.stack([a[t].double() @ w[int(expert[t])].double().cpu().T for t in range(T)])
+    sorted_rows = order.to(torch.int32).to(DEV)
+    out = ops.tc_grouped_gemm(a_sorted, w, offsets, mode=ops.TC_MODE_STORE, row_tile=row_tile)
+    ops.check_status(DEV)
+    assert torch.allclose(out.double().cpu(), ref[order], rtol=1e-4, atol=1e-3)
+    base = rnd(T, N, seed=4)
+    acc = base.clone()
+    ops.tc_grouped_gemm(a_sorted, w, offsets, mode=ops.TC_MODE_STORE, out=acc, out_rows=sorted_rows, accumulate=True,
+                        row_tile=row_tile)
+    ops.check_status(DEV)
+    assert torch.allclose(acc.double().cpu(), base.double().cpu() + ref, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("T,E,I,K,row_tile", [(8, 4, 128, 128, 16), (7, 3, 40, 88, 16), (64, 16, 256, 320, 16),
+                                              (300, 5, 72, 264, 64), (900, 3, 200, 128, 128), (600, 2, 136, 64, 256)])
+def test_tc_grouped_gemm_swiglu(ops, T, E, I, K, row_tile):
+    expert, order, offsets, a = grouped_case(T, E, K, seed=T + I, empty=(0,) if E > 2 else ())
+    w = rnd(E, 2 * I, K, dtype=torch.bfloat16, scale=0.1, seed=5)
+    scale = (torch.rand(T, generator=torch.Generator().manual_seed(6)) * 0.5 + 0.25)
+    a_sorted = ops.gather_rows_bf16(a.to(DEV), order.to(torch.int32).to(DEV))
+    assert torch.equal(a_sorted.cpu(), a[order])
+    act = ops.tc_grouped_gemm(a_sorted, w, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale.to(DEV),
+                              scale_rows=order.to(torch.int32).to(DEV), row_tile=row_tile)
+    ops.check_status(DEV)
+    ref = []
+    for t in order.tolist():
+        gu = (a[t].double() @ w[int(expert[t])].double().cpu().T) * float(scale[t])
+        g, u = gu[:I], gu[I:]
+        ref.append(g / (1 + torch.exp(-g)) * u)
+    ref = torch.stack(ref)
+    assert act.dtype == torch.bfloat16 and act.shape == (T, I)
+    assert torch.allclose(act.double().cpu(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+
+
+def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
+    """A row alone, in a small batch and in a large one gives bit-identical results."""
+    E, N, K = 4, 256, 320
+    w = rnd(E, N, K, dtype=torch.bfloat16, scale=0.1, seed=7)
+    a = rnd(400, K, dtype=torch.bfloat16, seed=8)
+    expert = torch.arange(400) % E
+    order = torch.argsort(expert, stable=True)
+    offsets = torch.tensor([0, 100, 200, 300, 400], dtype=torch.int32, device=DEV)
+    big = ops.tc_grouped_gemm(a[order.to(DEV)].contiguous(), w, offsets, mode=ops.TC_MODE_STORE, row_tile=128)
+    t = 37                                                   # row 37 goes to expert 1, sorted position 100 + 9
+    one = ops.tc_grouped_gemm(a[t:t + 1].contiguous(), w, torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device=DEV),
+                              mode=ops.TC_MODE_STORE, row_tile=16)
+    ops.check_status(DEV)
+    assert torch.equal(one[0], big[100 + 9])
