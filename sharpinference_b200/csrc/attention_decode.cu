@@ -1,0 +1,292 @@
+// Paged attention for rows that bring one query each (decode), bf16 cache, split over the keys.
+//
+// The work is reading every visible key and value once, so the kernel is organised around
+// bytes in flight: one CTA takes one (row, kv head, split of 256 keys) and serves all the query
+// heads of that kv head at once, so keys and values are read once per group, not once per
+// query head.  Splits sit at absolute multiples of 256 positions, so the order in which a row's
+// keys are reduced depends on the row's position alone, never on the batch.  Each CTA writes an
+// unnormalised partial (max, sum, weighted values); a second kernel merges a row's partials.
+//
+// The reference's counterparts: llm_attention_splitkv_grouped + llm_attention_combine (fixed
+// 512-key splits, one block per (kv head, split), scalar math;
+// src/SharpInference.Cuda/CudaTextKernels.cs:8829-9072) and llm_attention_ragged for several
+// sequences in one launch (src/SharpInference.Cuda/CudaRaggedKernels.cs:291-325).  Here QK^T and PV
+// run on the tensor cores (m16n8k16, the query heads of a group padded to 16 rows), softmax
+// statistics are fp32, masks are full / chunk / window as in common.cuh.
+#include "common.cuh"
+#include "mma_sync.cuh"
+
+using namespace mma16;
+
+constexpr int DEC_SPLIT = 256;   // keys per CTA
+constexpr int DEC_CHUNK = 32;    // keys per warp pass
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+
+struct DecodeArgs {
+    const bf16* q;            // [T, nq, D]
+    const bf16* kv;           // [pages, 2, nkv, page_size, D]
+    const int* block_table;   // [B, max_blocks]
+    const int* row_req;       // [T]
+    const int* positions;     // [T]
+    const int* rows;          // [R] rows served by this launch, or null for rows 0 .. R-1
+    float* part_o;            // [R, nq, max_splits, D]
+    float* part_ml;           // [R, nq, max_splits, 2]   (max in log2 units, sum)
+    bf16* out;                // [T, nq * D]
+    int nq, nkv, max_blocks, page_size, mask_kind, mask_span, max_splits;
+    float scale_log2;         // softmax scale * log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(DecodeArgs a) {
+    constexpr int LD = D + 8;       // padded row, in elements: 8 ldmatrix rows fall into different banks
+    constexpr int VEC = D / 8;      // 16-byte pieces per row
+    extern __shared__ __align__(16) uint8_t smem_bytes[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_bytes);       // [16][LD]
+    bf16* kv_s = q_s + 16 * LD;                              // [warps][2][DEC_CHUNK][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = a.nq / a.nkv;
+    const int groups = (G + 15) / 16;
+    const int kvh = blockIdx.y / groups, hg = blockIdx.y % groups;
+    const int head0 = kvh * G + hg * 16;
+    const int heads_here = min(16, G - hg * 16);
+    const int ri = blockIdx.z;
+    const int r = a.rows ? a.rows[ri] : ri;
+    const int pos = a.positions[r];
+    const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
+    const int split = lo / DEC_SPLIT + blockIdx.x;
+    const int k_begin = max(lo, split * DEC_SPLIT);
+    const int k_end = min(pos, split * DEC_SPLIT + DEC_SPLIT - 1);
+    if (k_begin > k_end) return;
+
+    // queries of this group: rows >= heads_here are zero
+    for (int idx = threadIdx.x; idx < 16 * VEC; idx += DEC_THREADS) {
+        const int g = idx / VEC, c = idx % VEC;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (g < heads_here) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)r * a.nq + head0 + g) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + g * LD + c * 8) = v;
+    }
+    __syncthreads();
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * LD + ks * 16 + (lane / 16) * 8);
+
+    bf16* k_s = kv_s + (size_t)warp * 2 * DEC_CHUNK * LD;
+    bf16* v_s = k_s + DEC_CHUNK * LD;
+    const int* table = a.block_table + (size_t)a.row_req[r] * a.max_blocks;
+    const size_t plane = (size_t)a.nkv * a.page_size * D;
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    for (int c = warp; c < DEC_SPLIT / DEC_CHUNK; c += DEC_WARPS) {
+        const int chunk0 = split * DEC_SPLIT + c * DEC_CHUNK;
+        if (chunk0 > k_end || chunk0 + DEC_CHUNK - 1 < k_begin) continue;   // uniform over the warp
+        for (int idx = lane; idx < DEC_CHUNK * VEC; idx += 32) {
+            const int row = idx / VEC, col = idx % VEC;
+            const int key = chunk0 + row;
+            bool valid = key >= k_begin && key <= k_end;
+            const int page = valid ? table[key / a.page_size] : -1;
+            valid = valid && page >= 0;
+            const bf16* src = a.kv;
+            if (valid) src = a.kv + (size_t)page * 2 * plane + ((size_t)kvh * a.page_size + key % a.page_size) * D + col * 8;
+            cp_async_16(k_s + row * LD + col * 8, src, valid ? 16 : 0);
+            cp_async_16(v_s + row * LD + col * 8, valid ? src + plane : src, valid ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+
+        // S = Q K^T for 32 keys: 4 tiles of 8 keys
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+#pragma unroll
+            for (int k2 = 0; k2 < D / 32; ++k2) {
+                uint32_t b[4];
+                ldmatrix_x4(b, k_s + (nt * 8 + (lane % 8)) * LD + k2 * 32 + (lane / 8) * 8);
+                mma_bf16(s[nt], qa[2 * k2], b[0], b[1]);
+                mma_bf16(s[nt], qa[2 * k2 + 1], b[2], b[3]);
+            }
+            if (D % 32 != 0) {
+                uint32_t b[2];
+                ldmatrix_x2(b, k_s + (nt * 8 + (lane % 8)) * LD + (D - 16) + ((lane / 8) % 2) * 8);
+                mma_bf16(s[nt], qa[D / 16 - 1], b[0], b[1]);
+            }
+        }
+        // mask, running max and sum (rows lane/4 and lane/4 + 8 of the group)
+        float m_c[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = chunk0 + nt * 8 + (lane % 4) * 2 + (e & 1);
+                const bool valid = key >= k_begin && key <= k_end;
+                s[nt][e] = valid ? s[nt][e] * a.scale_log2 : -INFINITY;
+                m_c[e >> 1] = fmaxf(m_c[e >> 1], s[nt][e]);
+            }
+        float corr[2], l_c[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 1));
+            m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 2));
+            const float m_new = fmaxf(m_run[h], m_c[h]);
+            corr[h] = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_run[e >> 1]);
+                s[nt][e] = p;
+                l_c[e >> 1] += p;
+            }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 1);
+            l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 2);
+            l_run[h] = l_run[h] * corr[h] + l_c[h];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V: P (16 x 32) straight from the S accumulators
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            pa[j][0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+            pa[j][1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+            pa[j][2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+            pa[j][3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+        }
+#pragma unroll
+        for (int d2 = 0; d2 < D / 16; ++d2)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, v_s + (j * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
+                mma_bf16(o[2 * d2], pa[j], b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], pa[j], b[2], b[3]);
+            }
+        __syncwarp();
+    }
+
+    // each warp leaves its partial in its own staging area, then the block merges the four
+    float* o_w = reinterpret_cast<float*>(k_s);                 // [16][D]
+    float* ml_w = o_w + 16 * D;                                  // [16][2]
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            o_w[(lane / 4 + 8 * (e >> 1)) * D + i * 8 + (lane % 4) * 2 + (e & 1)] = o[i][e];
+    if (lane % 4 == 0) {
+        ml_w[(lane / 4) * 2] = m_run[0];
+        ml_w[(lane / 4) * 2 + 1] = l_run[0];
+        ml_w[(lane / 4 + 8) * 2] = m_run[1];
+        ml_w[(lane / 4 + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    const size_t warp_stride = (size_t)2 * DEC_CHUNK * LD * sizeof(bf16) / sizeof(float);
+    const float* base_o = reinterpret_cast<const float*>(kv_s);
+    for (int idx = threadIdx.x; idx < heads_here * D; idx += DEC_THREADS) {
+        const int g = idx / D, dd = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, base_o[w * warp_stride + 16 * D + g * 2]);
+        float acc = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = base_o[w * warp_stride + 16 * D + g * 2];
+            const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+            acc += f * base_o[w * warp_stride + g * D + dd];
+            L += f * base_o[w * warp_stride + 16 * D + g * 2 + 1];
+        }
+        const size_t slot = ((size_t)ri * a.nq + head0 + g) * a.max_splits + blockIdx.x;
+        a.part_o[slot * D + dd] = acc;
+        if (dd == 0) {
+            a.part_ml[slot * 2] = M;
+            a.part_ml[slot * 2 + 1] = L;
+        }
+    }
+}
+
+template <int D>
+__global__ void attn_decode_merge_kernel(DecodeArgs a) {
+    const int ri = blockIdx.x, head = blockIdx.y;
+    const int r = a.rows ? a.rows[ri] : ri;
+    const int pos = a.positions[r];
+    const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
+    const int n_s = pos / DEC_SPLIT - lo / DEC_SPLIT + 1;
+    const size_t slot0 = ((size_t)ri * a.nq + head) * a.max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_s; ++s) M = fmaxf(M, a.part_ml[(slot0 + s) * 2]);
+    float L = 0.0f;
+    for (int s = 0; s < n_s; ++s) L += exp2f(a.part_ml[(slot0 + s) * 2] - M) * a.part_ml[(slot0 + s) * 2 + 1];
+    const float inv = 1.0f / L;
+    for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_s; ++s) acc += exp2f(a.part_ml[(slot0 + s) * 2] - M) * a.part_o[(slot0 + s) * D + dd];
+        a.out[((size_t)r * a.nq + head) * D + dd] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int D>
+static int launch_decode(const DecodeArgs& a, int R, int splits, cudaStream_t stream) {
+    constexpr int LD = D + 8;
+    constexpr int SMEM = (16 * LD + DEC_WARPS * 2 * DEC_CHUNK * LD) * 2;
+    static_assert(2 * DEC_CHUNK * LD * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
+            cudaSuccess)
+            return SHARPI_LAUNCH_FAILED;
+        configured = true;
+    }
+    const int G = a.nq / a.nkv;
+    dim3 grid(splits, a.nkv * ((G + 15) / 16), R);
+    attn_decode_split_kernel<D><<<grid, DEC_THREADS, SMEM, stream>>>(a);
+    SHARPI_CHECK_LAUNCH();
+    attn_decode_merge_kernel<D><<<dim3(R, a.nq), D >= 64 ? 64 : 32, 0, stream>>>(a);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// `splits` is the largest number of 256-key splits any served row needs; part_o / part_ml are
+// scratch of [R, nq, splits, D] and [R, nq, splits, 2] floats.
+SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int* block_table, const int* row_req,
+                                       const int* positions, const int* rows, float* part_o, float* part_ml,
+                                       void* out, int R, int nq, int nkv, int d, int max_blocks, int page_size,
+                                       int mask_kind, int mask_span, int splits, float scale, cudaStream_t stream) {
+    if (R <= 0) return SHARPI_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || splits <= 0 || R > 65535 ||
+        nq > 65535)
+        return SHARPI_BAD_ARGUMENT;
+    if (mask_kind != SHARPI_MASK_FULL && mask_span <= 0) return SHARPI_BAD_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv)) & 15) return SHARPI_UNALIGNED;
+    DecodeArgs a;
+    a.q = (const bf16*)q; a.kv = (const bf16*)kv; a.block_table = block_table; a.row_req = row_req;
+    a.positions = positions; a.rows = rows; a.part_o = part_o; a.part_ml = part_ml; a.out = (bf16*)out;
+    a.nq = nq; a.nkv = nkv; a.max_blocks = max_blocks; a.page_size = page_size; a.mask_kind = mask_kind;
+    a.mask_span = mask_span; a.max_splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
+    switch (d) {
+        case 16: return launch_decode<16>(a, R, splits, stream);
+        case 32: return launch_decode<32>(a, R, splits, stream);
+        case 48: return launch_decode<48>(a, R, splits, stream);
+        case 64: return launch_decode<64>(a, R, splits, stream);
+        case 80: return launch_decode<80>(a, R, splits, stream);
+        case 96: return launch_decode<96>(a, R, splits, stream);
+        case 112: return launch_decode<112>(a, R, splits, stream);
+        case 128: return launch_decode<128>(a, R, splits, stream);
+        default: return SHARPI_BAD_ARGUMENT;   // other head sizes use the generic kernel
+    }
+}

@@ -38,6 +38,9 @@ class StepEntry:
 
 
 class StepRunner:
+    ATTENTION_TILE = 64        # rows of one request that one attention CTA serves
+    DECODE_ROWS_UP_TO = 4      # entries this short are served row by row by the split-KV kernel
+
     def __init__(self, model, cache: CacheManager):
         self.model = model
         self.cache = cache
@@ -93,9 +96,16 @@ class StepRunner:
         row_request = np.empty(T, dtype=np.int32)
         row_offsets = np.zeros(B + 1, dtype=np.int32)
         want_rows: List[int] = []
+        tiles: List[int] = []            # (first row, rows, first position, request) per attention tile
+        decode_rows: List[int] = []
         r = 0
         for b, e in enumerate(entries):
             n = lengths[b]
+            if n <= self.DECODE_ROWS_UP_TO:
+                decode_rows.extend(range(r, r + n))
+            else:
+                for t0 in range(0, n, self.ATTENTION_TILE):
+                    tiles.extend((r + t0, min(self.ATTENTION_TILE, n - t0), starts[b] + t0, b))
             tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int64)
             positions[r:r + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             row_request[r:r + n] = b
@@ -112,7 +122,8 @@ class StepRunner:
         G = len(cache.groups)
         R = len(want_rows)
         # layout of the one int32 staging buffer
-        sizes = [T, T, T, B, B + 1, B, R] + [B * width] * G
+        n_tiles, n_dec = len(tiles) // 4, len(decode_rows)
+        sizes = [T, T, T, B, B + 1, B, R] + [B * width] * G + [4 * n_tiles, n_dec]
         offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         host = torch.empty(int(offsets[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
         hv = host.numpy()
@@ -130,6 +141,8 @@ class StepRunner:
                 table[b, :len(t)] = t
             o = offsets[7 + gi]
             hv[o:o + B * width] = table.reshape(-1)
+        hv[offsets[7 + G]:offsets[7 + G] + 4 * n_tiles] = tiles
+        hv[offsets[8 + G]:offsets[8 + G] + n_dec] = decode_rows
         dev = host.to(self.device, non_blocking=True)
 
         def view(i: int, n: int) -> torch.Tensor:
@@ -143,6 +156,8 @@ class StepRunner:
             host_starts=starts, host_lengths=lengths, host_state_slots=slots,
             max_rows_per_request=max(lengths), max_context=max(s + n for s, n in zip(starts, lengths)),
             decode_only=all(n == 1 for n in lengths),
+            attn_tiles=view(7 + G, 4 * n_tiles).view(n_tiles, 4) if n_tiles else None, num_attn_tiles=n_tiles,
+            decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
         )
 
     @torch.no_grad()

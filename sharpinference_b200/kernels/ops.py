@@ -165,6 +165,59 @@ def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table
     return out
 
 
+FAST_ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128)
+DECODE_SPLIT = 256
+
+
+def decode_splits(max_context: int, mask_kind: int, mask_span: int) -> int:
+    """An upper bound on the 256-key splits a decode row needs (the kernel skips the empty ones)."""
+    full = (max_context + DECODE_SPLIT - 1) // DECODE_SPLIT
+    if mask_kind == MASK_FULL:
+        return max(full, 1)
+    return max(1, min(full, (mask_span + DECODE_SPLIT - 1) // DECODE_SPLIT + 1))
+
+
+def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, row_req: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, *, rows: Optional[torch.Tensor], num_rows: int,
+                     nq: int, nkv: int, d: int, page_size: int, mask_kind: int, mask_span: int, scale: float,
+                     max_context: int) -> None:
+    """Split-KV paged attention for rows that bring one query each (bfloat16).  ``rows`` (int32) names
+    the rows to serve, or None for rows ``0 .. num_rows - 1``; results go to ``out[row]``."""
+    _need(q, "q", torch.bfloat16)
+    _need(kv_layer, "kv_layer", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(block_table, "block_table", torch.int32)
+    if d not in FAST_ATTENTION_HEAD_SIZES:
+        raise KernelError(f"head size {d} is not served by the tensor-core attention kernels "
+                          f"({FAST_ATTENTION_HEAD_SIZES}); use the generic kernel")
+    splits = decode_splits(max_context, mask_kind, mask_span)
+    part_o = torch.empty((num_rows, nq, splits, d), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((num_rows, nq, splits, 2), dtype=torch.float32, device=q.device)
+    check(kernel("sharpi_attention_decode")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
+                                            row_req.data_ptr(), positions.data_ptr(), _ptr(rows), part_o.data_ptr(),
+                                            part_ml.data_ptr(), out.data_ptr(), num_rows, nq, nkv, d,
+                                            block_table.shape[-1], page_size, mask_kind, mask_span, splits,
+                                            float(scale), _stream()), "sharpi_attention_decode")
+
+
+def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
+                      out: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int, mask_kind: int,
+                      mask_span: int, scale: float) -> None:
+    """Paged attention for tiles of up to 64 consecutive rows of one request (bfloat16).  ``tiles`` is
+    int32 [n, 4]: first row, number of rows, position of the first row, request index."""
+    _need(q, "q", torch.bfloat16)
+    _need(kv_layer, "kv_layer", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32)
+    if d not in FAST_ATTENTION_HEAD_SIZES:
+        raise KernelError(f"head size {d} is not served by the tensor-core attention kernels "
+                          f"({FAST_ATTENTION_HEAD_SIZES}); use the generic kernel")
+    check(kernel("sharpi_attention_prefill")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
+                                             tiles.data_ptr(), out.data_ptr(), tiles.shape[0], nq, nkv, d,
+                                             block_table.shape[-1], page_size, mask_kind, mask_span, float(scale),
+                                             _stream()), "sharpi_attention_prefill")
+
+
 def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
             out_rows: Optional[torch.Tensor] = None, rows: Optional[int] = None, accumulate: bool = False

@@ -70,7 +70,22 @@ class PagedAttention(Mixer):
                      page_size=slot.page_size, pairing=pairing,
                      l2_eps=self.qk_norm.eps if self.qk_norm is not None else -1.0,
                      temp_attn_scale=attn_scale, temp_floor_scale=floor_scale, write_kv=slot.writes_cache)
-        o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
-                                        page_size=slot.page_size, mask_kind=_MASK_CODE[self.cache_spec.kind],
-                                        mask_span=max(self.cache_spec.span, 1), scale=self.softmax_scale)
+        mask_kind, mask_span = _MASK_CODE[self.cache_spec.kind], max(self.cache_spec.span, 1)
+        if self.act_dtype == torch.bfloat16 and d in ops.FAST_ATTENTION_HEAD_SIZES and \
+                ctx.num_attn_tiles + ctx.num_decode_rows > 0:
+            # tensor-core kernels: tiles of prompt rows, and single rows split over their keys
+            o = torch.empty((T, nq * d), dtype=torch.bfloat16, device=h.device)
+            if ctx.num_attn_tiles:
+                ops.attention_prefill(q, slot.kv, table, ctx.attn_tiles, o, nq=nq, nkv=nkv, d=d,
+                                      page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
+                                      scale=self.softmax_scale)
+            if ctx.num_decode_rows:
+                ops.attention_decode(q, slot.kv, table, ctx.row_request, ctx.positions, o, rows=ctx.decode_rows,
+                                     num_rows=ctx.num_decode_rows, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
+                                     mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale,
+                                     max_context=ctx.max_context)
+        else:
+            o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
+                                            page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
+                                            scale=self.softmax_scale)
         return self.out(o)

@@ -107,6 +107,13 @@ class StepContext:
     max_rows_per_request: int = 0
     max_context: int = 0                    # highest position + 1 over the step
     decode_only: bool = False               # every request brings exactly one row
+    # how attention kernels split the step's rows: tiles of up to 64 consecutive rows of one request
+    # (int32 [n, 4]: first row, rows, first position, request index) for portions of prompts, and a
+    # list of single rows (int32 [m]; None with num_decode_rows == num_tokens means "all rows")
+    attn_tiles: Optional[torch.Tensor] = None
+    num_attn_tiles: int = 0
+    decode_rows: Optional[torch.Tensor] = None
+    num_decode_rows: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)
 
 

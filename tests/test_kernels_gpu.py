@@ -448,3 +448,116 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
                               mode=ops.TC_MODE_STORE, row_tile=16)
     ops.check_status(DEV)
     assert torch.equal(one[0], big[100 + 9])
+
+
+# ---------------------------------------------------------------------------------------
+# tensor-core attention kernels (bfloat16): single rows split over their keys, and tiles of rows
+# ---------------------------------------------------------------------------------------
+MASKS = {"full": (0, lambda span: (lambda p: 0)), "chunk": (1, lambda span: (lambda p: p // span * span)),
+         "window": (2, lambda span: (lambda p: max(0, p - span + 1)))}
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 4), (6, 3, 48, 16), (5, 1, 128, 64), (40, 8, 128, 64), (34, 2, 64, 32),
+                                         (3, 3, 112, 16)])
+@pytest.mark.parametrize("mask", [("full", 0), ("chunk", 300), ("chunk", 256), ("window", 100), ("window", 700)])
+def test_attention_decode_rows(ops, nq, nkv, d, ps, mask):
+    lens = [1000, 37, 1, 513, 256, 257]
+    kv, table, ks, vs = paged_setup(lens, nkv, d, ps, torch.bfloat16, seed=d + ps + nq)
+    rows = [(0, 999), (1, 36), (2, 0), (3, 512), (4, 255), (5, 256), (0, 511), (0, 600)]
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([b for b, _ in rows], dtype=torch.int32, device=DEV)
+    q = rnd(len(rows), nq, d, dtype=torch.bfloat16, seed=12)
+    kind, span = mask
+    code, lo_factory = MASKS[kind]
+    scale = 1.0 / math.sqrt(d)
+    ref = attention_ref(q.cpu(), ks, vs, positions.cpu(), row_req.cpu(), lo_factory(span), scale, nq, nkv)
+    out = torch.zeros(len(rows), nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=len(rows), nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=code, mask_span=max(span, 1), scale=scale, max_context=1000)
+    assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2)
+    # a subset of the rows, named by index; the others stay untouched
+    some = torch.tensor([6, 1, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.full_like(out, 7.0)
+    ops.attention_decode(q, kv, table, row_req, positions, out2, rows=some, num_rows=3, nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=code, mask_span=max(span, 1), scale=scale, max_context=1000)
+    assert torch.equal(out2[some.long()], out[some.long()])
+    rest = [i for i in range(len(rows)) if i not in (6, 1, 3)]
+    assert bool((out2[rest] == 7.0).all())
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 4), (6, 3, 48, 16), (5, 1, 128, 64), (8, 2, 128, 16), (3, 3, 80, 32)])
+@pytest.mark.parametrize("mask", [("full", 0), ("chunk", 100), ("chunk", 64), ("window", 50), ("window", 200)])
+def test_attention_prefill_tiles(ops, nq, nkv, d, ps, mask):
+    """Portions of three requests in one launch: one from an empty cache, one continuing at an odd
+    position across a chunk edge, one short."""
+    lens = [333, 150, 9]
+    kv, table, ks, vs = paged_setup(lens, nkv, d, ps, torch.bfloat16, seed=d + ps)
+    portions = [(0, 0, 333), (1, 77, 73), (2, 4, 5)]                     # request, first position, rows
+    rows, tiles = [], []
+    for b, p0, n in portions:
+        for t0 in range(0, n, 64):
+            tiles.append([len(rows) + t0, min(64, n - t0), p0 + t0, b])
+        rows.extend((b, p0 + i) for i in range(n))
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32)
+    row_req = torch.tensor([b for b, _ in rows], dtype=torch.int32)
+    q = rnd(len(rows), nq, d, dtype=torch.bfloat16, seed=13)
+    kind, span = mask
+    code, lo_factory = MASKS[kind]
+    scale = 1.0 / math.sqrt(d)
+    ref = attention_ref(q.cpu(), ks, vs, positions, row_req, lo_factory(span), scale, nq, nkv)
+    out = torch.zeros(len(rows), nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill(q, kv, table, torch.tensor(tiles, dtype=torch.int32, device=DEV), out, nq=nq, nkv=nkv, d=d,
+                          page_size=ps, mask_kind=code, mask_span=max(span, 1), scale=scale)
+    assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2)
+    # the generic kernel agrees too (it is what the float32 path and odd head sizes use)
+    gen = ops.paged_attention_generic(q, kv, table, row_req.to(DEV), positions.to(DEV), nq=nq, nkv=nkv, d=d,
+                                      page_size=ps, mask_kind=code, mask_span=max(span, 1), scale=scale)
+    assert torch.allclose(out.float(), gen.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_fast_attention_finds_one_far_key_and_respects_edges(ops):
+    nq, nkv, d, ps, n = 4, 2, 32, 16, 700
+    scale = 1 / math.sqrt(d)
+    for far in (0, 1, 15, 16, 63, 64, 255, 256, 257, 511, 512, 698, 699):
+        kv, table, ks, vs = paged_setup([n], nkv, d, ps, torch.bfloat16, seed=far)
+        q = rnd(64, nq, d, dtype=torch.bfloat16, seed=far + 1)          # rows at positions 636 .. 699
+        page, off = int(table[0, far // ps]), far % ps
+        for h in range(nkv):
+            kv[page, 0, h, off] = (q[63, h * 2].float() * 8.0).to(torch.bfloat16)
+        target = [kv[page, 1, h, off].float() for h in range(nkv)]
+        positions = torch.arange(n - 64, n, dtype=torch.int32, device=DEV)
+        row_req = torch.zeros(64, dtype=torch.int32, device=DEV)
+        out_d = torch.zeros(64, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(q, kv, table, row_req, positions, out_d, rows=torch.tensor([63], dtype=torch.int32, device=DEV),
+                             num_rows=1, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=0, mask_span=1, scale=scale,
+                             max_context=n)
+        out_p = torch.zeros(64, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill(q, kv, table, torch.tensor([[0, 64, n - 64, 0]], dtype=torch.int32, device=DEV), out_p,
+                              nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=0, mask_span=1, scale=scale)
+        for out in (out_d, out_p):
+            got = out[63].view(nq, d).float()
+            for h in range(nkv):
+                assert torch.allclose(got[h * 2], target[h], atol=6e-2), (far, h)
+    # edges: the key just outside must not be seen, the one just inside must
+    for kind, span, pos, outside, inside in (("chunk", 24, 50, 47, 48), ("chunk", 64, 64, 63, 64), ("window", 9, 60, 51, 52),
+                                             ("chunk", 256, 256, 255, 256), ("window", 256, 600, 344, 345)):
+        code = {"chunk": 1, "window": 2}[kind]
+        for which, key in (("outside", outside), ("inside", inside)):
+            kv, table, ks, vs = paged_setup([n], 1, 16, 8, torch.bfloat16, seed=pos)
+            q = rnd(1, 2, 16, dtype=torch.bfloat16, seed=3)
+            page, off = int(table[0, key // 8]), key % 8
+            kv[page, 0, 0, off] = (q[0, 0].float() * 10.0).to(torch.bfloat16)
+            kv[page, 1, 0, off] = 50.0
+            positions = torch.tensor([pos], dtype=torch.int32, device=DEV)
+            zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+            out_d = torch.zeros(1, 32, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode(q, kv, table, zero, positions, out_d, rows=None, num_rows=1, nq=2, nkv=1, d=16,
+                                 page_size=8, mask_kind=code, mask_span=span, scale=0.25, max_context=pos + 1)
+            out_p = torch.zeros(1, 32, dtype=torch.bfloat16, device=DEV)
+            ops.attention_prefill(q, kv, table, torch.tensor([[0, 1, pos, 0]], dtype=torch.int32, device=DEV), out_p,
+                                  nq=2, nkv=1, d=16, page_size=8, mask_kind=code, mask_span=span, scale=0.25)
+            for out in (out_d.float(), out_p.float()):
+                if which == "outside":
+                    assert float(out[0, :16].abs().max()) < 10.0, (kind, pos, key)
+                else:
+                    assert float(out[0, :16].min()) > 40.0, (kind, pos, key)
