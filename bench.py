@@ -225,7 +225,7 @@ def main() -> int:
     # ---- decode -----------------------------------------------------------------------------
     def decode_run(B, timed_steps, through_engine):
         """B requests at `context`; returns (ms per step, distinct experts per layer, bytes moved per step)."""
-        total = warmup + timed_steps
+        total = warmup + timed_steps + 1
         ids = [inject_prefilled(engine, tokens(ns.context - total), greedy) for _ in range(B)]
         reqs = [engine._requests[i] for i in ids]
         h2d = d2h = 0
@@ -246,12 +246,14 @@ def main() -> int:
             d2h = 4 * B
         else:
             last = [r.tokens[-1] for r in reqs]
-            engine.runner.trace_router = True
-            for _ in range(warmup):
-                logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
-                last = engine.sampler.sample(logits, [r.sampler for r in reqs])
+            engine.runner.trace_router = True        # one traced step: which experts this batch uses
+            logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
+            last = engine.sampler.sample(logits, [r.sampler for r in reqs])
             distinct = [len(set(c.tolist())) for c in engine.runner.last_router_choices]
             engine.runner.trace_router = False
+            for _ in range(warmup):                   # includes the capture of this shape's CUDA graph
+                logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
+                last = engine.sampler.sample(logits, [r.sampler for r in reqs])
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             launches0 = library.launch_count

@@ -19,7 +19,7 @@ constexpr int ROUTER_THREADS = 256;
 __global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int H, int E,
                                    int* __restrict__ expert_id, float* __restrict__ expert_weight,
                                    float* __restrict__ logits_out) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* h_s = smem;          // [H]
     float* r_s = smem + H;      // [E]
     const int t = blockIdx.x;
@@ -27,10 +27,26 @@ __global__ void router_top1_kernel(const float* __restrict__ h, const float* __r
     for (int i = threadIdx.x; i < H; i += ROUTER_THREADS) h_s[i] = hr[i];
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // A lane sums its own quarter-strided elements in order and the warp adds the 32 partial sums
+    // in a fixed tree: the order depends on H alone.  16-byte loads where the rows allow it.
+    const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
     for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
         const float* w = wr + (size_t)e * H;
         float acc = 0.0f;
-        for (int i = lane; i < H; i += 32) acc = fmaf(h_s[i], w[i], acc);
+        if (vec) {
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* h4 = reinterpret_cast<const float4*>(h_s);
+#pragma unroll 4
+            for (int i = lane; i < H / 4; i += 32) {
+                const float4 a = h4[i], b = __ldg(w4 + i);
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) acc = fmaf(h_s[i], w[i], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) r_s[e] = acc;
     }

@@ -54,11 +54,22 @@ __device__ int row_argmax(const float* __restrict__ row, int V, ArgBest* scratch
     ArgBest mine;
     mine.v = -INFINITY;
     mine.i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > mine.v) {  // ascending i per thread: strict > keeps the lowest index
-            mine.v = v;
-            mine.i = i;
+    if ((V % 4 == 0) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < V / 4; i += blockDim.x) {   // ascending indices per thread
+            const float4 v = row4[i];
+            if (v.x > mine.v) { mine.v = v.x; mine.i = 4 * i; }
+            if (v.y > mine.v) { mine.v = v.y; mine.i = 4 * i + 1; }
+            if (v.z > mine.v) { mine.v = v.z; mine.i = 4 * i + 2; }
+            if (v.w > mine.v) { mine.v = v.w; mine.i = 4 * i + 3; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (v > mine.v) {  // ascending i per thread: strict > keeps the lowest index
+                mine.v = v;
+                mine.i = i;
+            }
         }
     }
     ArgBest r = block_argmax(mine, scratch);

@@ -39,6 +39,7 @@ class EngineOptions:
     memory_fraction: float = 0.85       # share of the free device memory the cache may take when sized from it
     max_batch: int = 64                 # live requests (and state slots)
     max_tokens_per_step: int = 2048     # token budget of one step
+    cuda_graphs: bool = True            # capture decode-only steps as CUDA graphs (when the model's parts allow)
 
 
 @dataclass
@@ -68,6 +69,7 @@ class Engine:
                                   num_pages=num_pages, max_requests=o.max_batch, dtype=self.model.act_dtype,
                                   device=self.device)
         self.runner = StepRunner(self.model, self.cache)
+        self.runner.use_graphs = self.runner.use_graphs and o.cuda_graphs
         self.scheduler = Scheduler(self.cache, max_batch=o.max_batch, max_tokens_per_step=o.max_tokens_per_step)
         self.sampler = Sampler(self.device)
         self._requests: Dict[Hashable, Request] = {}

@@ -16,13 +16,13 @@ committed after it.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
-from ..kernels import ops
+from ..kernels import library, ops
 from ..parts.base import StepContext
 
 
@@ -57,6 +57,18 @@ class StepRunner:
         # (a 4-byte copy; the step's result is read by the host right after anyway)
         self.check_kernel_status = True
         self.last_router_choices: List[torch.Tensor] = []
+        # Decode-only steps are launch-bound at small batches, so they are captured once per shape
+        # (requests, wanted rows, block-table width) as a CUDA graph and replayed; the step's metadata
+        # lives in one static device buffer that is refreshed before each replay.  The reference does
+        # the same for its per-token decode (src/SharpInference.Engine/CudaForwardPass.cs:1668-1675).
+        # Only models whose parts read the step through device tensors alone can be captured.
+        self.use_graphs = all(getattr(b.mixer, "graph_safe", False) and getattr(getattr(b, "ffn", None), "graph_safe", False)
+                              for b in model.blocks) if hasattr(model, "blocks") else False
+        self.max_graphs = 32
+        self._graphs: Dict[tuple, dict] = {}
+        self._graph_seen: set = set()
+        self._graph_pool = None
+        self.graph_replays = 0
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         """Refuse, before any page is taken, a step that cannot run as given."""
@@ -80,8 +92,18 @@ class StepRunner:
                 if not (0 <= t < V):
                     raise StepError(f"token id {t} is outside the vocabulary [0, {V})")
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Lay out the step's metadata: one pinned host buffer, one copy to the device."""
+    def _layout(self, T: int, B: int, R: int, width: int, n_tiles: int, n_dec: int) -> np.ndarray:
+        """Offsets (in int32 words, each segment starting on 16 bytes) of the staging buffer's segments:
+        token ids, positions, row -> request, request starts, row offsets, state slots, wanted rows, one
+        block table per cache group, attention tiles, single rows."""
+        sizes = [T, T, T, B, B + 1, B, R] + [B * width] * len(self.cache.groups) + [4 * n_tiles, n_dec]
+        return np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
+
+    def build_context(self, entries: Sequence[StepEntry], width: Optional[int] = None,
+                      buffers: Optional[tuple] = None) -> StepContext:
+        """Lay out the step's metadata: one pinned host buffer, one copy to the device.  ``width``
+        pads the block tables to a fixed number of columns; ``buffers`` = (pinned host tensor, device
+        tensor) of exactly the layout's size are reused instead of fresh ones (graph replay)."""
         cache = self.cache
         starts, lengths, slots = [], [], []
         for e in entries:
@@ -115,17 +137,23 @@ class StepRunner:
 
         # Block tables, one per group, padded to a common width with -1.
         ids = [e.request_id for e in entries]
-        width = 1
-        for g in cache.groups:
-            for rid in ids:
-                width = max(width, len(cache.requests[rid].tables[g.index]))
+        needed = self.table_width(ids)
+        if width is None:
+            width = needed
+        elif width < needed:
+            raise StepError(f"block tables need {needed} columns, the buffer has {width}")
         G = len(cache.groups)
         R = len(want_rows)
         # layout of the one int32 staging buffer
         n_tiles, n_dec = len(tiles) // 4, len(decode_rows)
-        sizes = [T, T, T, B, B + 1, B, R] + [B * width] * G + [4 * n_tiles, n_dec]
-        offsets = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
-        host = torch.empty(int(offsets[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        offsets = self._layout(T, B, R, width, n_tiles, n_dec)
+        total = int(offsets[-1])
+        if buffers is None:
+            host = torch.empty(total, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        else:
+            host = buffers[0]
+            if host.numel() != total:
+                raise StepError(f"static step buffer holds {host.numel()} words, this step needs {total}")
         hv = host.numpy()
         hv[offsets[0]:offsets[0] + T] = tokens
         hv[offsets[1]:offsets[1] + T] = positions
@@ -143,7 +171,11 @@ class StepRunner:
             hv[o:o + B * width] = table.reshape(-1)
         hv[offsets[7 + G]:offsets[7 + G] + 4 * n_tiles] = tiles
         hv[offsets[8 + G]:offsets[8 + G] + n_dec] = decode_rows
-        dev = host.to(self.device, non_blocking=True)
+        if buffers is None:
+            dev = host.to(self.device, non_blocking=True)
+        else:
+            dev = buffers[1]
+            dev.copy_(host, non_blocking=True)
 
         def view(i: int, n: int) -> torch.Tensor:
             return dev[int(offsets[i]):int(offsets[i]) + n]
@@ -154,7 +186,10 @@ class StepRunner:
             block_tables={g.index: view(7 + gi, B * width).view(B, width) for gi, g in enumerate(cache.groups)},
             want_rows=view(6, R) if R else None, slots=self._slots,
             host_starts=starts, host_lengths=lengths, host_state_slots=slots,
-            max_rows_per_request=max(lengths), max_context=max(s + n for s, n in zip(starts, lengths)),
+            max_rows_per_request=max(lengths),
+            # with a fixed table width the bound must hold for every later step that reuses the layout
+            max_context=(max(s + n for s, n in zip(starts, lengths)) if buffers is None
+                         else width * cache.page_size),
             decode_only=all(n == 1 for n in lengths),
             attn_tiles=view(7 + G, 4 * n_tiles).view(n_tiles, 4) if n_tiles else None, num_attn_tiles=n_tiles,
             decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
@@ -167,15 +202,70 @@ class StepRunner:
         :class:`OutOfPages` before anything ran if the pages for the step cannot all be had."""
         self.validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
-        ctx = self.build_context(entries)
-        if self.trace_router:
-            ctx.extras["router_choices"] = []
-        logits = self.model.forward(ctx)
+        logits, done, num_tokens = None, False, sum(len(e.tokens) for e in entries)
+        if self.use_graphs and not self.trace_router and num_tokens == len(entries):
+            done, logits = self._run_decode_graph(entries)
+        if not done:
+            ctx = self.build_context(entries)
+            if self.trace_router:
+                ctx.extras["router_choices"] = []
+            logits = self.model.forward(ctx)
+            self.last_router_choices = ctx.extras.get("router_choices", [])
         if self.check_kernel_status:
             ops.check_status(self.device)
-        self.last_router_choices = ctx.extras.get("router_choices", [])
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
-        self.rows_run += ctx.num_tokens
+        self.rows_run += num_tokens
         return logits
+
+    # -- CUDA graphs for decode-only steps -------------------------------------------------------
+    TABLE_WIDTH_STEP = 16      # block-table columns are rounded up to a multiple of this in a graph
+
+    def table_width(self, request_ids) -> int:
+        return max([1] + [len(self.cache.requests[r].tables[g.index]) for r in request_ids for g in self.cache.groups])
+
+    def _run_decode_graph(self, entries: Sequence[StepEntry]):
+        """Replay (capturing first, if this shape was seen once before) the graph of a decode-only
+        step.  Returns (handled, logits); not handled means "run it eagerly this time"."""
+        step = self.TABLE_WIDTH_STEP
+        width = (self.table_width([e.request_id for e in entries]) + step - 1) // step * step
+        key = (len(entries), sum(len(e.want) for e in entries), width)
+        rec = self._graphs.get(key)
+        if rec is None:
+            if key not in self._graph_seen:          # first sight: an eager run warms every kernel up
+                self._graph_seen.add(key)
+                return False, None
+            rec = self._capture(entries, width)
+            while len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = rec
+        else:
+            rec["copied"].synchronize()              # the previous copy out of the pinned buffer is over
+            self.build_context(entries, width=width, buffers=(rec["host"], rec["dev"]))
+            rec["copied"].record()
+        rec["graph"].replay()
+        library.launch_count += rec["launches"]     # the replay launches what the capture recorded
+        self.graph_replays += 1
+        self.last_router_choices = []
+        return True, rec["logits"]
+
+    def _capture(self, entries: Sequence[StepEntry], width: int) -> dict:
+        B, R = len(entries), sum(len(e.want) for e in entries)
+        size = int(self._layout(B, B, R, width, 0, B)[-1])
+        host = torch.empty(size, dtype=torch.int32, pin_memory=True)
+        dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        ctx = self.build_context(entries, width=width, buffers=(host, dev))
+        copied = torch.cuda.Event()
+        copied.record()
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = library.launch_count
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(ctx)
+        launches = library.launch_count - before
+        library.launch_count = before                # recorded, not run: replays do the counting
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        return {"graph": graph, "host": host, "dev": dev, "ctx": ctx, "logits": logits, "copied": copied,
+                "launches": launches}

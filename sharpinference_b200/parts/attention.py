@@ -49,6 +49,8 @@ class PagedAttention(Mixer):
         self.temperature = temperature          # (attn_scale, floor_scale) or None
         self.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
         self.act_dtype = act_dtype
+        # an encoding that edits q and k itself may look at the step's host-side lists: no graph then
+        self.graph_safe = position is None or position.rotary() is not None
 
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         T = ctx.num_tokens

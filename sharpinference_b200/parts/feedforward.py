@@ -23,6 +23,7 @@ from .linear import GroupedLinear, Linear
 
 @register_part("feed_forward", "dense_swiglu")
 class DenseSwiGLU(FeedForward):
+    graph_safe = True        # reads the step through device tensors only: may be captured in a CUDA graph
     def __init__(self, *, gate_up: Linear, down: Linear, act_dtype: torch.dtype = torch.bfloat16):
         if gate_up.out_features != 2 * down.in_features:
             raise ValueError(f"fused gate|up weight has {gate_up.out_features} rows, expected 2 * {down.in_features}")
@@ -36,6 +37,7 @@ class DenseSwiGLU(FeedForward):
 @register_part("feed_forward", "moe_sigmoid_top1")
 class MoESigmoidTop1(FeedForward):
     wants_fp32_input = True
+    graph_safe = True
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
                  shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):

@@ -208,3 +208,39 @@ def test_temperature_sampling_is_reproducible_and_follows_the_distribution(model
             dist = plain.sample_distribution(plain.forward(cfg, w, seq)[-1], 0.8)
             assert plain.draw(dist, uniform01(1234, n)) == tok
             seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_replayed_as_cuda_graphs_give_the_same_logits(model_dirs, dtype):
+    """Decode-only steps are captured per shape and replayed; the numbers must be those of eager steps,
+    also when the batch changes shape and when a request's block table grows past the captured width."""
+    from sharpinference_b200 import Engine, EngineOptions
+    name = "B"
+    cfg, w = plain.load_folder(model_dirs[name])
+    reqs = {f"g{i}": traces.random_tokens(cfg["vocab_size"], n, seed=50 + i) for i, n in enumerate([300, 280, 40])}
+    # whole prompts first, then token by token: three live, then two, then one
+    steps, s = [], 0
+    heads = {"g0": 20, "g1": 10, "g2": 5}
+    steps.append({"step": s, "entries": [{"id": r, "tokens": t[:heads[r]], "want": []} for r, t in reqs.items()], "end": []})
+    at = dict(heads)
+    while at:
+        s += 1
+        entries = [{"id": r, "tokens": [reqs[r][p]], "want": [0]} for r, p in at.items()]
+        at = {r: p + 1 for r, p in at.items()}
+        ended = [r for r, p in at.items() if p == len(reqs[r])]
+        steps.append({"step": s, "entries": entries, "end": ended})
+        for r in ended:
+            del at[r]
+    outs = {}
+    for graphs in (False, True):
+        eng = Engine(model_dirs[name], dtype=dtype, device="cuda:0",
+                     options=EngineOptions(page_size=16, max_cache_tokens=traces.max_tokens(steps), max_batch=4,
+                                           cuda_graphs=graphs))
+        outs[graphs] = traces.replay(eng, steps)
+        assert (eng.runner.graph_replays > 200) == graphs
+        assert not graphs or len(eng.runner._graphs) >= 4       # three batch shapes, and a wider table for the long ones
+    for key, row in outs[False].items():
+        assert torch.equal(row, outs[True][key]), key
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    err, where = traces.worst_error(outs[True], ref)
+    assert err < (TOL["float32"] if dtype == "float32" else 0.1), (err, where)
