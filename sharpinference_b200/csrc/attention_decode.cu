@@ -19,9 +19,10 @@
 using namespace mma16;
 
 constexpr int DEC_SPLIT = 256;   // keys per CTA
-constexpr int DEC_CHUNK = 32;    // keys per warp pass
+constexpr int DEC_CHUNK = 16;    // keys per warp pass; a warp owns 64 keys of the split and double-buffers its passes
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
+constexpr int DEC_WARP_KEYS = DEC_SPLIT / DEC_WARPS;
 
 struct DecodeArgs {
     const bf16* q;            // [T, nq, D]
@@ -33,17 +34,41 @@ struct DecodeArgs {
     float* part_o;            // [R, nq, max_splits, D]
     float* part_ml;           // [R, nq, max_splits, 2]   (max in log2 units, sum)
     bf16* out;                // [T, nq * D]
-    int nq, nkv, max_blocks, page_size, mask_kind, mask_span, max_splits;
+    int nq, nkv, max_blocks, page_size, page_shift, mask_kind, mask_span, max_splits;
     float scale_log2;         // softmax scale * log2(e)
 };
+
+template <int D>
+__device__ __forceinline__ void decode_load_chunk(const DecodeArgs& a, const int* table, int kvh, size_t plane,
+                                                  int chunk0, int k_begin, int k_end, bf16* k_s, bf16* v_s, int lane) {
+    constexpr int LD = D + 8, VEC = D / 8;
+#pragma unroll
+    for (int idx = lane; idx < DEC_CHUNK * VEC; idx += 32) {
+        const int row = idx / VEC, col = idx % VEC;
+        const int key = chunk0 + row;
+        bool valid = key >= k_begin && key <= k_end;
+        int page = -1, off = 0;
+        if (valid) {
+            const int blk = a.page_shift >= 0 ? (key >> a.page_shift) : (key / a.page_size);
+            off = key - blk * a.page_size;
+            page = table[blk];
+        }
+        valid = valid && page >= 0;
+        const bf16* src = a.kv;
+        if (valid) src = a.kv + (size_t)page * 2 * plane + ((size_t)kvh * a.page_size + off) * D + col * 8;
+        cp_async_16(k_s + row * LD + col * 8, src, valid ? 16 : 0);
+        cp_async_16(v_s + row * LD + col * 8, valid ? src + plane : src, valid ? 16 : 0);
+    }
+}
 
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(DecodeArgs a) {
     constexpr int LD = D + 8;       // padded row, in elements: 8 ldmatrix rows fall into different banks
     constexpr int VEC = D / 8;      // 16-byte pieces per row
+    constexpr int BUF = 2 * DEC_CHUNK * LD;     // one buffer: K rows then V rows, in elements
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_bytes);       // [16][LD]
-    bf16* kv_s = q_s + 16 * LD;                              // [warps][2][DEC_CHUNK][LD]
+    bf16* kv_s = q_s + 16 * LD;                              // [warps][2 buffers][K|V][DEC_CHUNK][LD]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nq / a.nkv;
@@ -60,6 +85,20 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
     const int k_end = min(pos, split * DEC_SPLIT + DEC_SPLIT - 1);
     if (k_begin > k_end) return;
 
+    bf16* w_s = kv_s + (size_t)warp * 2 * BUF;
+    const int* table = a.block_table + (size_t)a.row_req[r] * a.max_blocks;
+    const size_t plane = (size_t)a.nkv * a.page_size * D;
+
+    // this warp's keys and its first pass are requested before anything else
+    const int wbase = split * DEC_SPLIT + warp * DEC_WARP_KEYS;
+    const int wk0 = max(k_begin, wbase), wk1 = min(k_end, wbase + DEC_WARP_KEYS - 1);
+    const int c_first = (wk0 - wbase) / DEC_CHUNK, c_last = (wk1 - wbase) / DEC_CHUNK;    // meaningful if wk0 <= wk1
+    const bool has_keys = wk0 <= wk1;
+    if (has_keys) {
+        decode_load_chunk<D>(a, table, kvh, plane, wbase + c_first * DEC_CHUNK, k_begin, k_end, w_s, w_s + DEC_CHUNK * LD, lane);
+        cp_async_commit();
+    }
+
     // queries of this group: rows >= heads_here are zero
     for (int idx = threadIdx.x; idx < 16 * VEC; idx += DEC_THREADS) {
         const int g = idx / VEC, c = idx % VEC;
@@ -72,11 +111,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * LD + ks * 16 + (lane / 16) * 8);
 
-    bf16* k_s = kv_s + (size_t)warp * 2 * DEC_CHUNK * LD;
-    bf16* v_s = k_s + DEC_CHUNK * LD;
-    const int* table = a.block_table + (size_t)a.row_req[r] * a.max_blocks;
-    const size_t plane = (size_t)a.nkv * a.page_size * D;
-
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i)
@@ -84,105 +118,99 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
         for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
 
-    for (int c = warp; c < DEC_SPLIT / DEC_CHUNK; c += DEC_WARPS) {
-        const int chunk0 = split * DEC_SPLIT + c * DEC_CHUNK;
-        if (chunk0 > k_end || chunk0 + DEC_CHUNK - 1 < k_begin) continue;   // uniform over the warp
-        for (int idx = lane; idx < DEC_CHUNK * VEC; idx += 32) {
-            const int row = idx / VEC, col = idx % VEC;
-            const int key = chunk0 + row;
-            bool valid = key >= k_begin && key <= k_end;
-            const int page = valid ? table[key / a.page_size] : -1;
-            valid = valid && page >= 0;
-            const bf16* src = a.kv;
-            if (valid) src = a.kv + (size_t)page * 2 * plane + ((size_t)kvh * a.page_size + key % a.page_size) * D + col * 8;
-            cp_async_16(k_s + row * LD + col * 8, src, valid ? 16 : 0);
-            cp_async_16(v_s + row * LD + col * 8, valid ? src + plane : src, valid ? 16 : 0);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncwarp();
+    if (has_keys) {
+        for (int c = c_first; c <= c_last; ++c) {
+            const int buf = (c - c_first) & 1;
+            bf16* k_s = w_s + buf * BUF;
+            bf16* v_s = k_s + DEC_CHUNK * LD;
+            if (c < c_last) {       // ask for the next pass while this one is computed
+                bf16* nk = w_s + (buf ^ 1) * BUF;
+                decode_load_chunk<D>(a, table, kvh, plane, wbase + (c + 1) * DEC_CHUNK, k_begin, k_end, nk, nk + DEC_CHUNK * LD, lane);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncwarp();
+            const int chunk0 = wbase + c * DEC_CHUNK;
 
-        // S = Q K^T for 32 keys: 4 tiles of 8 keys
-        float s[4][4];
+            // S = Q K^T for 16 keys: 2 tiles of 8 keys
+            float s[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+                for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
 #pragma unroll
-            for (int k2 = 0; k2 < D / 32; ++k2) {
+                for (int k2 = 0; k2 < D / 32; ++k2) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, k_s + (nt * 8 + (lane % 8)) * LD + k2 * 32 + (lane / 8) * 8);
+                    mma_bf16(s[nt], qa[2 * k2], b[0], b[1]);
+                    mma_bf16(s[nt], qa[2 * k2 + 1], b[2], b[3]);
+                }
+                if (D % 32 != 0) {
+                    uint32_t b[2];
+                    ldmatrix_x2(b, k_s + (nt * 8 + (lane % 8)) * LD + (D - 16) + ((lane / 8) % 2) * 8);
+                    mma_bf16(s[nt], qa[D / 16 - 1], b[0], b[1]);
+                }
+            }
+            // mask, running max and sum (rows lane/4 and lane/4 + 8 of the group)
+            float m_c[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = chunk0 + nt * 8 + (lane % 4) * 2 + (e & 1);
+                    const bool valid = key >= k_begin && key <= k_end;
+                    s[nt][e] = valid ? s[nt][e] * a.scale_log2 : -INFINITY;
+                    m_c[e >> 1] = fmaxf(m_c[e >> 1], s[nt][e]);
+                }
+            float corr[2], l_c[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 1));
+                m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 2));
+                const float m_new = fmaxf(m_run[h], m_c[h]);
+                corr[h] = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - m_new);
+                m_run[h] = m_new;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_run[e >> 1]);
+                    s[nt][e] = p;
+                    l_c[e >> 1] += p;
+                }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 1);
+                l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 2);
+                l_run[h] = l_run[h] * corr[h] + l_c[h];
+            }
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+            // O += P V: P (16 x 16) straight from the S accumulators
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]);
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int d2 = 0; d2 < D / 16; ++d2) {
                 uint32_t b[4];
-                ldmatrix_x4(b, k_s + (nt * 8 + (lane % 8)) * LD + k2 * 32 + (lane / 8) * 8);
-                mma_bf16(s[nt], qa[2 * k2], b[0], b[1]);
-                mma_bf16(s[nt], qa[2 * k2 + 1], b[2], b[3]);
+                ldmatrix_x4_trans(b, v_s + ((lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
+                mma_bf16(o[2 * d2], pa, b[0], b[1]);
+                mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
             }
-            if (D % 32 != 0) {
-                uint32_t b[2];
-                ldmatrix_x2(b, k_s + (nt * 8 + (lane % 8)) * LD + (D - 16) + ((lane / 8) % 2) * 8);
-                mma_bf16(s[nt], qa[D / 16 - 1], b[0], b[1]);
-            }
+            __syncwarp();
         }
-        // mask, running max and sum (rows lane/4 and lane/4 + 8 of the group)
-        float m_c[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = chunk0 + nt * 8 + (lane % 4) * 2 + (e & 1);
-                const bool valid = key >= k_begin && key <= k_end;
-                s[nt][e] = valid ? s[nt][e] * a.scale_log2 : -INFINITY;
-                m_c[e >> 1] = fmaxf(m_c[e >> 1], s[nt][e]);
-            }
-        float corr[2], l_c[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 1));
-            m_c[h] = fmaxf(m_c[h], __shfl_xor_sync(0xffffffffu, m_c[h], 2));
-            const float m_new = fmaxf(m_run[h], m_c[h]);
-            corr[h] = (m_run[h] == -INFINITY) ? 0.0f : exp2f(m_run[h] - m_new);
-            m_run[h] = m_new;
-        }
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_run[e >> 1]);
-                s[nt][e] = p;
-                l_c[e >> 1] += p;
-            }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 1);
-            l_c[h] += __shfl_xor_sync(0xffffffffu, l_c[h], 2);
-            l_run[h] = l_run[h] * corr[h] + l_c[h];
-        }
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
-        }
-        // O += P V: P (16 x 32) straight from the S accumulators
-        uint32_t pa[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            pa[j][0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
-            pa[j][1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
-            pa[j][2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
-            pa[j][3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
-        }
-#pragma unroll
-        for (int d2 = 0; d2 < D / 16; ++d2)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, v_s + (j * 16 + (lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
-                mma_bf16(o[2 * d2], pa[j], b[0], b[1]);
-                mma_bf16(o[2 * d2 + 1], pa[j], b[2], b[3]);
-            }
-        __syncwarp();
     }
 
     // each warp leaves its partial in its own staging area, then the block merges the four
-    float* o_w = reinterpret_cast<float*>(k_s);                 // [16][D]
+    float* o_w = reinterpret_cast<float*>(w_s);                 // [16][D]
     float* ml_w = o_w + 16 * D;                                  // [16][2]
 #pragma unroll
     for (int i = 0; i < D / 8; ++i)
@@ -196,7 +224,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
         ml_w[(lane / 4 + 8) * 2 + 1] = l_run[1];
     }
     __syncthreads();
-    const size_t warp_stride = (size_t)2 * DEC_CHUNK * LD * sizeof(bf16) / sizeof(float);
+    constexpr size_t warp_stride = (size_t)2 * BUF * sizeof(bf16) / sizeof(float);
     const float* base_o = reinterpret_cast<const float*>(kv_s);
     for (int idx = threadIdx.x; idx < heads_here * D; idx += DEC_THREADS) {
         const int g = idx / D, dd = idx % D;
@@ -220,31 +248,46 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
     }
 }
 
+// One block per (row, query head): the row's partials, weighted by exp2(max_s - max) and normalised.
+constexpr int MERGE_THREADS = 128;
+
 template <int D>
-__global__ void attn_decode_merge_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(DecodeArgs a) {
+    __shared__ float w_s[MERGE_THREADS];
+    __shared__ float scratch[32];
     const int ri = blockIdx.x, head = blockIdx.y;
     const int r = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[r];
     const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
     const int n_s = pos / DEC_SPLIT - lo / DEC_SPLIT + 1;
     const size_t slot0 = ((size_t)ri * a.nq + head) * a.max_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_s; ++s) M = fmaxf(M, a.part_ml[(slot0 + s) * 2]);
-    float L = 0.0f;
-    for (int s = 0; s < n_s; ++s) L += exp2f(a.part_ml[(slot0 + s) * 2] - M) * a.part_ml[(slot0 + s) * 2 + 1];
-    const float inv = 1.0f / L;
-    for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
-        float acc = 0.0f;
-        for (int s = 0; s < n_s; ++s) acc += exp2f(a.part_ml[(slot0 + s) * 2] - M) * a.part_o[(slot0 + s) * D + dd];
-        a.out[((size_t)r * a.nq + head) * D + dd] = __float2bfloat16_rn(acc * inv);
+    float m = -INFINITY;
+    for (int s = threadIdx.x; s < n_s; s += MERGE_THREADS) m = fmaxf(m, a.part_ml[(slot0 + s) * 2]);
+    const float M = block_max(m, scratch);
+    float acc = 0.0f, l = 0.0f;
+    for (int s0 = 0; s0 < n_s; s0 += MERGE_THREADS) {
+        const int s = s0 + threadIdx.x;
+        float w = 0.0f;
+        if (s < n_s) {
+            w = exp2f(a.part_ml[(slot0 + s) * 2] - M);
+            l += w * a.part_ml[(slot0 + s) * 2 + 1];
+        }
+        __syncthreads();
+        w_s[threadIdx.x] = w;
+        __syncthreads();
+        const int n_here = min(MERGE_THREADS, n_s - s0);
+        if (threadIdx.x < D)
+            for (int j = 0; j < n_here; ++j) acc += w_s[j] * a.part_o[(slot0 + s0 + j) * D + threadIdx.x];
     }
+    const float L = block_sum(l, scratch);
+    if (threadIdx.x < D) a.out[((size_t)r * a.nq + head) * D + threadIdx.x] = __float2bfloat16_rn(acc / L);
 }
 
 template <int D>
 static int launch_decode(const DecodeArgs& a, int R, int splits, cudaStream_t stream) {
     constexpr int LD = D + 8;
-    constexpr int SMEM = (16 * LD + DEC_WARPS * 2 * DEC_CHUNK * LD) * 2;
-    static_assert(2 * DEC_CHUNK * LD * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
+    constexpr int SMEM = (16 * LD + DEC_WARPS * 2 * 2 * DEC_CHUNK * LD) * 2;
+    static_assert(2 * 2 * DEC_CHUNK * LD * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attn_decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
@@ -256,7 +299,7 @@ static int launch_decode(const DecodeArgs& a, int R, int splits, cudaStream_t st
     dim3 grid(splits, a.nkv * ((G + 15) / 16), R);
     attn_decode_split_kernel<D><<<grid, DEC_THREADS, SMEM, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
-    attn_decode_merge_kernel<D><<<dim3(R, a.nq), D >= 64 ? 64 : 32, 0, stream>>>(a);
+    attn_decode_merge_kernel<D><<<dim3(R, a.nq), MERGE_THREADS, 0, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -278,6 +321,9 @@ SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int*
     a.positions = positions; a.rows = rows; a.part_o = part_o; a.part_ml = part_ml; a.out = (bf16*)out;
     a.nq = nq; a.nkv = nkv; a.max_blocks = max_blocks; a.page_size = page_size; a.mask_kind = mask_kind;
     a.mask_span = mask_span; a.max_splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
+    a.page_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+        if ((1 << sft) == page_size) a.page_shift = sft;
     switch (d) {
         case 16: return launch_decode<16>(a, R, splits, stream);
         case 32: return launch_decode<32>(a, R, splits, stream);
