@@ -111,10 +111,38 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, const float* __
     out[(size_t)m * I + i] = from_float<TO>(act * u);
 }
 
+// Four elements per thread with 16-byte loads, for widths that are multiples of 4.
+template <typename TO>
+__global__ void swiglu_vec4_kernel(const float* __restrict__ gate_up, const float* __restrict__ row_scale,
+                                   const int* __restrict__ scale_rows, TO* __restrict__ out, int I) {
+    const int m = blockIdx.x;
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (i >= I) return;
+    const float s = row_scale ? row_scale[scale_rows ? scale_rows[m] : m] : 1.0f;
+    const float4 g4 = *reinterpret_cast<const float4*>(gate_up + (size_t)m * 2 * I + i);
+    const float4 u4 = *reinterpret_cast<const float4*>(gate_up + (size_t)m * 2 * I + I + i);
+    const float g[4] = {g4.x * s, g4.y * s, g4.z * s, g4.w * s};
+    const float u[4] = {u4.x * s, u4.y * s, u4.z * s, u4.w * s};
+    TO* dst = out + (size_t)m * I + i;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = from_float<TO>(g[j] / (1.0f + expf(-g[j])) * u[j]);
+}
+
 SHARPI_API int sharpi_swiglu(const float* gate_up, const float* row_scale, const int* scale_rows, void* out,
                              int out_dtype, int M, int I, cudaStream_t stream) {
     if (M <= 0) return SHARPI_OK;
     if (I <= 0 || (I + 255) / 256 > 65535) return SHARPI_BAD_ARGUMENT;
+    if (I % 4 == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0) {
+        dim3 grid4(M, (I / 4 + 255) / 256);
+        if (out_dtype == SHARPI_F32)
+            swiglu_vec4_kernel<float><<<grid4, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (float*)out, I);
+        else if (out_dtype == SHARPI_BF16)
+            swiglu_vec4_kernel<bf16><<<grid4, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (bf16*)out, I);
+        else
+            return SHARPI_BAD_ARGUMENT;
+        SHARPI_CHECK_LAUNCH();
+        return SHARPI_OK;
+    }
     dim3 grid(M, (I + 255) / 256);
     if (out_dtype == SHARPI_F32)
         swiglu_kernel<float><<<grid, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (float*)out, I);

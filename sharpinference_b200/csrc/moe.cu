@@ -16,72 +16,101 @@ enum RouterGate : int {
 
 constexpr int ROUTER_THREADS = 256;
 
-__global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int H, int E,
+// One block serves TPB consecutive tokens: a warp reads a router row once and forms the dot product
+// with each of the block's tokens.  Every token's sum is the same chain of operations whatever TPB
+// is (a lane adds its own stride-32 elements in order, the warp adds the 32 lane sums in a fixed
+// tree), so the logits do not depend on how many tokens share a block.
+template <int TPB>
+__global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
                                    int* __restrict__ expert_id, float* __restrict__ expert_weight,
                                    float* __restrict__ logits_out) {
     extern __shared__ __align__(16) float smem[];
-    float* h_s = smem;          // [H]
-    float* r_s = smem + H;      // [E]
-    const int t = blockIdx.x;
-    const float* hr = h + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += ROUTER_THREADS) h_s[i] = hr[i];
+    float* h_s = smem;                // [TPB][H]
+    float* r_s = smem + TPB * H;      // [TPB][E]
+    const int t0 = blockIdx.x * TPB;
+    const int n_tok = min(TPB, T - t0);
+    for (int i = threadIdx.x; i < TPB * H; i += ROUTER_THREADS) {
+        const int tt = i / H;
+        h_s[i] = (tt < n_tok) ? h[(size_t)t0 * H + i] : 0.0f;
+    }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // A lane sums its own quarter-strided elements in order and the warp adds the 32 partial sums
-    // in a fixed tree: the order depends on H alone.  16-byte loads where the rows allow it.
     const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
     for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
         const float* w = wr + (size_t)e * H;
-        float acc = 0.0f;
+        float acc[TPB];
+#pragma unroll
+        for (int tt = 0; tt < TPB; ++tt) acc[tt] = 0.0f;
         if (vec) {
             const float4* w4 = reinterpret_cast<const float4*>(w);
-            const float4* h4 = reinterpret_cast<const float4*>(h_s);
-#pragma unroll 4
+#pragma unroll 2
             for (int i = lane; i < H / 4; i += 32) {
-                const float4 a = h4[i], b = __ldg(w4 + i);
-                acc = fmaf(a.x, b.x, acc);
-                acc = fmaf(a.y, b.y, acc);
-                acc = fmaf(a.z, b.z, acc);
-                acc = fmaf(a.w, b.w, acc);
+                const float4 b = __ldg(w4 + i);
+#pragma unroll
+                for (int tt = 0; tt < TPB; ++tt) {
+                    const float4 a = reinterpret_cast<const float4*>(h_s + tt * H)[i];
+                    acc[tt] = fmaf(a.x, b.x, acc[tt]);
+                    acc[tt] = fmaf(a.y, b.y, acc[tt]);
+                    acc[tt] = fmaf(a.z, b.z, acc[tt]);
+                    acc[tt] = fmaf(a.w, b.w, acc[tt]);
+                }
             }
         } else {
-            for (int i = lane; i < H; i += 32) acc = fmaf(h_s[i], w[i], acc);
+            for (int i = lane; i < H; i += 32) {
+                const float b = w[i];
+#pragma unroll
+                for (int tt = 0; tt < TPB; ++tt) acc[tt] = fmaf(h_s[tt * H + i], b, acc[tt]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) r_s[e] = acc;
+#pragma unroll
+        for (int tt = 0; tt < TPB; ++tt) {
+            const float total = warp_sum(acc[tt]);
+            if (lane == 0) r_s[tt * E + e] = total;
+        }
     }
     __syncthreads();
     if (logits_out)
-        for (int e = threadIdx.x; e < E; e += ROUTER_THREADS) logits_out[(size_t)t * E + e] = r_s[e];
-    if (threadIdx.x == 0) {
+        for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_THREADS) logits_out[(size_t)t0 * E + i] = r_s[i];
+    if (threadIdx.x < n_tok) {
+        const float* r = r_s + threadIdx.x * E;
         int best = 0;
-        float best_p = 1.0f / (1.0f + expf(-r_s[0]));
+        float best_p = 1.0f / (1.0f + expf(-r[0]));
         for (int e = 1; e < E; ++e) {
-            const float p = 1.0f / (1.0f + expf(-r_s[e]));
+            const float p = 1.0f / (1.0f + expf(-r[e]));
             if (p > best_p) {
                 best_p = p;
                 best = e;
             }
         }
-        expert_id[t] = best;
-        expert_weight[t] = best_p;
+        expert_id[t0 + threadIdx.x] = best;
+        expert_weight[t0 + threadIdx.x] = best_p;
     }
+}
+
+template <int TPB>
+static int launch_router(const float* h, const float* wr, int T, int H, int E, int* expert_id, float* expert_weight,
+                         float* logits_out, cudaStream_t stream) {
+    const size_t smem = (size_t)TPB * (H + E) * sizeof(float);
+    if (smem > 200 * 1024) return SHARPI_BAD_ARGUMENT;
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(router_top1_kernel<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem);
+        if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
+    }
+    router_top1_kernel<TPB><<<(T + TPB - 1) / TPB, ROUTER_THREADS, smem, stream>>>(h, wr, T, H, E, expert_id,
+                                                                                   expert_weight, logits_out);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
 }
 
 SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H, int E, int gate, int* expert_id,
                                   float* expert_weight, float* logits_out, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || E <= 0 || gate != ROUTER_GATE_SIGMOID) return SHARPI_BAD_ARGUMENT;
-    const size_t smem = (size_t)(H + E) * sizeof(float);
-    if (smem > 200 * 1024) return SHARPI_BAD_ARGUMENT;
-    if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(router_top1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)smem);
-        if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
-    }
-    router_top1_kernel<<<T, ROUTER_THREADS, smem, stream>>>(h, wr, H, E, expert_id, expert_weight, logits_out);
-    SHARPI_CHECK_LAUNCH();
-    return SHARPI_OK;
+    // many tokens: four share a block and a read of the router; few tokens: one block each
+    if (T >= 256 && (size_t)4 * (H + E) * sizeof(float) <= 200 * 1024)
+        return launch_router<4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+    return launch_router<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
 }
 
 // ---------------------------------------------------------------------------------------

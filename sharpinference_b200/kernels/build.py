@@ -49,13 +49,24 @@ def find_nvcc() -> str:
         "are compiled at first use and there is no fallback without them")
 
 
-def _headers() -> List[str]:
-    return sorted(os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+def _included(path: str, seen: Optional[set] = None) -> List[str]:
+    """``path`` and every file of ``csrc/`` it includes with quotes, directly or not."""
+    seen = seen if seen is not None else set()
+    if path in seen or not os.path.isfile(path):
+        return []
+    seen.add(path)
+    out = [path]
+    with open(path, "r", encoding="utf-8") as fh:
+        for line in fh:
+            line = line.strip()
+            if line.startswith("#include \""):
+                out.extend(_included(os.path.join(CSRC_DIR, line.split('"')[1]), seen))
+    return out
 
 
 def _fingerprint(name: str, nvcc: str) -> str:
     h = hashlib.sha256()
-    for path in [os.path.join(CSRC_DIR, name + ".cu"), *_headers()]:
+    for path in sorted(_included(os.path.join(CSRC_DIR, name + ".cu"))):
         h.update(os.path.basename(path).encode())
         with open(path, "rb") as fh:
             h.update(fh.read())

@@ -1,0 +1,142 @@
+"""Single-kernel timing at model sizes, for profiling one kernel without the model around it.
+
+    python -m sharpinference_b200.kernels.microbench tc_gemm --mode gate_up --rows 2048 --row-tile 128
+    python -m sharpinference_b200.kernels.microbench tc_gemm --mode down --rows 8
+    python -m sharpinference_b200.kernels.microbench attention_decode --batch 64 --context 8192
+    python -m sharpinference_b200.kernels.microbench attention_prefill --tokens 2048
+
+Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
+the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
+cache at the default sizes.  Profiler captures name this module so that they run committed code only.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    return a.elapsed_time(b) / iters
+
+
+def tc_gemm(ns) -> None:
+    E, I, H, T = ns.experts, ns.inter, ns.hidden, ns.rows
+    g = torch.Generator(device=DEV).manual_seed(0)
+    used = min(E, ns.active) if ns.active else E
+    counts = torch.zeros(E, dtype=torch.int64)
+    counts[:used] = T // used
+    counts[: T - int(counts.sum())] += 1
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(counts, 0)]).to(torch.int32).to(DEV)
+    if ns.mode == "gate_up":
+        w = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02, generator=g)
+        a = torch.empty(T, H, dtype=torch.bfloat16, device=DEV).normal_(0, 1, generator=g)
+        scale = torch.rand(T, device=DEV, generator=g)
+        fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale, row_tile=ns.row_tile)
+        weight_bytes, flops = used * 2 * I * H * 2, 2 * T * 2 * I * H
+    else:
+        w = torch.empty(E, H, I, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02, generator=g)
+        a = torch.empty(T, I, dtype=torch.bfloat16, device=DEV).normal_(0, 1, generator=g)
+        out = torch.zeros(T, H, device=DEV)
+        rows = torch.randperm(T, device=DEV).to(torch.int32)
+        fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_STORE, out=out, out_rows=rows, accumulate=True,
+                                         row_tile=ns.row_tile)
+        weight_bytes, flops = used * H * I * 2, 2 * T * H * I
+    ms = _time(fn, ns.iters)
+    print(f"tc_gemm {ns.mode} rows={T} experts={used}/{E} row_tile={ns.row_tile or ops.tc_row_tile(T)}: {ms * 1e3:.1f} us, "
+          f"weights {weight_bytes / ms / 1e6:.0f} GB/s, {flops / ms / 1e9:.0f} TFLOP/s")
+
+
+def _cache(batch: int, context: int, nkv: int, d: int, ps: int):
+    blocks = (context + ps - 1) // ps
+    pages = batch * blocks
+    kv = torch.empty(pages, 2, nkv, ps, d, dtype=torch.bfloat16, device=DEV).normal_(0, 1)
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(batch, blocks).contiguous()
+    return kv, table
+
+
+def attention_decode(ns) -> None:
+    B, S, nq, nkv, d, ps = ns.batch, ns.context, ns.heads, ns.kv_heads, ns.head_dim, ns.page_size
+    kv, table = _cache(B, S, nkv, d, ps)
+    q = torch.randn(B, nq, d, device=DEV).to(torch.bfloat16)
+    positions = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
+    row_req = torch.arange(B, dtype=torch.int32, device=DEV)
+    out = torch.empty(B, nq * d, dtype=torch.bfloat16, device=DEV)
+    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
+    fn = lambda: ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=B, nq=nq, nkv=nkv, d=d,
+                                      page_size=ps, mask_kind=kind, mask_span=ns.span, scale=1 / math.sqrt(d),
+                                      max_context=S)
+    ms = _time(fn, ns.iters)
+    nbytes = B * S * nkv * d * 2 * 2
+    print(f"attention_decode batch={B} context={S} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
+
+
+def attention_prefill(ns) -> None:
+    T, nq, nkv, d, ps = ns.tokens, ns.heads, ns.kv_heads, ns.head_dim, ns.page_size
+    start = ns.start
+    kv, table = _cache(1, start + T, nkv, d, ps)
+    q = torch.randn(T, nq, d, device=DEV).to(torch.bfloat16)
+    tiles = torch.tensor([[t0, min(64, T - t0), start + t0, 0] for t0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
+    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
+    fn = lambda: ops.attention_prefill(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=kind,
+                                       mask_span=ns.span, scale=1 / math.sqrt(d))
+    ms = _time(fn, ns.iters)
+    pairs = sum(min(start + t + 1, (start + t) % ns.span + 1 if kind == ops.MASK_CHUNK else start + t + 1) for t in range(T))
+    flops = 4 * nq * d * pairs
+    print(f"attention_prefill tokens={T} start={start} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="kernel", required=True)
+    p = sub.add_parser("tc_gemm")
+    p.add_argument("--mode", choices=["gate_up", "down"], default="gate_up")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--experts", type=int, default=16)
+    p.add_argument("--active", type=int, default=0, help="experts that receive rows (0 = all)")
+    p.add_argument("--hidden", type=int, default=5120)
+    p.add_argument("--inter", type=int, default=8192)
+    p.add_argument("--row-tile", type=int, default=None)
+    p.set_defaults(fn=tc_gemm)
+    for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
+        p = sub.add_parser(name)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--context", type=int, default=8192)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--start", type=int, default=0)
+        p.add_argument("--heads", type=int, default=40)
+        p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=128)
+        p.add_argument("--page-size", type=int, default=64)
+        p.add_argument("--mask", choices=["full", "chunk"], default="full")
+        p.add_argument("--span", type=int, default=8192)
+        p.set_defaults(fn=fn)
+    for sp in sub.choices.values():
+        sp.add_argument("--iters", type=int, default=10)
+    ns = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a CUDA device", file=sys.stderr)
+        return 2
+    ns.fn(ns)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -561,3 +561,14 @@ def test_fast_attention_finds_one_far_key_and_respects_edges(ops):
                     assert float(out[0, :16].abs().max()) < 10.0, (kind, pos, key)
                 else:
                     assert float(out[0, :16].min()) > 40.0, (kind, pos, key)
+
+
+def test_router_rows_do_not_depend_on_the_batch(ops):
+    """A token's router logits are the same bits alone, in a small batch and in a large one (where four
+    tokens share a block)."""
+    h, wr = rnd(600, 1000, seed=21), rnd(16, 1000, scale=0.05, seed=22)
+    e_big, w_big, l_big = ops.router_top1(h, wr, want_logits=True)
+    e_small, w_small, l_small = ops.router_top1(h[:7].contiguous(), wr, want_logits=True)
+    e_one, w_one, l_one = ops.router_top1(h[301:302].contiguous(), wr, want_logits=True)
+    assert torch.equal(l_big[:7], l_small) and torch.equal(l_big[301:302], l_one)
+    assert torch.equal(e_big[:7], e_small) and torch.equal(w_big[301:302], w_one)
