@@ -15,6 +15,9 @@
 // statistics are fp32, masks are full / chunk / window as in common.cuh.
 #include "common.cuh"
 #include "mma_sync.cuh"
+#include "sm100.cuh"
+#include "tensor_map.cuh"
+#include <string.h>
 
 using namespace mma16;
 
@@ -36,6 +39,7 @@ struct DecodeArgs {
     bf16* out;                // [T, nq * D]
     int nq, nkv, max_blocks, page_size, page_shift, mask_kind, mask_span, max_splits;
     float scale_log2;         // softmax scale * log2(e)
+    int* status;              // device word for a wait that gave up (TMA path)
 };
 
 template <int D>
@@ -61,14 +65,26 @@ __device__ __forceinline__ void decode_load_chunk(const DecodeArgs& a, const int
     }
 }
 
-template <int D>
-__global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(DecodeArgs a) {
-    constexpr int LD = D + 8;       // padded row, in elements: 8 ldmatrix rows fall into different banks
-    constexpr int VEC = D / 8;      // 16-byte pieces per row
-    constexpr int BUF = 2 * DEC_CHUNK * LD;     // one buffer: K rows then V rows, in elements
-    extern __shared__ __align__(16) uint8_t smem_bytes[];
-    bf16* q_s = reinterpret_cast<bf16*>(smem_bytes);       // [16][LD]
-    bf16* kv_s = q_s + 16 * LD;                              // [warps][2 buffers][K|V][DEC_CHUNK][LD]
+// Two ways of bringing a pass's 16 keys and values into shared memory:
+//   TMA == false  cp.async, 16 bytes per thread, rows padded by 8 elements against bank conflicts; any
+//                 page size, any head size that is a multiple of 16.
+//   TMA == true   one thread of the warp issues bulk tensor copies (a [16 rows x 64 elements] box per half
+//                 of the head size, 128-byte swizzle) that complete on an mbarrier; ldmatrix undoes the
+//                 swizzle in its addresses.  Needs pages of a multiple of 16 positions and a head size of
+//                 64 or 128, and cuts the instructions spent on loading to a few per pass.
+template <int D, bool TMA>
+__global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                           DecodeArgs a) {
+    constexpr int LD = TMA ? 64 : D + 8;   // row pitch in elements: swizzled 128-byte rows, or padded rows
+    constexpr int VEC = D / 8;             // 16-byte pieces per row
+    constexpr int HALVES = TMA ? D / 64 : 1;
+    constexpr int BUF = 2 * DEC_CHUNK * (TMA ? D : D + 8);     // one buffer: K rows then V rows, in elements
+    constexpr int QLD = D + 8;
+    extern __shared__ __align__(1024) uint8_t smem_bytes[];
+    // TMA: the staging buffers come first so that they sit on 1024-byte boundaries (each is a multiple of 1024)
+    bf16* kv_s = reinterpret_cast<bf16*>(smem_bytes);                       // [warps][2 buffers][K|V][...]
+    bf16* q_s = kv_s + DEC_WARPS * 2 * BUF;                                  // [16][QLD]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 16 * QLD);            // [warps][2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nq / a.nkv;
@@ -94,7 +110,40 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
     const int wk0 = max(k_begin, wbase), wk1 = min(k_end, wbase + DEC_WARP_KEYS - 1);
     const int c_first = (wk0 - wbase) / DEC_CHUNK, c_last = (wk1 - wbase) / DEC_CHUNK;    // meaningful if wk0 <= wk1
     const bool has_keys = wk0 <= wk1;
-    if (has_keys) {
+    uint64_t* my_bars = bars + warp * 2;
+    uint32_t phase[2] = {0, 0};
+    bool tma_ok = true;
+
+    // One pass by TMA: K and V of 16 consecutive keys of one page (a pass never straddles pages, which
+    // hold a multiple of 16 positions), as 2 * HALVES boxes of [16 rows x 64 elements].
+    auto tma_issue = [&](int chunk0, int buf) {
+        const int blk = chunk0 >> a.page_shift;
+        const int page = table[blk];
+        const int off = chunk0 - (blk << a.page_shift);
+        bf16* dst = w_s + buf * BUF;
+        const int row_k = ((page * 2 + 0) * a.nkv + kvh) * a.page_size + off;
+        const int row_v = ((page * 2 + 1) * a.nkv + kvh) * a.page_size + off;
+        sm100::mbar_arrive_expect_tx(&my_bars[buf], 2 * DEC_CHUNK * D * 2);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+            sm100::tma_load_2d(dst + hf * DEC_CHUNK * 64, &kv_map, &my_bars[buf], hf * 64, row_k);
+            sm100::tma_load_2d(dst + DEC_CHUNK * D + hf * DEC_CHUNK * 64, &kv_map, &my_bars[buf], hf * 64, row_v);
+        }
+    };
+    if (TMA && (sm100::smem_u32(kv_s) & 1023u) != 0) {
+        // the swizzle that ldmatrix undoes assumes staging buffers on 1024-byte boundaries
+        if (threadIdx.x == 0) atomicExch(a.status, 5);
+        return;
+    }
+    if (TMA) {
+        if (lane == 0) {
+            sm100::mbar_init(&my_bars[0], 1);
+            sm100::mbar_init(&my_bars[1], 1);
+            sm100::fence_barrier_init();
+        }
+        __syncwarp();
+        if (has_keys && lane == 0) tma_issue(wbase + c_first * DEC_CHUNK, 0);
+    } else if (has_keys) {
         decode_load_chunk<D>(a, table, kvh, plane, wbase + c_first * DEC_CHUNK, k_begin, k_end, w_s, w_s + DEC_CHUNK * LD, lane);
         cp_async_commit();
     }
@@ -104,12 +153,19 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
         const int g = idx / VEC, c = idx % VEC;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (g < heads_here) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)r * a.nq + head0 + g) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_s + g * LD + c * 8) = v;
+        *reinterpret_cast<uint4*>(q_s + g * QLD + c * 8) = v;
     }
     __syncthreads();
     uint32_t qa[D / 16][4];
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * LD + ks * 16 + (lane / 16) * 8);
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qa[ks], q_s + (lane % 16) * QLD + ks * 16 + (lane / 16) * 8);
+
+    // Address of the 8-element piece at (row, first column col) of a staged K or V tile.  With TMA the
+    // tile is [halves][16 rows][64 elements] and the 16-byte pieces of a row are XOR-swizzled by row % 8.
+    auto piece = [&](bf16* tile, int row, int col) -> bf16* {
+        if (TMA) return tile + (col >> 6) * (DEC_CHUNK * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
+        return tile + row * LD + col;
+    };
 
     float o[D / 8][4];
 #pragma unroll
@@ -122,8 +178,16 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
         for (int c = c_first; c <= c_last; ++c) {
             const int buf = (c - c_first) & 1;
             bf16* k_s = w_s + buf * BUF;
-            bf16* v_s = k_s + DEC_CHUNK * LD;
-            if (c < c_last) {       // ask for the next pass while this one is computed
+            bf16* v_s = k_s + (TMA ? DEC_CHUNK * D : DEC_CHUNK * LD);
+            if (TMA) {
+                if (c < c_last && lane == 0) tma_issue(wbase + (c + 1) * DEC_CHUNK, buf ^ 1);
+                const bool landed = sm100::mbar_wait(&my_bars[buf], phase[buf]);
+                if (!__all_sync(0xffffffffu, landed)) {     // the whole warp leaves together
+                    tma_ok = false;
+                    break;
+                }
+                phase[buf] ^= 1;
+            } else if (c < c_last) {       // ask for the next pass while this one is computed
                 bf16* nk = w_s + (buf ^ 1) * BUF;
                 decode_load_chunk<D>(a, table, kvh, plane, wbase + (c + 1) * DEC_CHUNK, k_begin, k_end, nk, nk + DEC_CHUNK * LD, lane);
                 cp_async_commit();
@@ -143,13 +207,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
 #pragma unroll
                 for (int k2 = 0; k2 < D / 32; ++k2) {
                     uint32_t b[4];
-                    ldmatrix_x4(b, k_s + (nt * 8 + (lane % 8)) * LD + k2 * 32 + (lane / 8) * 8);
+                    ldmatrix_x4(b, piece(k_s, nt * 8 + (lane % 8), k2 * 32 + (lane / 8) * 8));
                     mma_bf16(s[nt], qa[2 * k2], b[0], b[1]);
                     mma_bf16(s[nt], qa[2 * k2 + 1], b[2], b[3]);
                 }
                 if (D % 32 != 0) {
                     uint32_t b[2];
-                    ldmatrix_x2(b, k_s + (nt * 8 + (lane % 8)) * LD + (D - 16) + ((lane / 8) % 2) * 8);
+                    ldmatrix_x2(b, piece(k_s, nt * 8 + (lane % 8), (D - 16) + ((lane / 8) % 2) * 8));
                     mma_bf16(s[nt], qa[D / 16 - 1], b[0], b[1]);
                 }
             }
@@ -201,16 +265,24 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(Decod
 #pragma unroll
             for (int d2 = 0; d2 < D / 16; ++d2) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, v_s + ((lane % 8) + ((lane / 8) % 2) * 8) * LD + d2 * 16 + (lane / 16) * 8);
+                ldmatrix_x4_trans(b, piece(v_s, (lane % 8) + ((lane / 8) % 2) * 8, d2 * 16 + (lane / 16) * 8));
                 mma_bf16(o[2 * d2], pa, b[0], b[1]);
                 mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
             }
             __syncwarp();
         }
     }
+    if (TMA && !tma_ok) {
+        // a copy did not complete in time: record it, give a copy that may still be in flight time to land
+        if (lane == 0) atomicExch(a.status, 4);
+        sm100::mbar_wait(&my_bars[0], phase[0], 1u << 14);
+        sm100::mbar_wait(&my_bars[1], phase[1], 1u << 14);
+        m_run[0] = m_run[1] = -INFINITY;
+        l_run[0] = l_run[1] = 0.0f;
+    }
 
     // each warp leaves its partial in its own staging area, then the block merges the four
-    float* o_w = reinterpret_cast<float*>(w_s);                 // [16][D]
+    float* o_w = reinterpret_cast<float*>(w_s);                 // [16][D] (every copy into the buffers has landed)
     float* ml_w = o_w + 16 * D;                                  // [16][2]
 #pragma unroll
     for (int i = 0; i < D / 8; ++i)
@@ -283,22 +355,38 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
     if (threadIdx.x < D) a.out[((size_t)r * a.nq + head) * D + threadIdx.x] = __float2bfloat16_rn(acc / L);
 }
 
-template <int D>
-static int launch_decode(const DecodeArgs& a, int R, int splits, cudaStream_t stream) {
-    constexpr int LD = D + 8;
-    constexpr int SMEM = (16 * LD + DEC_WARPS * 2 * 2 * DEC_CHUNK * LD) * 2;
-    static_assert(2 * 2 * DEC_CHUNK * LD * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
+template <int D, bool TMA>
+static int launch_split(const CUtensorMap& map, const DecodeArgs& a, int R, int splits, cudaStream_t stream) {
+    constexpr int ROW = TMA ? D : D + 8;
+    constexpr int SMEM = (DEC_WARPS * 2 * 2 * DEC_CHUNK * ROW + 16 * (D + 8)) * 2 + DEC_WARPS * 2 * 8;
+    static_assert(2 * 2 * DEC_CHUNK * ROW * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
+        if (cudaFuncSetAttribute(attn_decode_split_kernel<D, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
             cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
     const int G = a.nq / a.nkv;
     dim3 grid(splits, a.nkv * ((G + 15) / 16), R);
-    attn_decode_split_kernel<D><<<grid, DEC_THREADS, SMEM, stream>>>(a);
+    attn_decode_split_kernel<D, TMA><<<grid, DEC_THREADS, SMEM, stream>>>(map, a);
     SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+template <int D>
+static int launch_decode(const DecodeArgs& a, int R, int splits, long long pool_rows, cudaStream_t stream) {
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    int rc;
+    const bool tma = (D % 64 == 0) && a.page_shift >= 4 && a.status != nullptr && pool_rows > 0;
+    if (tma) {
+        if (!tmap::make_bf16_map(&map, a.kv, (uint64_t)D, (uint64_t)pool_rows, 0, 64, DEC_CHUNK)) return SHARPI_LAUNCH_FAILED;
+        rc = launch_split<D, (D % 64 == 0)>(map, a, R, splits, stream);
+    } else {
+        rc = launch_split<D, false>(map, a, R, splits, stream);
+    }
+    if (rc != SHARPI_OK) return rc;
     attn_decode_merge_kernel<D><<<dim3(R, a.nq), MERGE_THREADS, 0, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
@@ -308,8 +396,9 @@ static int launch_decode(const DecodeArgs& a, int R, int splits, cudaStream_t st
 // scratch of [R, nq, splits, D] and [R, nq, splits, 2] floats.
 SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int* block_table, const int* row_req,
                                        const int* positions, const int* rows, float* part_o, float* part_ml,
-                                       void* out, int R, int nq, int nkv, int d, int max_blocks, int page_size,
-                                       int mask_kind, int mask_span, int splits, float scale, cudaStream_t stream) {
+                                       void* out, int* status, int num_pages, int R, int nq, int nkv, int d,
+                                       int max_blocks, int page_size, int mask_kind, int mask_span, int splits,
+                                       float scale, cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || splits <= 0 || R > 65535 ||
         nq > 65535)
@@ -324,15 +413,17 @@ SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int*
     a.page_shift = -1;
     for (int sft = 0; sft < 31; ++sft)
         if ((1 << sft) == page_size) a.page_shift = sft;
+    a.status = status;
+    const long long pool_rows = (long long)num_pages * 2 * nkv * page_size;
     switch (d) {
-        case 16: return launch_decode<16>(a, R, splits, stream);
-        case 32: return launch_decode<32>(a, R, splits, stream);
-        case 48: return launch_decode<48>(a, R, splits, stream);
-        case 64: return launch_decode<64>(a, R, splits, stream);
-        case 80: return launch_decode<80>(a, R, splits, stream);
-        case 96: return launch_decode<96>(a, R, splits, stream);
-        case 112: return launch_decode<112>(a, R, splits, stream);
-        case 128: return launch_decode<128>(a, R, splits, stream);
+        case 16: return launch_decode<16>(a, R, splits, pool_rows, stream);
+        case 32: return launch_decode<32>(a, R, splits, pool_rows, stream);
+        case 48: return launch_decode<48>(a, R, splits, pool_rows, stream);
+        case 64: return launch_decode<64>(a, R, splits, pool_rows, stream);
+        case 80: return launch_decode<80>(a, R, splits, pool_rows, stream);
+        case 96: return launch_decode<96>(a, R, splits, pool_rows, stream);
+        case 112: return launch_decode<112>(a, R, splits, pool_rows, stream);
+        case 128: return launch_decode<128>(a, R, splits, pool_rows, stream);
         default: return SHARPI_BAD_ARGUMENT;   // other head sizes use the generic kernel
     }
 }

@@ -28,6 +28,7 @@
 // independent of which tile or batch the row fell into.
 #include "common.cuh"
 #include "sm100.cuh"
+#include "tensor_map.cuh"
 
 using namespace sm100;
 
@@ -220,36 +221,6 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-// bf16 tensor [d2, d1, d0] (d0 innermost, contiguous), box [1, box1, 64], 128-byte swizzle, zero fill.
-static bool make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box1) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return false;
-    const bool three = d2 > 0;
-    cuuint64_t dims[3] = {d0, d1, three ? d2 : 1};
-    cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
-    cuuint32_t box[3] = {TC_BK, box1, 1};
-    cuuint32_t elem[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, three ? 3 : 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int MODE, int NT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmParams& p, int n_tiles, int row_tiles,
                   cudaStream_t stream) {
@@ -279,8 +250,8 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     if (mode == MODE_SWIGLU && (N % 2 != 0)) return SHARPI_BAD_ARGUMENT;
     if (!status || !group_offsets) return SHARPI_BAD_ARGUMENT;
     CUtensorMap mw, ma;
-    if (!make_map(&mw, W, (uint64_t)K, (uint64_t)N, (uint64_t)E, TC_BM)) return SHARPI_LAUNCH_FAILED;
-    if (!make_map(&ma, A, (uint64_t)K, (uint64_t)rows, 0, (uint32_t)row_tile)) return SHARPI_LAUNCH_FAILED;
+    if (!tmap::make_bf16_map(&mw, W, (uint64_t)K, (uint64_t)N, (uint64_t)E, TC_BK, TC_BM)) return SHARPI_LAUNCH_FAILED;
+    if (!tmap::make_bf16_map(&ma, A, (uint64_t)K, (uint64_t)rows, 0, TC_BK, (uint32_t)row_tile)) return SHARPI_LAUNCH_FAILED;
     TcGemmParams p;
     p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;

@@ -195,7 +195,8 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     part_ml = torch.empty((num_rows, nq, splits, 2), dtype=torch.float32, device=q.device)
     check(kernel("sharpi_attention_decode")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
                                             row_req.data_ptr(), positions.data_ptr(), _ptr(rows), part_o.data_ptr(),
-                                            part_ml.data_ptr(), out.data_ptr(), num_rows, nq, nkv, d,
+                                            part_ml.data_ptr(), out.data_ptr(), status_word(q.device).data_ptr(),
+                                            kv_layer.shape[0], num_rows, nq, nkv, d,
                                             block_table.shape[-1], page_size, mask_kind, mask_span, splits,
                                             float(scale), _stream()), "sharpi_attention_decode")
 
@@ -281,8 +282,9 @@ def check_status(device) -> None:
         code = int(w.item())
         if code != 0:
             w.zero_()
-            raise KernelError(f"a tensor-core kernel gave up waiting (code {code}: 1 = free stage, 2 = loaded stage, "
-                              f"3 = finished accumulator); its output is incomplete")
+            raise KernelError(f"a tensor-core kernel gave up (code {code}: 1 = wait for a free stage, 2 = for a loaded "
+                              f"stage, 3 = for the accumulator, 4 = for a key/value copy, 5 = misaligned staging "
+                              f"buffer); its output is incomplete")
 
 
 TC_MODE_STORE, TC_MODE_SWIGLU = 0, 1
