@@ -48,9 +48,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
+    // try_wait itself suspends the thread for a while when the phase is not complete, so the loop
+    // does not burn issue slots; a sleep between polls would only add its wake-up delay to every
+    // hand-over between producer and consumer.
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(32);
     }
     return false;
 }

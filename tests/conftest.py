@@ -67,7 +67,20 @@ TINY_C = {
 }
 TINY_C_INIT = {"seed": 2, "std": 0.08, "norm_std": 0.2}
 
-TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+# A fourth with head size 64, which (with pages of 16 or more positions) takes the kernels that
+# fetch keys and values by TMA; 5 query heads share each kv head as in the large models.
+TINY_D = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 200, "hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 10,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 48, "intermediate_size_mlp": 96,
+    "num_local_experts": 2, "num_experts_per_tok": 1, "interleave_moe_layer_step": 2,
+    "rope_theta": 20000.0, "rope_scaling": None, "no_rope_layers": [1], "attention_chunk_size": 48,
+    "use_qk_norm": True, "attn_temperature_tuning": True, "floor_scale": 20, "attn_scale": 0.2,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+TINY_D_INIT = {"seed": 3, "std": 0.04, "norm_std": 0.1}
+
+TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT)}
 
 
 def make_model_dir(tmp_path_factory, name: str, store_dtype: str = "bfloat16") -> str:

@@ -20,7 +20,7 @@ TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 # the plain implementation with the engine's expert choices and require that every differing
 # choice was such a near-tie: its gate value lies within MARGIN of the largest one.
 MARGIN = 4e-3
-LENGTHS = {"A": [5, 17, 40, 70], "B": [1, 9, 33, 70, 100], "C": [3, 50, 61]}
+LENGTHS = {"A": [5, 17, 40, 70], "B": [1, 9, 33, 70, 100], "C": [3, 50, 61], "D": [130, 7, 75]}
 
 
 def requests_for(name):
