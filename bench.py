@@ -34,6 +34,10 @@ SCOUT = dict(
     rms_norm_eps=1e-5, tie_word_embeddings=False,
 )
 SCOUT_FULL_LAYERS = 48
+# Llama-4-Maverick layer sizes: dense SwiGLU (16384) and 128-expert layers alternate.
+MAVERICK = dict(SCOUT, num_local_experts=128, interleave_moe_layer_step=2, intermediate_size_mlp=16384,
+                rope_scaling=None)
+MAVERICK_FULL_LAYERS = 48
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -148,10 +152,65 @@ def inject_prefilled(engine, prompt, params):
     return rid
 
 
+def long_context_run(ns, cfg, pk, pk_kind) -> int:
+    """One request with a 65536-token prompt, prefilled through the engine in 2048-token portions, then
+    256 decoded tokens.  The prompt crosses eight attention chunks: the chunked layers give their pages
+    back behind the live chunk, the global layers keep the whole history."""
+    import torch
+
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams, build_random_model
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    prompt_len, portion, new_tokens, page = 65536, ns.prefill_tokens, 256, 64
+    model = build_random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
+    engine = Engine(model, dtype="bfloat16", device=dev,
+                    options=EngineOptions(page_size=page, max_cache_tokens=prompt_len + new_tokens + 2 * page, max_batch=1,
+                                          max_tokens_per_step=portion))
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
+    rid = engine.add_request(prompt, SamplingParams(temperature=0.0, max_new_tokens=new_tokens))
+    req = engine._requests[rid]
+    chunk_group = [g for g in engine.cache.groups if g.spec.kind == "chunk"][0].index
+    full_group = [g for g in engine.cache.groups if g.spec.kind == "full"][0].index
+    most_chunk_pages = 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    portions = 0
+    while not req.generated:
+        engine.step()
+        portions += 1
+        most_chunk_pages = max(most_chunk_pages, engine.cache.held_pages(rid)[chunk_group])
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    full_pages = engine.cache.held_pages(rid)[full_group]
+    while engine.has_unfinished:
+        engine.step()
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    out = {
+        "metric": "long context: prefill tok/s over a 65536-token prompt in 2048-token portions, then decode tok/s",
+        "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
+        "prefill": {"value": prompt_len / (t1 - t0), "unit": "tokens/s", "tokens": prompt_len, "portions": portions,
+                    "seconds": t1 - t0},
+        "decode": {"value": (new_tokens - 1) / (t2 - t1), "unit": "tokens/s", "tokens": new_tokens - 1,
+                   "ms_per_step": (t2 - t1) * 1e3 / (new_tokens - 1)},
+        "cache": {"page_size": page, "chunk_group_pages_at_most": most_chunk_pages,
+                  "chunk_group_positions_at_most": most_chunk_pages * page,
+                  "global_group_pages_after_prefill": full_pages},
+        "config": {"model": "llama4-scout-sizes", "layers": ns.layers, "layers_full_model": SCOUT_FULL_LAYERS,
+                   "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "experts": cfg.num_local_experts, "chunk": cfg.attention_chunk_size,
+                   "prompt": prompt_len, "portion": portion, "new_tokens": new_tokens},
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=20)
@@ -159,7 +218,20 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--preset", default="scout", choices=["scout", "maverick", "long"],
+                    help="scout: 20 Scout-sized layers, batch 8 at context 8192 (the default run); maverick: 4 "
+                         "Maverick-sized layers (dense / 128 experts alternating), batch 64 at context 4096; long: 8 "
+                         "Scout-sized layers, one 65536-token prompt prefilled in 2048-token portions, then 256 "
+                         "decoded tokens")
     ns = ap.parse_args()
+    if ns.preset == "maverick":
+        defaults = ap.parse_args([])
+        ns.layers = 4 if ns.layers == defaults.layers else ns.layers
+        ns.batch = 64 if ns.batch == defaults.batch else ns.batch
+        ns.context = 4096 if ns.context == defaults.context else ns.context
+        ns.points = "" if ns.points == defaults.points else ns.points
+    if ns.preset == "long":
+        ns.layers = 8 if ns.layers == ap.get_default("layers") else ns.layers
 
     if ns.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -177,9 +249,12 @@ def main() -> int:
     from sharpinference_b200.config import Llama4TextConfig
     from sharpinference_b200.kernels import library
 
-    cfg = Llama4TextConfig.from_dict(dict(SCOUT, num_hidden_layers=ns.layers,
+    base = MAVERICK if ns.preset == "maverick" else SCOUT
+    cfg = Llama4TextConfig.from_dict(dict(base, num_hidden_layers=ns.layers,
                                           no_rope_layers=[i for i in range(ns.layers) if (i + 1) % 4 == 0]))
     pk, pk_kind = peaks()
+    if ns.preset == "long":
+        return long_context_run(ns, cfg, pk, pk_kind)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     t0 = time.time()
@@ -281,11 +356,12 @@ def main() -> int:
         points[f"decode_b{b}"] = b / pms * 1e3
 
     out = {
-        "metric": "decode tok/s @ batch 8, context 8192 (Llama-4-Scout layer sizes, random bf16 weights)",
+        "metric": f"decode tok/s @ batch {ns.batch}, context {ns.context} "
+                  f"(Llama-4-{'Maverick' if ns.preset == 'maverick' else 'Scout'} layer sizes, random bf16 weights)",
         "value": ns.batch / ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0, 0.02), uniform random token ids, cache pre-filled with random keys and values",
-        "config": {"model": "llama4-scout-sizes", "layers": ns.layers, "layers_full_model": SCOUT_FULL_LAYERS,
+        "config": {"model": f"llama4-{ns.preset}-sizes", "layers": ns.layers, "layers_full_model": SCOUT_FULL_LAYERS,
                    "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "experts": cfg.num_local_experts, "expert_inter": cfg.intermediate_size,
                    "shared_inter": cfg.intermediate_size, "vocab": cfg.vocab_size, "chunk": cfg.attention_chunk_size,

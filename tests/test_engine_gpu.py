@@ -1,5 +1,7 @@
 """The engine against the plain implementation under every way of cutting the work, in 32-bit and
 in bfloat16 (needs a GPU)."""
+import os
+
 import pytest
 import torch
 
@@ -244,3 +246,53 @@ def test_decode_steps_replayed_as_cuda_graphs_give_the_same_logits(model_dirs, d
     ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
     err, where = traces.worst_error(outs[True], ref)
     assert err < (TOL["float32"] if dtype == "float32" else 0.1), (err, where)
+
+
+def test_sampling_options_through_the_entry_point(model_dirs):
+    """top-k / top-p / min-p / penalties / logit bias / stop tokens as request parameters."""
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams
+    cfg, w = plain.load_folder(model_dirs["A"])
+    eng = Engine(model_dirs["A"], dtype="float32", device="cuda:0",
+                 options=EngineOptions(page_size=16, max_cache_tokens=512, max_batch=4, max_tokens_per_step=32))
+    prompt = traces.random_tokens(cfg["vocab_size"], 12, seed=77)
+    greedy = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=6))[0]
+    # top_k = 1 is greedy whatever the temperature and the seed
+    assert eng.generate([prompt], SamplingParams(temperature=1.5, top_k=1, max_new_tokens=6, seed=5))[0] == greedy
+    # a logit bias large enough forces its token; a stop token ends the request and is not reported
+    forced = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=3, logit_bias={7: 1e4}))[0]
+    assert forced == [7, 7, 7]
+    stopped = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=6, stop_token_ids=[greedy[2]]))[0]
+    assert stopped == greedy[:2]
+    # a presence penalty that large forbids every token seen so far (prompt tail included)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=10, presence_penalty=1e4))[0]
+    assert len(set(out)) == len(out) and not (set(out) & set(prompt))
+    # nucleus sampling only ever returns tokens of the nucleus
+    sp = SamplingParams(temperature=1.0, top_p=0.3, max_new_tokens=1, seed=11)
+    dist = plain.sample_distribution(plain.forward(cfg, w, prompt)[-1], 1.0, top_p=0.3)
+    for seed in range(20):
+        tok = eng.generate([prompt], SamplingParams(temperature=1.0, top_p=0.3, max_new_tokens=1, seed=seed))[0][0]
+        assert dist[tok] > 0
+    assert not eng.cache.requests
+
+
+def test_command_line_generates(model_dirs, tmp_path):
+    import json
+    import subprocess
+    from conftest import ROOT, TINY_B
+    cfg, w = plain.load_folder(model_dirs["B"])
+    cli = os.path.join(ROOT, "bin", "sharpi-cli")
+    proc = subprocess.run([cli, "-m", model_dirs["B"], "-p", "5 17 3; 9 9 200 1", "-n", "5", "--temp", "0", "--dtype",
+                           "float32", "--page-size", "16", "--max-cache-tokens", "256", "--repeat-penalty", "1.0",
+                           "--json"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    outs = json.loads(proc.stdout.strip().splitlines()[-1])["outputs"]
+    assert [o["tokens"] for o in outs] == [plain.generate_greedy(cfg, w, p, 5) for p in ([5, 17, 3], [9, 9, 200, 1])]
+    assert "Prefill: 7 tokens" in proc.stderr and "Decode: 8 tokens" in proc.stderr
+    # random-weights mode: a config file and a seed are enough
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY_B))
+    proc = subprocess.run([cli, "--random-weights", "3", "--config", str(cfg_path), "--tokens", "1,2,3", "-n", "4",
+                           "--temp", "0.8", "-s", "9", "--max-cache-tokens", "128"], capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    assert len(proc.stdout.strip().splitlines()[-1].split("|")[-1].split()) == 4
