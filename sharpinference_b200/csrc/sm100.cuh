@@ -30,6 +30,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Make shared-memory writes of this thread visible to the asynchronous proxy (TMA, tcgen05.mma).
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -125,6 +134,21 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive fp32 columns; the caller waits (tmem_ld_wait) before using the values.
+__device__ __forceinline__ void tmem_ld_32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // ---- tcgen05.mma -----------------------------------------------------------------------
 // Shared-memory matrix descriptor of a K-major tile written by TMA with 128-byte swizzle: rows of
 // 64 bf16 (128 bytes), groups of 8 rows 1024 bytes apart.  The tile base is 1024-byte aligned; a
@@ -140,11 +164,27 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(const void* tile, int k_by
     return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, D is M x N.
-__host__ __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n) {
+// The same for an operand whose M or N index is the contiguous one ("MN-major"), as a [K rows][64
+// elements] tile written by TMA with 128-byte swizzle: 64 contiguous MN elements and 8 K rows make one
+// 1024-byte atom; `mn_atom_bytes` is the distance to the next 64 MN elements, the next 8 K rows are
+// 1024 bytes on.  A step of 16 along K adds 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t mn_atom_bytes, int byte_offset = 0) {
+    const uint32_t addr = smem_u32(tile) + (uint32_t)byte_offset;
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((mn_atom_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset: between MN atoms
+    d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset: between 8-row K groups
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, D is M x N; operands K-major unless b_mn_major.
+__host__ __device__ __forceinline__ uint32_t instr_desc_bf16(int m, int n, bool b_mn_major = false) {
     return (1u << 4)                     // D format: fp32
            | (1u << 7)                   // A format: bf16
            | (1u << 10)                  // B format: bf16
+           | ((b_mn_major ? 1u : 0u) << 16)
            | ((uint32_t)(n >> 3) << 17)  // N / 8
            | ((uint32_t)(m >> 4) << 24); // M / 16
 }

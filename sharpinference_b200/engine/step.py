@@ -38,7 +38,7 @@ class StepEntry:
 
 
 class StepRunner:
-    ATTENTION_TILE = 64        # rows of one request that one attention CTA serves
+    ATTENTION_TILE = 64        # rows of one request that one attention CTA serves (128 with the tcgen05 kernel)
     DECODE_ROWS_UP_TO = 4      # entries this short are served row by row by the split-KV kernel
 
     def __init__(self, model, cache: CacheManager):
@@ -46,6 +46,10 @@ class StepRunner:
         self.cache = cache
         self.device = cache.device
         self._slots = cache.layer_slots()
+        # rows per attention tile: the largest size every mixer that cares can take
+        sizes = [b.mixer.prefill_tile_rows(cache.page_size) for b in getattr(model, "blocks", [])
+                 if hasattr(b.mixer, "prefill_tile_rows")]
+        self.attention_tile = min(sizes) if sizes else self.ATTENTION_TILE
         self.steps_run = 0
         self.rows_run = 0
         # Tracing, for hunting the first difference: when `trace_router` is set, every routed
@@ -126,8 +130,8 @@ class StepRunner:
             if n <= self.DECODE_ROWS_UP_TO:
                 decode_rows.extend(range(r, r + n))
             else:
-                for t0 in range(0, n, self.ATTENTION_TILE):
-                    tiles.extend((r + t0, min(self.ATTENTION_TILE, n - t0), starts[b] + t0, b))
+                for t0 in range(0, n, self.attention_tile):
+                    tiles.extend((r + t0, min(self.attention_tile, n - t0), starts[b] + t0, b))
             tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int64)
             positions[r:r + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             row_request[r:r + n] = b
@@ -192,6 +196,7 @@ class StepRunner:
                          else width * cache.page_size),
             decode_only=all(n == 1 for n in lengths),
             attn_tiles=view(7 + G, 4 * n_tiles).view(n_tiles, 4) if n_tiles else None, num_attn_tiles=n_tiles,
+            attn_tile_rows=self.attention_tile,
             decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
         )
 

@@ -92,15 +92,17 @@ def attention_prefill(ns) -> None:
     start = ns.start
     kv, table = _cache(1, start + T, nkv, d, ps)
     q = torch.randn(T, nq, d, device=DEV).to(torch.bfloat16)
-    tiles = torch.tensor([[t0, min(64, T - t0), start + t0, 0] for t0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+    rows = 64 if ns.warp_mma else ops.TC_PREFILL_TILE
+    tiles = torch.tensor([[t0, min(rows, T - t0), start + t0, 0] for t0 in range(0, T, rows)], dtype=torch.int32, device=DEV)
     out = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
     kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
-    fn = lambda: ops.attention_prefill(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=kind,
-                                       mask_span=ns.span, scale=1 / math.sqrt(d))
+    kernel = ops.attention_prefill if ns.warp_mma else ops.attention_prefill_tc
+    fn = lambda: kernel(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=kind,
+                        mask_span=ns.span, scale=1 / math.sqrt(d))
     ms = _time(fn, ns.iters)
     pairs = sum(min(start + t + 1, (start + t) % ns.span + 1 if kind == ops.MASK_CHUNK else start + t + 1) for t in range(T))
     flops = 4 * nq * d * pairs
-    print(f"attention_prefill tokens={T} start={start} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
+    print(f"attention_prefill ({'m16n8k16' if ns.warp_mma else 'tcgen05'}) tokens={T} start={start} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.0f} TFLOP/s")
 
 
 def main(argv=None) -> int:
@@ -127,6 +129,7 @@ def main(argv=None) -> int:
         p.add_argument("--page-size", type=int, default=64)
         p.add_argument("--mask", choices=["full", "chunk"], default="full")
         p.add_argument("--span", type=int, default=8192)
+        p.add_argument("--warp-mma", action="store_true", help="attention_prefill: the m16n8k16 kernel with 64-row tiles")
         p.set_defaults(fn=fn)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=10)

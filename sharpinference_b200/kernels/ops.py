@@ -219,6 +219,33 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                                              _stream()), "sharpi_attention_prefill")
 
 
+TC_PREFILL_TILE = 128
+
+
+def tc_prefill_supported(dtype: torch.dtype, d: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention kernel takes this layer: bfloat16, head size 64 or 128,
+    pages of a power of two >= 64 positions."""
+    return dtype == torch.bfloat16 and d in (64, 128) and page_size >= 64 and (page_size & (page_size - 1)) == 0
+
+
+def attention_prefill_tc(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
+                         out: torch.Tensor, *, nq: int, nkv: int, d: int, page_size: int, mask_kind: int,
+                         mask_span: int, scale: float) -> None:
+    """Paged attention for tiles of up to 128 consecutive rows of one request on tcgen05 / TMEM / TMA."""
+    _need(q, "q", torch.bfloat16)
+    _need(kv_layer, "kv_layer", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32)
+    if not tc_prefill_supported(q.dtype, d, page_size):
+        raise KernelError(f"the tcgen05 attention kernel takes head sizes 64 and 128 and pages of 64 * 2^k positions, "
+                          f"found head size {d}, page size {page_size}")
+    check(kernel("sharpi_attention_prefill_tc")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
+                                                tiles.data_ptr(), out.data_ptr(), status_word(q.device).data_ptr(),
+                                                q.shape[0], kv_layer.shape[0], tiles.shape[0], nq, nkv, d,
+                                                block_table.shape[-1], page_size, mask_kind, mask_span, float(scale),
+                                                _stream()), "sharpi_attention_prefill_tc")
+
+
 def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
             out_rows: Optional[torch.Tensor] = None, rows: Optional[int] = None, accumulate: bool = False
@@ -284,7 +311,8 @@ def check_status(device) -> None:
             w.zero_()
             raise KernelError(f"a tensor-core kernel gave up (code {code}: 1 = wait for a free stage, 2 = for a loaded "
                               f"stage, 3 = for the accumulator, 4 = for a key/value copy, 5 = misaligned staging "
-                              f"buffer); its output is incomplete")
+                              f"buffer, 11-17 = attention: queries, keys, values, scores, probabilities, outputs, "
+                              f"free stage); its output is incomplete")
 
 
 TC_MODE_STORE, TC_MODE_SWIGLU = 0, 1

@@ -52,6 +52,11 @@ class PagedAttention(Mixer):
         # an encoding that edits q and k itself may look at the step's host-side lists: no graph then
         self.graph_safe = position is None or position.rotary() is not None
 
+    def prefill_tile_rows(self, page_size: int) -> int:
+        """Rows of one request that one attention CTA serves in a prompt portion: 128 where the tcgen05
+        kernel takes this layer (bfloat16, head size 64 or 128, pages of 64 * 2^k), else 64."""
+        return ops.TC_PREFILL_TILE if ops.tc_prefill_supported(self.act_dtype, self.head_dim, page_size) else 64
+
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         T = ctx.num_tokens
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
@@ -78,9 +83,9 @@ class PagedAttention(Mixer):
             # tensor-core kernels: tiles of prompt rows, and single rows split over their keys
             o = torch.empty((T, nq * d), dtype=torch.bfloat16, device=h.device)
             if ctx.num_attn_tiles:
-                ops.attention_prefill(q, slot.kv, table, ctx.attn_tiles, o, nq=nq, nkv=nkv, d=d,
-                                      page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
-                                      scale=self.softmax_scale)
+                prefill = ops.attention_prefill_tc if ctx.attn_tile_rows == ops.TC_PREFILL_TILE else ops.attention_prefill
+                prefill(q, slot.kv, table, ctx.attn_tiles, o, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
+                        mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale)
             if ctx.num_decode_rows:
                 ops.attention_decode(q, slot.kv, table, ctx.row_request, ctx.positions, o, rows=ctx.decode_rows,
                                      num_rows=ctx.num_decode_rows, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,

@@ -112,6 +112,7 @@ class StepContext:
     # list of single rows (int32 [m]; None with num_decode_rows == num_tokens means "all rows")
     attn_tiles: Optional[torch.Tensor] = None
     num_attn_tiles: int = 0
+    attn_tile_rows: int = 64                # rows per tile: 128 when every attention layer takes the tcgen05 kernel
     decode_rows: Optional[torch.Tensor] = None
     num_decode_rows: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)

@@ -572,3 +572,63 @@ def test_router_rows_do_not_depend_on_the_batch(ops):
     e_one, w_one, l_one = ops.router_top1(h[301:302].contiguous(), wr, want_logits=True)
     assert torch.equal(l_big[:7], l_small) and torch.equal(l_big[301:302], l_one)
     assert torch.equal(e_big[:7], e_small) and torch.equal(w_big[301:302], w_one)
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps", [(2, 1, 64, 64), (5, 1, 128, 64), (8, 2, 128, 128), (6, 3, 64, 256)])
+@pytest.mark.parametrize("mask", [("full", 0), ("chunk", 100), ("chunk", 128), ("window", 50), ("window", 300)])
+def test_attention_prefill_tcgen05(ops, nq, nkv, d, ps, mask):
+    """The tcgen05 / TMEM kernel: tiles of 128 rows; portions that start at odd positions, cross chunk
+    edges and end inside a page."""
+    lens = [700, 333, 150, 9]
+    kv, table, ks, vs = paged_setup(lens, nkv, d, ps, torch.bfloat16, seed=d + ps + nq)
+    portions = [(0, 0, 333), (1, 77, 256), (2, 140, 10), (3, 4, 5), (0, 333, 367)]      # request, first position, rows
+    rows, tiles = [], []
+    for b, p0, n in portions:
+        for t0 in range(0, n, 128):
+            tiles.append([len(rows) + t0, min(128, n - t0), p0 + t0, b])
+        rows.extend((b, p0 + i) for i in range(n))
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32)
+    row_req = torch.tensor([b for b, _ in rows], dtype=torch.int32)
+    q = rnd(len(rows), nq, d, dtype=torch.bfloat16, seed=14)
+    kind, span = mask
+    code, lo_factory = MASKS[kind]
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(len(rows), nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill_tc(q, kv, table, torch.tensor(tiles, dtype=torch.int32, device=DEV), out, nq=nq, nkv=nkv, d=d,
+                             page_size=ps, mask_kind=code, mask_span=max(span, 1), scale=scale)
+    ops.check_status(DEV)
+    ref = attention_ref(q.cpu(), ks, vs, positions, row_req, lo_factory(span), scale, nq, nkv)
+    assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_prefill_tcgen05_far_key_and_edges(ops):
+    nq, nkv, d, ps, n = 2, 1, 64, 64, 700
+    scale = 1 / math.sqrt(d)
+    for far in (0, 1, 63, 64, 127, 128, 383, 384, 571, 572, 698, 699):
+        kv, table, ks, vs = paged_setup([n], nkv, d, ps, torch.bfloat16, seed=far)
+        q = rnd(128, nq, d, dtype=torch.bfloat16, seed=far + 1)           # rows at positions 572 .. 699
+        page, off = int(table[0, far // ps]), far % ps
+        kv[page, 0, 0, off] = (q[127, 0].float() * 6.0).to(torch.bfloat16)
+        target = kv[page, 1, 0, off].float()
+        out = torch.zeros(128, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_tc(q, kv, table, torch.tensor([[0, 128, n - 128, 0]], dtype=torch.int32, device=DEV), out,
+                                 nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=0, mask_span=1, scale=scale)
+        ops.check_status(DEV)
+        assert torch.allclose(out[127, :d].float(), target, atol=6e-2), far
+    for kind, span, pos, outside, inside in (("chunk", 24, 50, 47, 48), ("chunk", 64, 64, 63, 64), ("window", 9, 60, 51, 52),
+                                             ("chunk", 256, 256, 255, 256), ("window", 256, 600, 344, 345)):
+        code = {"chunk": 1, "window": 2}[kind]
+        for which, key in (("outside", outside), ("inside", inside)):
+            kv, table, ks, vs = paged_setup([n], 1, 64, 64, torch.bfloat16, seed=pos)
+            q = rnd(1, 2, 64, dtype=torch.bfloat16, seed=3)
+            page, off = int(table[0, key // 64]), key % 64
+            kv[page, 0, 0, off] = (q[0, 0].float() * 4.0).to(torch.bfloat16)
+            kv[page, 1, 0, off] = 50.0
+            out = torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV)
+            ops.attention_prefill_tc(q, kv, table, torch.tensor([[0, 1, pos, 0]], dtype=torch.int32, device=DEV), out,
+                                     nq=2, nkv=1, d=64, page_size=64, mask_kind=code, mask_span=span, scale=0.125)
+            ops.check_status(DEV)
+            if which == "outside":
+                assert float(out[0, :64].float().abs().max()) < 10.0, (kind, pos, key)
+            else:
+                assert float(out[0, :64].float().min()) > 40.0, (kind, pos, key)
