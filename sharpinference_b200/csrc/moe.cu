@@ -15,11 +15,56 @@ enum RouterGate : int {
 };
 
 constexpr int ROUTER_THREADS = 256;
+constexpr int ROUTER_SEGMENTS = 8;
 
-// One block serves TPB consecutive tokens: a warp reads a router row once and forms the dot product
-// with each of the block's tokens.  Every token's sum is the same chain of operations whatever TPB
-// is (a lane adds its own stride-32 elements in order, the warp adds the 32 lane sums in a fixed
-// tree), so the logits do not depend on how many tokens share a block.
+// The one summation order of a router logit, whatever kernel computes it: the width is cut into
+// ROUTER_SEGMENTS contiguous segments (of a multiple of 4 elements); inside a segment a lane adds its own
+// stride-32 pieces in ascending order (four-element pieces when `vec`), the warp adds the 32 lane sums in
+// a fixed tree; the segment sums are added in ascending order.  So a token's logits are the same bits
+// alone or in a large batch, and it picks the same expert in every way of cutting the work.
+__host__ __device__ __forceinline__ int router_segment_len(int H) {
+    return (((H + ROUTER_SEGMENTS - 1) / ROUTER_SEGMENTS) + 3) & ~3;
+}
+
+__device__ __forceinline__ float router_segment_dot(const float* __restrict__ h, const float* __restrict__ w,
+                                                    int begin, int end, bool vec, int lane) {
+    float acc = 0.0f;
+    if (end > begin) {
+        if (vec) {
+            const float4* h4 = reinterpret_cast<const float4*>(h + begin);
+            const float4* w4 = reinterpret_cast<const float4*>(w + begin);
+            const int n4 = (end - begin) >> 2;       // vec implies H % 4 == 0: every segment is whole pieces
+#pragma unroll 8
+            for (int i = lane; i < n4; i += 32) {
+                const float4 a = h4[i], b = __ldg(w4 + i);
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int i = begin + lane; i < end; i += 32) acc = fmaf(h[i], w[i], acc);
+        }
+    }
+    return warp_sum(acc);
+}
+
+__device__ __forceinline__ void router_pick(const float* r, int E, int* expert_id, float* expert_weight) {
+    int best = 0;
+    float best_p = 1.0f / (1.0f + expf(-r[0]));
+    for (int e = 1; e < E; ++e) {
+        const float p = 1.0f / (1.0f + expf(-r[e]));
+        if (p > best_p) {
+            best_p = p;
+            best = e;
+        }
+    }
+    *expert_id = best;
+    *expert_weight = best_p;
+}
+
+// Many tokens: one block serves TPB consecutive tokens; a warp reads a router row once and forms the
+// logits of all the block's tokens with it.
 template <int TPB>
 __global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
                                    int* __restrict__ expert_id, float* __restrict__ expert_weight,
@@ -36,55 +81,52 @@ __global__ void router_top1_kernel(const float* __restrict__ h, const float* __r
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
+    const int seg = router_segment_len(H);
     for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
         const float* w = wr + (size_t)e * H;
-        float acc[TPB];
+        float total[TPB];
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) acc[tt] = 0.0f;
-        if (vec) {
-            const float4* w4 = reinterpret_cast<const float4*>(w);
+        for (int tt = 0; tt < TPB; ++tt) total[tt] = 0.0f;
+        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) {
+            const int begin = min(H, sgm * seg), end = min(H, begin + seg);
+            // the same operations per token as router_segment_dot, with one read of the router row for all
+            float acc[TPB];
+#pragma unroll
+            for (int tt = 0; tt < TPB; ++tt) acc[tt] = 0.0f;
+            if (vec) {
+                const float4* w4 = reinterpret_cast<const float4*>(w + begin);
+                const int n4 = (end - begin) >> 2;
 #pragma unroll 2
-            for (int i = lane; i < H / 4; i += 32) {
-                const float4 b = __ldg(w4 + i);
+                for (int i = lane; i < n4; i += 32) {
+                    const float4 b = __ldg(w4 + i);
 #pragma unroll
-                for (int tt = 0; tt < TPB; ++tt) {
-                    const float4 a = reinterpret_cast<const float4*>(h_s + tt * H)[i];
-                    acc[tt] = fmaf(a.x, b.x, acc[tt]);
-                    acc[tt] = fmaf(a.y, b.y, acc[tt]);
-                    acc[tt] = fmaf(a.z, b.z, acc[tt]);
-                    acc[tt] = fmaf(a.w, b.w, acc[tt]);
+                    for (int tt = 0; tt < TPB; ++tt) {
+                        const float4 a = reinterpret_cast<const float4*>(h_s + tt * H + begin)[i];
+                        acc[tt] = fmaf(a.x, b.x, acc[tt]);
+                        acc[tt] = fmaf(a.y, b.y, acc[tt]);
+                        acc[tt] = fmaf(a.z, b.z, acc[tt]);
+                        acc[tt] = fmaf(a.w, b.w, acc[tt]);
+                    }
+                }
+            } else {
+                for (int i = begin + lane; i < end; i += 32) {
+                    const float b = w[i];
+#pragma unroll
+                    for (int tt = 0; tt < TPB; ++tt) acc[tt] = fmaf(h_s[tt * H + i], b, acc[tt]);
                 }
             }
-        } else {
-            for (int i = lane; i < H; i += 32) {
-                const float b = w[i];
 #pragma unroll
-                for (int tt = 0; tt < TPB; ++tt) acc[tt] = fmaf(h_s[tt * H + i], b, acc[tt]);
-            }
+            for (int tt = 0; tt < TPB; ++tt) total[tt] += warp_sum(acc[tt]);
         }
+        if (lane == 0)
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) {
-            const float total = warp_sum(acc[tt]);
-            if (lane == 0) r_s[tt * E + e] = total;
-        }
+            for (int tt = 0; tt < TPB; ++tt) r_s[tt * E + e] = total[tt];
     }
     __syncthreads();
     if (logits_out)
         for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_THREADS) logits_out[(size_t)t0 * E + i] = r_s[i];
-    if (threadIdx.x < n_tok) {
-        const float* r = r_s + threadIdx.x * E;
-        int best = 0;
-        float best_p = 1.0f / (1.0f + expf(-r[0]));
-        for (int e = 1; e < E; ++e) {
-            const float p = 1.0f / (1.0f + expf(-r[e]));
-            if (p > best_p) {
-                best_p = p;
-                best = e;
-            }
-        }
-        expert_id[t0 + threadIdx.x] = best;
-        expert_weight[t0 + threadIdx.x] = best_p;
-    }
+    if (threadIdx.x < n_tok)
+        router_pick(r_s + threadIdx.x * E, E, expert_id + t0 + threadIdx.x, expert_weight + t0 + threadIdx.x);
 }
 
 template <int TPB>
@@ -103,11 +145,66 @@ static int launch_router(const float* h, const float* wr, int T, int H, int E, i
     return SHARPI_OK;
 }
 
+// Few tokens: what costs time is the chain of dependent loads of one block walking every expert, so each
+// (token, expert) pair gets a block of its own whose eight warps take one segment each; every load of the
+// step is then in flight at once.  The logits go to `logits`; the block that finishes last for a token (a
+// ticket counter per token, which it resets) picks the expert.
+__global__ void __launch_bounds__(ROUTER_SEGMENTS * 32)
+router_top1_small_kernel(const float* __restrict__ h, const float* __restrict__ wr, int H, int E,
+                         int* __restrict__ expert_id, float* __restrict__ expert_weight,
+                         float* __restrict__ logits, int* __restrict__ tickets) {
+    __shared__ float seg_s[ROUTER_SEGMENTS];
+    __shared__ int last_s;
+    const int t = blockIdx.x, e = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(h) & 15) == 0);
+    const int seg = router_segment_len(H);
+    const int begin = min(H, warp * seg), end = min(H, begin + seg);
+    const float part = router_segment_dot(h + (size_t)t * H, wr + (size_t)e * H, begin, end, vec, lane);
+    if (lane == 0) seg_s[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+#pragma unroll
+        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) total += seg_s[sgm];
+        logits[(size_t)t * E + e] = total;
+        __threadfence();
+        last_s = (atomicAdd(&tickets[t], 1) == (int)gridDim.y - 1);
+        if (last_s) {
+            tickets[t] = 0;
+            __threadfence();
+            const float* r = logits + (size_t)t * E;
+            int best = 0;
+            float best_p = 1.0f / (1.0f + expf(-__ldcg(r)));
+            for (int x = 1; x < E; ++x) {
+                const float p = 1.0f / (1.0f + expf(-__ldcg(r + x)));
+                if (p > best_p) {
+                    best_p = p;
+                    best = x;
+                }
+            }
+            expert_id[t] = best;
+            expert_weight[t] = best_p;
+        }
+    }
+}
+
+// `scratch`, optional: [32 * E] floats then [32] zero-initialised ints (the tickets, left zero again).
+// With it, steps of up to 32 tokens take the kernel that gives every (token, expert) pair a block.
 SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H, int E, int gate, int* expert_id,
-                                  float* expert_weight, float* logits_out, cudaStream_t stream) {
+                                  float* expert_weight, float* logits_out, void* scratch, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || E <= 0 || gate != ROUTER_GATE_SIGMOID) return SHARPI_BAD_ARGUMENT;
-    // many tokens: four share a block and a read of the router; few tokens: one block each
+    if (T <= 32 && scratch && E <= 65535) {
+        float* logits = logits_out ? logits_out : reinterpret_cast<float*>(scratch);
+        int* tickets = reinterpret_cast<int*>(reinterpret_cast<float*>(scratch) + (size_t)32 * E);
+        router_top1_small_kernel<<<dim3(T, E), ROUTER_SEGMENTS * 32, 0, stream>>>(h, wr, H, E, expert_id, expert_weight,
+                                                                                 logits, tickets);
+        SHARPI_CHECK_LAUNCH();
+        return SHARPI_OK;
+    }
+    // many tokens: four share a block and a read of the router; else one block each
     if (T >= 256 && (size_t)4 * (H + E) * sizeof(float) <= 200 * 1024)
         return launch_router<4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
     return launch_router<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);

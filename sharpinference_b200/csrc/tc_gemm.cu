@@ -47,6 +47,11 @@ struct TcGemmParams {
     int* status;                // device word: 0 ok, else the code of the wait that gave up
     int rows, N, K, E;          // N: weight rows per expert (MODE_SWIGLU: 2 I)
     int accumulate;
+    // K split over gridDim.z CTAs (few rows and few experts: not enough tiles to fill the GPU otherwise).
+    // Each CTA then leaves its raw fp32 accumulators in partial[z][sorted row][N] and a second kernel adds
+    // the parts in a fixed order and applies the epilogue.
+    float* partial;
+    int k_split;
 };
 
 template <int MODE, int NT>
@@ -106,7 +111,10 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int row0 = tile_info[1], row_end = tile_info[2];
     const int n0 = blockIdx.x * TC_BM;            // MODE_SWIGLU: index into [0, I)
     const int I = p.N / 2;                        // MODE_SWIGLU only
-    const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+    const int k_blocks_all = (p.K + TC_BK - 1) / TC_BK;
+    const int kb_per = (k_blocks_all + p.k_split - 1) / p.k_split;
+    const int kb_begin = blockIdx.z * kb_per;
+    const int k_blocks = max(0, min(k_blocks_all, kb_begin + kb_per) - kb_begin);   // this CTA's share
 
     if (warp == 5) {
         tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -130,10 +138,11 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (!ok) { atomicExch(p.status, 1); break; }
                 uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
                 mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-                tma_load_3d(stage, &map_w, &full_bar[s], kb * TC_BK, n0, expert);
+                const int kx = (kb_begin + kb) * TC_BK;
+                tma_load_3d(stage, &map_w, &full_bar[s], kx, n0, expert);
                 if (MODE == MODE_SWIGLU)
-                    tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kb * TC_BK, I + n0, expert);
-                tma_load_2d(stage + Cfg::W_TILES * Cfg::W_BYTES, &map_a, &full_bar[s], kb * TC_BK, row0);
+                    tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kx, I + n0, expert);
+                tma_load_2d(stage + Cfg::W_TILES * Cfg::W_BYTES, &map_a, &full_bar[s], kx, row0);
                 issued = kb + 1;
             }
             if (!ok) {
@@ -181,7 +190,20 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (c0 >= valid) break;               // uniform over the warp
                 float g[16];
                 tmem_ld_16(lane_addr + c0, g);
-                if (MODE == MODE_SWIGLU) {
+                if (p.k_split > 1) {
+                    float* part = p.partial + (size_t)blockIdx.z * p.rows * p.N;
+                    float u[16];
+                    if (MODE == MODE_SWIGLU) tmem_ld_16(lane_addr + NT + c0, u);
+                    const bool n_ok = MODE == MODE_SWIGLU ? n < I : n < p.N;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int r = row0 + c0 + j;
+                        if (c0 + j < valid && n_ok) {
+                            part[(size_t)r * p.N + n] = (k_blocks > 0) ? g[j] : 0.0f;
+                            if (MODE == MODE_SWIGLU) part[(size_t)r * p.N + I + n] = (k_blocks > 0) ? u[j] : 0.0f;
+                        }
+                    }
+                } else if (MODE == MODE_SWIGLU) {
                     float u[16];
                     tmem_ld_16(lane_addr + NT + c0, u);
                     if (n < I) {
@@ -232,18 +254,43 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmPara
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
-    dim3 grid(n_tiles, row_tiles);
+    dim3 grid(n_tiles, row_tiles, p.k_split);
     tc_grouped_gemm_kernel<MODE, NT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, p);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
 
+// Second half of a K-split product: add the parts in the order z = 0, 1, ... and apply the epilogue.
+template <int MODE>
+__global__ void tc_split_reduce_kernel(const TcGemmParams p) {
+    const int r = blockIdx.x;
+    const int n = blockIdx.y * blockDim.x + threadIdx.x;
+    const int n_out = (MODE == MODE_SWIGLU) ? p.N / 2 : p.N;
+    if (n >= n_out) return;
+    const size_t plane = (size_t)p.rows * p.N;
+    const float* part = p.partial + (size_t)r * p.N;
+    float g = 0.0f, u = 0.0f;
+    for (int z = 0; z < p.k_split; ++z) {
+        g += part[z * plane + n];
+        if (MODE == MODE_SWIGLU) u += part[z * plane + n_out + n];
+    }
+    if (MODE == MODE_SWIGLU) {
+        const float s = p.row_scale ? p.row_scale[p.scale_rows ? p.scale_rows[r] : r] : 1.0f;
+        const float gv = g * s, uv = u * s;
+        reinterpret_cast<bf16*>(p.out)[(size_t)r * n_out + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+    } else {
+        float* dst = reinterpret_cast<float*>(p.out) + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
+        *dst = p.accumulate ? *dst + g : g;
+    }
+}
+
 // A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
 // `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes.
+// `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch) cuts K over that many CTAs per tile.
 SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
                                       const int* out_rows, const float* row_scale, const int* scale_rows,
-                                      int* status, int rows, int N, int K, int E, int mode, int row_tile,
-                                      int accumulate, cudaStream_t stream) {
+                                      int* status, float* partial, int rows, int N, int K, int E, int mode,
+                                      int row_tile, int accumulate, int k_split, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return SHARPI_OK;
     if (K <= 0 || E <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;          // TMA: rows 16-byte aligned
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return SHARPI_UNALIGNED;
@@ -255,15 +302,27 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     TcGemmParams p;
     p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
+    if (k_split < 1 || k_split > 16 || (k_split > 1 && !partial)) return SHARPI_BAD_ARGUMENT;
+    p.partial = partial; p.k_split = k_split;
     const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
     const int n_tiles = (n_out + TC_BM - 1) / TC_BM;
-    const long long row_tiles = (rows + row_tile - 1) / row_tile + E;
+    // tiles = sum over experts of ceil(rows_e / row_tile) <= (experts with rows) + rows / row_tile, and at
+    // most min(rows, E) experts have rows: no more CTAs than that are launched (empty ones cost a slot each)
+    const long long row_tiles = rows / row_tile + (rows < E ? rows : E);
     if (row_tiles > 65535) return SHARPI_BAD_ARGUMENT;
-#define TC_CASE(M, T) if (mode == M && row_tile == T) return launch<M, T>(mw, ma, p, n_tiles, (int)row_tiles, stream);
+    int rc = SHARPI_BAD_ARGUMENT;
+#define TC_CASE(M, T) if (mode == M && row_tile == T) rc = launch<M, T>(mw, ma, p, n_tiles, (int)row_tiles, stream);
     TC_CASE(MODE_STORE, 16) TC_CASE(MODE_STORE, 32) TC_CASE(MODE_STORE, 64) TC_CASE(MODE_STORE, 128) TC_CASE(MODE_STORE, 256)
     TC_CASE(MODE_SWIGLU, 16) TC_CASE(MODE_SWIGLU, 32) TC_CASE(MODE_SWIGLU, 64) TC_CASE(MODE_SWIGLU, 128) TC_CASE(MODE_SWIGLU, 256)
 #undef TC_CASE
-    return SHARPI_BAD_ARGUMENT;
+    if (rc != SHARPI_OK || k_split == 1) return rc;
+    dim3 rgrid(rows, (n_out + 255) / 256);
+    if (mode == MODE_SWIGLU)
+        tc_split_reduce_kernel<MODE_SWIGLU><<<rgrid, 256, 0, stream>>>(p);
+    else
+        tc_split_reduce_kernel<MODE_STORE><<<rgrid, 256, 0, stream>>>(p);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
 }
 
 // out[r, :] = in[rows[r], :] for bf16 rows of width K (a multiple of 8): the activations sorted by

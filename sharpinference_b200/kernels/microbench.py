@@ -22,15 +22,31 @@ from . import ops
 DEV = "cuda:0"
 
 
+USE_GRAPH = False
+
+
 def _time(fn, iters: int, warmup: int = 3) -> float:
+    """Milliseconds per call.  With --graph the calls are captured once and replayed, which takes the
+    host's launch cost out of the measurement (short kernels are otherwise timed by it)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
+    if USE_GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(iters):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        a.record()
+        graph.replay()
+        b.record()
+    else:
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
     torch.cuda.synchronize()
     ops.check_status(DEV)
     return a.elapsed_time(b) / iters
@@ -48,7 +64,8 @@ def tc_gemm(ns) -> None:
         w = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02, generator=g)
         a = torch.empty(T, H, dtype=torch.bfloat16, device=DEV).normal_(0, 1, generator=g)
         scale = torch.rand(T, device=DEV, generator=g)
-        fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale, row_tile=ns.row_tile)
+        fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale, row_tile=ns.row_tile,
+                                         k_split=ns.k_split)
         weight_bytes, flops = used * 2 * I * H * 2, 2 * T * 2 * I * H
     else:
         w = torch.empty(E, H, I, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02, generator=g)
@@ -56,7 +73,7 @@ def tc_gemm(ns) -> None:
         out = torch.zeros(T, H, device=DEV)
         rows = torch.randperm(T, device=DEV).to(torch.int32)
         fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_STORE, out=out, out_rows=rows, accumulate=True,
-                                         row_tile=ns.row_tile)
+                                         row_tile=ns.row_tile, k_split=ns.k_split)
         weight_bytes, flops = used * H * I * 2, 2 * T * H * I
     ms = _time(fn, ns.iters)
     print(f"tc_gemm {ns.mode} rows={T} experts={used}/{E} row_tile={ns.row_tile or ops.tc_row_tile(T)}: {ms * 1e3:.1f} us, "
@@ -116,6 +133,7 @@ def main(argv=None) -> int:
     p.add_argument("--hidden", type=int, default=5120)
     p.add_argument("--inter", type=int, default=8192)
     p.add_argument("--row-tile", type=int, default=None)
+    p.add_argument("--k-split", type=int, default=None)
     p.set_defaults(fn=tc_gemm)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
@@ -133,7 +151,10 @@ def main(argv=None) -> int:
         p.set_defaults(fn=fn)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=10)
+        sp.add_argument("--graph", action="store_true", help="time replays of a CUDA graph of the calls")
     ns = ap.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = ns.graph
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 2

@@ -329,6 +329,18 @@ def tc_row_tile(rows: int) -> int:
     return 128
 
 
+def tc_k_split(rows: int, n_out: int, sms: int = 148) -> int:
+    """Into how many CTAs a tile's K range is cut.  With few rows few experts are active (at most one
+    per row), so 128-row weight tiles alone cannot fill the GPU; cutting K makes up to four times as many
+    CTAs.  The parts are added in a fixed order by a second kernel."""
+    if rows > 16:
+        return 1
+    ctas = rows * ((n_out + 127) // 128)
+    if ctas >= sms:
+        return 1
+    return max(1, min(4, (2 * sms + ctas - 1) // ctas))
+
+
 def gather_rows_bf16(x: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[r] = x[rows[r]]`` for bfloat16 rows whose width is a multiple of 8."""
     _need(x, "x", torch.bfloat16)
@@ -344,7 +356,8 @@ def gather_rows_bf16(x: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Te
 def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, *, mode: int,
                     out: Optional[torch.Tensor] = None, out_rows: Optional[torch.Tensor] = None,
                     row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
-                    accumulate: bool = False, row_tile: Optional[int] = None) -> torch.Tensor:
+                    accumulate: bool = False, row_tile: Optional[int] = None,
+                    k_split: Optional[int] = None) -> torch.Tensor:
     """Per-expert products on the tensor cores.  ``a`` bfloat16 [rows, K] sorted by expert,
     ``w`` bfloat16 [E, N, K], ``group_offsets`` int32 [E + 1].
 
@@ -368,10 +381,13 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
                else torch.empty((rows, N), dtype=torch.float32, device=a.device))
     _need(out, "out", torch.bfloat16 if mode == TC_MODE_SWIGLU else torch.float32)
     status = status_word(a.device)
+    if k_split is None:
+        k_split = tc_k_split(rows, (N // 2 if mode == TC_MODE_SWIGLU else N))
+    partial = torch.empty((k_split, rows, N), dtype=torch.float32, device=a.device) if k_split > 1 else None
     check(kernel("sharpi_tc_grouped_gemm")(a.data_ptr(), w.data_ptr(), group_offsets.data_ptr(), out.data_ptr(),
                                            _ptr(out_rows), _ptr(row_scale), _ptr(scale_rows), status.data_ptr(),
-                                           rows, N, K, E, mode, row_tile or tc_row_tile(rows), int(accumulate),
-                                           _stream()), "sharpi_tc_grouped_gemm")
+                                           _ptr(partial), rows, N, K, E, mode, row_tile or tc_row_tile(rows),
+                                           int(accumulate), k_split, _stream()), "sharpi_tc_grouped_gemm")
     return out
 
 
@@ -386,9 +402,25 @@ def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: 
     expert = torch.empty((T,), dtype=torch.int32, device=h32.device)
     weight = torch.empty((T,), dtype=torch.float32, device=h32.device)
     logits = torch.empty((T, E), dtype=torch.float32, device=h32.device) if want_logits else None
+    scratch = _router_scratch(h32.device, E) if T <= 32 else None
     check(kernel("sharpi_router_top1")(h32.data_ptr(), router_weight.data_ptr(), T, H, E, 0, expert.data_ptr(),
-                                       weight.data_ptr(), _ptr(logits), _stream()), "sharpi_router_top1")
+                                       weight.data_ptr(), _ptr(logits), _ptr(scratch), _stream()), "sharpi_router_top1")
     return expert, weight, logits
+
+
+_router_scratches = {}
+
+
+def _router_scratch(device, num_experts: int) -> torch.Tensor:
+    """Scratch of the few-token router kernel: 32 x E logits, then 32 ticket counters that start at zero
+    and are left at zero by every launch.  One per device and expert count, shared by all layers (launches
+    on one stream run one after the other)."""
+    key = (torch.device(device), num_experts)
+    buf = _router_scratches.get(key)
+    if buf is None:
+        buf = torch.zeros(32 * num_experts + 32, dtype=torch.float32, device=device)
+        _router_scratches[key] = buf
+    return buf
 
 
 def moe_sort(expert_id: torch.Tensor, num_experts: int):

@@ -445,9 +445,42 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
     big = ops.tc_grouped_gemm(a[order.to(DEV)].contiguous(), w, offsets, mode=ops.TC_MODE_STORE, row_tile=128)
     t = 37                                                   # row 37 goes to expert 1, sorted position 100 + 9
     one = ops.tc_grouped_gemm(a[t:t + 1].contiguous(), w, torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device=DEV),
-                              mode=ops.TC_MODE_STORE, row_tile=16)
+                              mode=ops.TC_MODE_STORE, row_tile=16, k_split=1)
     ops.check_status(DEV)
     assert torch.equal(one[0], big[100 + 9])
+    # with K cut over several CTAs the parts are added in another order: equal to rounding, not to the bit
+    cut = ops.tc_grouped_gemm(a[t:t + 1].contiguous(), w, torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device=DEV),
+                              mode=ops.TC_MODE_STORE, row_tile=16, k_split=3)
+    ops.check_status(DEV)
+    assert torch.allclose(cut[0], big[100 + 9], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("k_split", [2, 4, 7])
+def test_tc_grouped_gemm_k_split(ops, k_split):
+    """Few rows: K is cut over several CTAs per tile and a second kernel adds the parts and applies the epilogue."""
+    T, E, I, K = 5, 4, 136, 328
+    expert, order, offsets, a = grouped_case(T, E, K, seed=31)
+    w_gu = rnd(E, 2 * I, K, dtype=torch.bfloat16, scale=0.1, seed=32)
+    scale = torch.rand(T, generator=torch.Generator().manual_seed(33)) * 0.5 + 0.25
+    a_sorted = a[order].contiguous().to(DEV)
+    sorted_rows = order.to(torch.int32).to(DEV)
+    act = ops.tc_grouped_gemm(a_sorted, w_gu, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale.to(DEV),
+                              scale_rows=sorted_rows, k_split=k_split)
+    ops.check_status(DEV)
+    ref = []
+    for t in order.tolist():
+        gu = (a[t].double() @ w_gu[int(expert[t])].double().cpu().T) * float(scale[t])
+        ref.append(gu[:I] / (1 + torch.exp(-gu[:I])) * gu[I:])
+    ref = torch.stack(ref)
+    assert torch.allclose(act.double().cpu(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+    w_d = rnd(E, 200, K, dtype=torch.bfloat16, scale=0.1, seed=34)
+    base = rnd(T, 200, seed=35)
+    acc = base.clone()
+    ops.tc_grouped_gemm(a_sorted, w_d, offsets, mode=ops.TC_MODE_STORE, out=acc, out_rows=sorted_rows, accumulate=True,
+                        k_split=k_split)
+    ops.check_status(DEV)
+    ref_d = torch.stack([a[t].double() @ w_d[int(expert[t])].double().cpu().T for t in range(T)])
+    assert torch.allclose(acc.double().cpu(), base.double().cpu() + ref_d, rtol=1e-4, atol=1e-3)
 
 
 # ---------------------------------------------------------------------------------------
