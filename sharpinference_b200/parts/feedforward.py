@@ -30,7 +30,10 @@ class DenseSwiGLU(FeedForward):
         self.gate_up, self.down, self.act_dtype = gate_up, down, act_dtype
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None) -> torch.Tensor:
-        act = ops.swiglu(self.gate_up(h), self.act_dtype)
+        if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h):
+            act = ops.tc_dense(h, self.gate_up.weight, swiglu=True)       # SwiGLU in the product's epilogue
+        else:
+            act = ops.swiglu(self.gate_up(h), self.act_dtype)
         return self.down(act)
 
 

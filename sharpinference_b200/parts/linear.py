@@ -4,11 +4,14 @@ Which routine runs is decided by the weight's dtype, not by a global mode:
 
 * float32 weight: the CUDA-core kernel with float32 accumulation (``gemm_generic.cu``), the
   product of the true 32-bit path; no tensor cores and no reduced-precision mode are involved.
-* bfloat16 weight: a tensor-core product with float32 accumulation and float32 output.  The
-  dense ones go to the vendor library through ``torch.mm``, which is where the reference uses a
-  library too (cublasGemmEx for batched projections,
-  src/SharpInference.Cuda/CudaBackend.cs:2083-2117); sizes the library path does not take
-  (an inner size that is no multiple of 8) use the CUDA-core kernel.
+* bfloat16 weight: a tensor-core product with float32 accumulation and float32 output.  With
+  many rows (prompt portions) the dense ones go to the vendor library through ``torch.mm``, which
+  is where the reference uses a library too (cublasGemmEx for batched projections,
+  src/SharpInference.Cuda/CudaBackend.cs:2083-2117); with few rows (decode), where the reference
+  runs its own matvec kernels (llm_matvec_*, src/SharpInference.Cuda/CudaTextKernels.cs:1325), they
+  can run our tcgen05 weight-streaming kernel (``stream_rows``; the library stays the default there
+  because it measured faster); sizes neither takes (an inner size that is no multiple of 8) use the
+  CUDA-core kernel.
 
 The grouped (per-expert) product has no library counterpart and always runs our own kernels.
 """
@@ -24,7 +27,7 @@ from ..kernels import ops
 class Linear:
     """A weight ``[out, in]`` and the product with it.  Output is float32 ``[M, out]``."""
 
-    def __init__(self, weight: torch.Tensor, name: str = ""):
+    def __init__(self, weight: torch.Tensor, name: str = "", stream_rows: int = 0):
         if weight.dim() != 2:
             raise ValueError(f"linear weight '{name}' must be 2-D, found shape {tuple(weight.shape)}")
         self.weight = weight
@@ -32,6 +35,10 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self._use_library = (weight.dtype == torch.bfloat16 and self.in_features % 8 == 0)
         self._wt = weight.t() if self._use_library else None
+        # Up to this many rows the product runs on our weight-streaming tcgen05 kernel instead of the
+        # library.  Off by default: measured on B200 at Scout sizes the library's split-K kernels are about
+        # 20 % faster on these shapes (qkv 14 vs 18 us, shared gate|up 28 vs 37 us at 8 rows).
+        self.stream_rows = stream_rows
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         w = self.weight
@@ -40,10 +47,16 @@ class Linear:
                 a = a.to(torch.float32)
             return ops.gemm_nt(a, w, out=out)
         if self._use_library and a.dtype == torch.bfloat16:
+            if a.shape[0] <= self.stream_rows:
+                return ops.tc_dense(a, w, out=out)
             if out is not None:
                 return torch.mm(a, self._wt, out_dtype=torch.float32, out=out)
             return torch.mm(a, self._wt, out_dtype=torch.float32)
         return ops.gemm_nt(a, w, out=out)
+
+    def streams(self, a: torch.Tensor) -> bool:
+        """Whether this product of ``a`` would run on the weight-streaming tensor-core kernel."""
+        return self._use_library and a.dtype == torch.bfloat16 and a.shape[0] <= self.stream_rows
 
 
 class GroupedLinear:

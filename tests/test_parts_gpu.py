@@ -167,3 +167,22 @@ def test_unknown_part_kind_names_the_known_ones():
     assert "paged_attention" in part_kinds("mixer") and "moe_sigmoid_top1" in part_kinds("feed_forward")
     with pytest.raises(ValueError, match="paged_attention"):
         make_part("mixer", "telepathy")
+
+
+def test_linear_on_the_weight_streaming_kernel():
+    """The dense products of a decode step can run on the tcgen05 kernel (one group, K cut over CTAs)."""
+    from sharpinference_b200.parts import DenseSwiGLU, Linear
+    H, I, T = 128, 200, 5
+    g, u, dn = rnd(I, H, scale=0.1, seed=1), rnd(I, H, scale=0.1, seed=2), rnd(H, I, scale=0.1, seed=3)
+    h = rnd(T, H, seed=4)
+    g, u, dn, h = (t.to(torch.bfloat16).float() for t in (g, u, dn, h))
+    gate_up = Linear(torch.cat([g, u]).to(torch.bfloat16).to(DEV), stream_rows=64)
+    down = Linear(dn.to(torch.bfloat16).to(DEV), stream_rows=64)
+    part = DenseSwiGLU(gate_up=gate_up, down=down, act_dtype=torch.bfloat16)
+    hb = h.to(torch.bfloat16).to(DEV)
+    assert gate_up.streams(hb)
+    out = part.forward(None, hb).double().cpu()
+    ref = plain.dense_ffn(h.double(), g.double(), u.double(), dn.double())
+    assert float((out - ref).abs().max()) / float(ref.abs().max()) < 1e-2
+    lib = DenseSwiGLU(gate_up=Linear(gate_up.weight), down=Linear(down.weight), act_dtype=torch.bfloat16)
+    assert float((lib.forward(None, hb).double().cpu() - out).abs().max()) / float(ref.abs().max()) < 1e-2
