@@ -4,13 +4,21 @@
 // page with TMA.  One CTA serves one query head and a tile of up to 128 consecutive rows of one
 // request; a softmax thread owns one row, so row maxima and sums need no shuffles.
 //
-//   warps 0-3  softmax: read S (tcgen05.ld), mask, exp2, running max / sum, write P (bf16, swizzled)
-//              to shared memory, then fold the previous block's O into the row's fp32 accumulator
+//   warps 0-3  softmax: read S (tcgen05.ld), mask, exp2, row max / sum, write P (bf16, swizzled) to
+//              shared memory; at the end read O, divide by the row sum, store
 //   warp 4     TMA producer: Q once, then K and V blocks of 64 keys through the block table
-//   warp 5     allocates tensor memory, issues the MMAs: S[j] = Q K_j^T, then O[j-1] = P[j-1] V[j-1]
+//   warp 5     allocates tensor memory, issues the MMAs: S[j] = Q K_j^T, then O += P[j-1] V[j-1]
 //
-// S, P and O are double-buffered, so QK^T of block j+1 runs while block j is in softmax.  Key blocks
-// sit at absolute multiples of 64 positions: a row's result depends on its own position and keys only.
+// O accumulates in tensor memory over all key blocks.  The exponentials of a row are taken against a
+// reference maximum that is only raised when the row's running maximum has grown by more than 2^8
+// since (p stays below 256, far inside bf16 and fp32 range); only then does the row's warp rescale its
+// 32 lanes of O in tensor memory (load, multiply, store), after the previous PV has completed.  With
+// causal prompts that happens in the first blocks of a row and hardly ever after.  S is double-
+// buffered, so QK^T of block j+1 runs while block j is in softmax; P has one buffer, which the PV of
+// block j has long left when the softmax of block j+1 wants to write it.  Shared memory (112 KB at
+// head size 128), tensor memory (256 columns) and registers are sized so that two CTAs share an SM:
+// the softmax of one hides the waits of the other.  Key blocks sit at absolute multiples of 64
+// positions: a row's result depends on its own position and keys only.
 // Every wait is bounded; a wait that gives up records a code in *status and the kernel winds down.
 //
 // Sizes: head size 64 or 128, pages of a multiple of 64 positions, bf16.  Everything else takes the
@@ -27,7 +35,7 @@ using namespace sm100;
 constexpr int TQ = 128;        // query rows per CTA (MMA M)
 constexpr int TK = 64;         // keys per block
 constexpr int TC_ATT_THREADS = 192;
-constexpr int KV_STAGES = 3;
+constexpr int KV_STAGES = 2;
 
 struct PrefillTcArgs {
     const int* block_table;   // [B, max_blocks]
@@ -46,38 +54,43 @@ struct AttCfg {
     static constexpr int Q_BYTES = TQ * D * 2;
     static constexpr int KV_BYTES = TK * D * 2;           // one K or V block
     static constexpr int P_BYTES = TQ * TK * 2;
-    static constexpr int SMEM = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 2 * P_BYTES + 1024 + 512;
+    static constexpr int BAR_BYTES = 256;
+    // the dynamic shared memory window has to start on a 1024-byte boundary (the kernel checks): there
+    // is no room for padding when two CTAs of head size 128 share an SM
+    static constexpr int SMEM = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + BAR_BYTES;
     static constexpr int S_COL = 0;                        // S[2]: 64 columns each
-    static constexpr int O_COL = 2 * TK;                   // O[2]: D columns each
-    static constexpr int TMEM_COLS = (2 * TK + 2 * D) <= 256 ? 256 : 512;
+    static constexpr int O_COL = 2 * TK;                   // O: D columns
+    static constexpr int TMEM_COLS = 256;                  // 128 + D <= 256
 };
 
 template <int D>
-__global__ void __launch_bounds__(TC_ATT_THREADS, 1)
+__global__ void __launch_bounds__(TC_ATT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                        const PrefillTcArgs a) {
     using Cfg = AttCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {                  // the swizzled tiles need it; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(a.status, ERR_ALIGN);
+        return;
+    }
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Cfg::Q_BYTES;                          // [stages][halves][64 keys][64]
     uint8_t* v_s = k_s + KV_STAGES * Cfg::KV_BYTES;
-    uint8_t* p_s = v_s + KV_STAGES * Cfg::KV_BYTES;             // [2][128 rows][64 keys]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * Cfg::P_BYTES);
+    uint8_t* p_s = v_s + KV_STAGES * Cfg::KV_BYTES;             // [128 rows][64 keys]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
     uint64_t* k_empty = k_full + KV_STAGES;
     uint64_t* v_full = k_empty + KV_STAGES;
     uint64_t* v_empty = v_full + KV_STAGES;
     uint64_t* s_full = v_empty + KV_STAGES;       // [2]
-    uint64_t* p_full = s_full + 2;                // [2] 128 arrivals
-    uint64_t* p_empty = p_full + 2;               // [2]
-    uint64_t* o_full = p_empty + 2;               // [2]
-    uint64_t* o_empty = o_full + 2;               // [2] 128 arrivals
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 2);
+    uint64_t* p_full = s_full + 2;                // 128 arrivals, once per block
+    uint64_t* pv_done = p_full + 1;               // completes once per block, when its PV is done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* tile = a.tiles + (size_t)blockIdx.x * 4;
+    // the last tiles of a prompt have the most keys: start them first, so that the short ones fill the tail
+    const int* tile = a.tiles + (size_t)(gridDim.x - 1 - blockIdx.x) * 4;
     const int row0 = tile[0], n_rows = tile[1], p0 = tile[2];
     const int* table = a.block_table + (size_t)tile[3] * a.max_blocks;
     const int head = blockIdx.y;
@@ -92,10 +105,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 128); mbar_init(&p_empty[s], 1);
-            mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 128);
-        }
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
         fence_barrier_init();
     }
     if (warp == 5) {
@@ -147,20 +159,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(a.status, ERR_Q);
             auto pv = [&](int i) -> bool {
-                const int st = i % KV_STAGES, b = i & 1;
-                if (!mbar_wait(&p_full[b], (i >> 1) & 1)) { atomicExch(a.status, ERR_P); return false; }
+                const int st = i % KV_STAGES;
+                if (!mbar_wait(p_full, i & 1)) { atomicExch(a.status, ERR_P); return false; }
                 if (!mbar_wait(&v_full[st], (i / KV_STAGES) & 1)) { atomicExch(a.status, ERR_V); return false; }
-                if (i >= 2 && !mbar_wait(&o_empty[b], ((i >> 1) - 1) & 1)) { atomicExch(a.status, ERR_O); return false; }
                 tcgen05_fence_after();
-                const uint8_t* pt = p_s + b * Cfg::P_BYTES;
+                const uint8_t* pt = p_s;
                 const uint8_t* vt = v_s + st * Cfg::KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < TK / 16; ++ks)
-                    mma_bf16_ss(tmem_base + Cfg::O_COL + b * D, smem_desc_k_sw128(pt, ks * 32),
-                                smem_desc_mn_sw128(vt, TK * 128, ks * 2048), idesc_pv, ks != 0);
+                    mma_bf16_ss(tmem_base + Cfg::O_COL, smem_desc_k_sw128(pt, ks * 32),
+                                smem_desc_mn_sw128(vt, TK * 128, ks * 2048), idesc_pv, (i | ks) != 0);
                 mma_commit(&v_empty[st]);
-                mma_commit(&p_empty[b]);
-                mma_commit(&o_full[b]);
+                mma_commit(pv_done);
                 return true;
             };
             for (int j = 0; j < n_blocks && ok; ++j) {
@@ -186,28 +196,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const int pos_r = p0 + r;
         const int lo_r = visible_lo(pos_r, a.mask_kind, a.mask_span);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f, corr_prev = 1.0f;
+        constexpr float RAISE = 8.0f;       // in log2 units: the reference maximum lags by at most this much
+        const float scale = a.scale_log2;   // > 0: the maximum of the raw scores is the maximum of the scaled ones
+        float m_ref = -INFINITY, l_run = 0.0f;      // m_ref in log2 units
         bool ok = true;
-
-        auto fold = [&](int i, float corr) -> bool {       // o = o * corr + O_i
-            const int b = i & 1;
-            if (!mbar_wait(&o_full[b], (i >> 1) & 1)) { atomicExch(a.status, ERR_O); return false; }
-            tcgen05_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32_nowait(lane_addr + Cfg::O_COL + b * D + c0, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i2 = 0; i2 < 32; ++i2) o[c0 + i2] = fmaf(o[c0 + i2], corr, __uint_as_float(v[i2]));
-            }
-            tcgen05_fence_before();
-            mbar_arrive(&o_empty[b]);
-            return true;
-        };
 
         for (int j = 0; j < n_blocks; ++j) {
             const int b = j & 1;
@@ -218,56 +210,94 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tmem_ld_32_nowait(lane_addr + Cfg::S_COL + b * TK + 32, sv + 32);
             tmem_ld_wait();
             const int key0 = (kb_first + j) * TK;
-            float m_blk = -INFINITY;
+            if (!(key0 + TK - 1 <= pos_r && key0 >= lo_r)) {        // some keys of the block are hidden from this row
 #pragma unroll
-            for (int c = 0; c < TK; ++c) {
-                const int key = key0 + c;
-                const float s = (key <= pos_r && key >= lo_r) ? __uint_as_float(sv[c]) * a.scale_log2 : -INFINITY;
-                sv[c] = __float_as_uint(s);
-                m_blk = fmaxf(m_blk, s);
+                for (int c = 0; c < TK; ++c) {
+                    const int key = key0 + c;
+                    if (!(key <= pos_r && key >= lo_r)) sv[c] = 0xff800000u;    // -inf: its exponential is 0
+                }
             }
-            const float m_new = fmaxf(m_run, m_blk);
-            const float corr = (m_run == -INFINITY) ? 1.0f : exp2f(m_run - m_new);   // nothing accumulated yet: any factor
-            float l_blk = 0.0f;
+            float m0 = fmax3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
+            float m1 = fmax3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
+#pragma unroll
+            for (int c = 6; c + 3 < TK; c += 4) {
+                m0 = fmax3(m0, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+                m1 = fmax3(m1, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
+            }
+            const float m_blk = fmax3(m0, m1, fmaxf(__uint_as_float(sv[TK - 2]), __uint_as_float(sv[TK - 1]))) * scale;
+            // raise the reference maximum only when this block's maximum is far above it; the rows of a warp
+            // share the decision to touch O, each row uses its own factor
+            const bool raise = m_blk > m_ref + RAISE;               // also true for the row's first visible block
+            if (__any_sync(0xffffffffu, raise)) {
+                const float m_new = fmaxf(m_ref, m_blk);
+                const float factor = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - m_new);   // nothing of value in O yet
+                if (j > 0) {
+                    // O holds the sums of blocks 0 .. j-1 once the PV of block j-1 is complete
+                    if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(a.status, ERR_O); ok = false; break; }
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32_nowait(lane_addr + Cfg::O_COL + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i2 = 0; i2 < 32; ++i2) v[i2] = __float_as_uint(__uint_as_float(v[i2]) * factor);
+                        tmem_st_32(lane_addr + Cfg::O_COL + c0, v);
+                    }
+                    tmem_st_wait();
+                }
+                l_run *= factor;
+                m_ref = m_new;
+            }
+            // exp2(s * scale - m_ref): one fused multiply-add and one ex2 per score; a hidden score is -inf and
+            // gives 0, also for a row that has seen no key yet (its reference stands in as 0)
+            const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            float l0 = 0.0f, l1 = 0.0f;
             uint32_t packed[TK / 2];
 #pragma unroll
             for (int c = 0; c < TK; c += 2) {
-                const float s0 = __uint_as_float(sv[c]), s1 = __uint_as_float(sv[c + 1]);
-                const float e0 = (s0 == -INFINITY) ? 0.0f : exp2f(s0 - m_new);
-                const float e1 = (s1 == -INFINITY) ? 0.0f : exp2f(s1 - m_new);
-                l_blk += e0 + e1;
+                const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c]), scale, neg_m));
+                const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c + 1]), scale, neg_m));
+                l0 += e0;
+                l1 += e1;
                 __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
                 packed[c / 2] = *reinterpret_cast<uint32_t*>(&pr);
             }
-            l_run = l_run * corr + l_blk;
-            m_run = m_new;
-            // P[b] may be overwritten once the MMAs that read it two blocks ago are done
-            if (j >= 2 && !mbar_wait(&p_empty[b], ((j >> 1) - 1) & 1)) { atomicExch(a.status, ERR_P); ok = false; break; }
-            uint8_t* prow = p_s + b * Cfg::P_BYTES + r * 128;
+            l_run += l0 + l1;
+            // P may be overwritten once the MMAs that read the previous block's are done
+            if (j >= 1 && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(a.status, ERR_P); ok = false; break; }
+            uint8_t* prow = p_s + r * 128;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)
                 *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
                     make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
             fence_proxy_async();
             tcgen05_fence_before();
-            mbar_arrive(&p_full[b]);
-            if (j >= 1 && !fold(j - 1, corr_prev)) { ok = false; break; }
-            corr_prev = corr;
+            mbar_arrive(p_full);
         }
-        if (ok) ok = fold(n_blocks - 1, corr_prev);
-        if (ok && r < n_rows) {
+        if (ok && !mbar_wait(pv_done, (n_blocks - 1) & 1)) { atomicExch(a.status, ERR_O); ok = false; }
+        if (ok) {
+            tcgen05_fence_after();
             const float inv = 1.0f / l_run;
             bf16* dst = a.out + ((size_t)(row0 + r) * a.nq + head) * D;
 #pragma unroll
-            for (int c = 0; c < D; c += 8) {
-                uint4 w;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-                w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
-                w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(dst + c) = w;
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32_nowait(lane_addr + Cfg::O_COL + c0, v);      // whole-warp operation: all rows take part
+                tmem_ld_wait();
+                if (r < n_rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[c + 2]) * inv, __uint_as_float(v[c + 3]) * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[c + 4]) * inv, __uint_as_float(v[c + 5]) * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(v[c + 6]) * inv, __uint_as_float(v[c + 7]) * inv);
+                        w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+                        w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+                    }
+                }
             }
         }
     }
@@ -302,6 +332,7 @@ SHARPI_API int sharpi_attention_prefill_tc(const void* q, const void* kv, const 
     if (n_tiles <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || max_blocks <= 0 || nq > 65535 || !status) return SHARPI_BAD_ARGUMENT;
     if (d != 64 && d != 128) return SHARPI_BAD_ARGUMENT;
+    if (!(scale > 0.0f)) return SHARPI_BAD_ARGUMENT;
     if (page_size < 64 || (page_size & (page_size - 1)) != 0) return SHARPI_BAD_ARGUMENT;
     if (mask_kind != SHARPI_MASK_FULL && mask_span <= 0) return SHARPI_BAD_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv) | reinterpret_cast<uintptr_t>(out)) & 15)
