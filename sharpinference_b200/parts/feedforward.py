@@ -29,12 +29,24 @@ class DenseSwiGLU(FeedForward):
             raise ValueError(f"fused gate|up weight has {gate_up.out_features} rows, expected 2 * {down.in_features}")
         self.gate_up, self.down, self.act_dtype = gate_up, down, act_dtype
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h):
             act = ops.tc_dense(h, self.gate_up.weight, swiglu=True)       # SwiGLU in the product's epilogue
         else:
             act = ops.swiglu(self.gate_up(h), self.act_dtype)
-        return self.down(act)
+        return self.down(act, out=out)
+
+
+_side_streams: dict = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """The second stream of a device, on which the shared expert runs beside the routed ones."""
+    key = torch.device(device).index
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 @register_part("feed_forward", "moe_sigmoid_top1")
@@ -64,22 +76,35 @@ class MoESigmoidTop1(FeedForward):
         T = h.shape[0]
         if h32 is None:
             h32 = h.to(torch.float32)
+        # The shared expert and the routed ones meet only where the routed outputs are added: the shared
+        # expert runs on a second stream beside routing, sorting and the routed gate|up product (short
+        # kernels bound by latency beside long ones bound by memory), and the streams join before the
+        # routed down product adds into y.  Inside a graph capture this becomes a fork and a join.
+        main = side = None
+        if self.shared is not None:
+            y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+            main, side = torch.cuda.current_stream(h.device), _side_stream(h.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self.shared.forward(ctx, h, out=y)
+        else:
+            y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
         expert, weight, _ = ops.router_top1(h32, self.router)
         offsets, sorted_rows = ops.moe_sort(expert, self.num_experts)
         if "router_choices" in ctx.extras:          # tracing: which expert every row went to
             ctx.extras["router_choices"].append(expert)
-        if self.shared is not None:
-            y = self.shared.forward(ctx, h)
-        else:
-            y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
         if self._tensor_core and h.dtype == torch.bfloat16:
             h_sorted = ops.gather_rows_bf16(h, sorted_rows)
             act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                       row_scale=weight, scale_rows=sorted_rows)
+            if side is not None:
+                main.wait_stream(side)
             ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
                                 out_rows=sorted_rows, accumulate=True)
             return y
         gu = self.experts_gate_up(h, offsets, rows=T, a_rows=sorted_rows)          # sorted order
         act = ops.swiglu(gu, self.act_dtype, row_scale=weight, scale_rows=sorted_rows)
+        if side is not None:
+            main.wait_stream(side)
         self.experts_down(act, offsets, rows=T, out_rows=sorted_rows, out=y, accumulate=True)
         return y
