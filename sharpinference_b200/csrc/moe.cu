@@ -14,7 +14,6 @@ enum RouterGate : int {
     ROUTER_GATE_SIGMOID = 0,
 };
 
-constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_SEGMENTS = 8;
 
 // The one summation order of a router logit, whatever kernel computes it: the width is cut into
@@ -63,84 +62,103 @@ __device__ __forceinline__ void router_pick(const float* r, int E, int* expert_i
     *expert_weight = best_p;
 }
 
-// Many tokens: one block serves TPB consecutive tokens; a warp reads a router row once and forms the
-// logits of all the block's tokens with it.
-template <int TPB>
-__global__ void router_top1_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
-                                   int* __restrict__ expert_id, float* __restrict__ expert_weight,
-                                   float* __restrict__ logits_out) {
+// Many tokens: one block serves TPB consecutive tokens and its eight warps take one segment each, so a
+// warp reads its slice of the activations from global memory (nobody else needs it) and its slice of a
+// router row once for all the block's tokens; the experts go by in passes of EPP, TPB x EPP sums per lane.
+// The segment sums meet in shared memory and are added in ascending order.
+template <int TPB, int EPP>
+__global__ void __launch_bounds__(ROUTER_SEGMENTS * 32)
+router_top1_tiled_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
+                         int* __restrict__ expert_id, float* __restrict__ expert_weight,
+                         float* __restrict__ logits_out) {
     extern __shared__ __align__(16) float smem[];
-    float* h_s = smem;                // [TPB][H]
-    float* r_s = smem + TPB * H;      // [TPB][E]
+    float* seg_s = smem;                                  // [segments][TPB][E]
+    float* r_s = smem + ROUTER_SEGMENTS * TPB * E;        // [TPB][E]
     const int t0 = blockIdx.x * TPB;
     const int n_tok = min(TPB, T - t0);
-    for (int i = threadIdx.x; i < TPB * H; i += ROUTER_THREADS) {
-        const int tt = i / H;
-        h_s[i] = (tt < n_tok) ? h[(size_t)t0 * H + i] : 0.0f;
-    }
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
+    const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(h) & 15) == 0);
     const int seg = router_segment_len(H);
-    for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
-        const float* w = wr + (size_t)e * H;
-        float total[TPB];
+    const int begin = min(H, warp * seg), end = min(H, begin + seg);
+    const float* hb = h + (size_t)t0 * H;
+    for (int e0 = 0; e0 < E; e0 += EPP) {
+        float acc[TPB][EPP];
 #pragma unroll
-        for (int tt = 0; tt < TPB; ++tt) total[tt] = 0.0f;
-        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) {
-            const int begin = min(H, sgm * seg), end = min(H, begin + seg);
-            // the same operations per token as router_segment_dot, with one read of the router row for all
-            float acc[TPB];
+        for (int tt = 0; tt < TPB; ++tt)
 #pragma unroll
-            for (int tt = 0; tt < TPB; ++tt) acc[tt] = 0.0f;
-            if (vec) {
-                const float4* w4 = reinterpret_cast<const float4*>(w + begin);
-                const int n4 = (end - begin) >> 2;
-#pragma unroll 2
-                for (int i = lane; i < n4; i += 32) {
-                    const float4 b = __ldg(w4 + i);
+            for (int ee = 0; ee < EPP; ++ee) acc[tt][ee] = 0.0f;
+        if (vec) {
+            const int n4 = (end - begin) >> 2;
+            for (int i = lane; i < n4; i += 32) {
+                float4 a[TPB];
 #pragma unroll
-                    for (int tt = 0; tt < TPB; ++tt) {
-                        const float4 a = reinterpret_cast<const float4*>(h_s + tt * H + begin)[i];
-                        acc[tt] = fmaf(a.x, b.x, acc[tt]);
-                        acc[tt] = fmaf(a.y, b.y, acc[tt]);
-                        acc[tt] = fmaf(a.z, b.z, acc[tt]);
-                        acc[tt] = fmaf(a.w, b.w, acc[tt]);
+                for (int tt = 0; tt < TPB; ++tt)
+                    a[tt] = (tt < n_tok) ? reinterpret_cast<const float4*>(hb + (size_t)tt * H + begin)[i]
+                                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int ee = 0; ee < EPP; ++ee) {
+                    if (e0 + ee < E) {
+                        const float4 b = __ldg(reinterpret_cast<const float4*>(wr + (size_t)(e0 + ee) * H + begin) + i);
+#pragma unroll
+                        for (int tt = 0; tt < TPB; ++tt) {
+                            acc[tt][ee] = fmaf(a[tt].x, b.x, acc[tt][ee]);
+                            acc[tt][ee] = fmaf(a[tt].y, b.y, acc[tt][ee]);
+                            acc[tt][ee] = fmaf(a[tt].z, b.z, acc[tt][ee]);
+                            acc[tt][ee] = fmaf(a[tt].w, b.w, acc[tt][ee]);
+                        }
                     }
                 }
-            } else {
-                for (int i = begin + lane; i < end; i += 32) {
-                    const float b = w[i];
+            }
+        } else {
+            for (int i = begin + lane; i < end; i += 32) {
+                float a[TPB];
 #pragma unroll
-                    for (int tt = 0; tt < TPB; ++tt) acc[tt] = fmaf(h_s[tt * H + i], b, acc[tt]);
+                for (int tt = 0; tt < TPB; ++tt) a[tt] = (tt < n_tok) ? hb[(size_t)tt * H + i] : 0.0f;
+#pragma unroll
+                for (int ee = 0; ee < EPP; ++ee) {
+                    if (e0 + ee < E) {
+                        const float b = wr[(size_t)(e0 + ee) * H + i];
+#pragma unroll
+                        for (int tt = 0; tt < TPB; ++tt) acc[tt][ee] = fmaf(a[tt], b, acc[tt][ee]);
+                    }
                 }
             }
-#pragma unroll
-            for (int tt = 0; tt < TPB; ++tt) total[tt] += warp_sum(acc[tt]);
         }
-        if (lane == 0)
 #pragma unroll
-            for (int tt = 0; tt < TPB; ++tt) r_s[tt * E + e] = total[tt];
+        for (int tt = 0; tt < TPB; ++tt)
+#pragma unroll
+            for (int ee = 0; ee < EPP; ++ee) {
+                const float part = warp_sum(acc[tt][ee]);
+                if (lane == 0 && e0 + ee < E) seg_s[(warp * TPB + tt) * E + e0 + ee] = part;
+            }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < TPB * E; i += ROUTER_SEGMENTS * 32) {
+        float total = 0.0f;
+#pragma unroll
+        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) total += seg_s[sgm * TPB * E + i];
+        r_s[i] = total;
     }
     __syncthreads();
     if (logits_out)
-        for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_THREADS) logits_out[(size_t)t0 * E + i] = r_s[i];
+        for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_SEGMENTS * 32) logits_out[(size_t)t0 * E + i] = r_s[i];
     if (threadIdx.x < n_tok)
         router_pick(r_s + threadIdx.x * E, E, expert_id + t0 + threadIdx.x, expert_weight + t0 + threadIdx.x);
 }
 
-template <int TPB>
+template <int TPB, int EPP>
 static int launch_router(const float* h, const float* wr, int T, int H, int E, int* expert_id, float* expert_weight,
                          float* logits_out, cudaStream_t stream) {
-    const size_t smem = (size_t)TPB * (H + E) * sizeof(float);
+    const size_t smem = (size_t)(ROUTER_SEGMENTS + 1) * TPB * E * sizeof(float);
     if (smem > 200 * 1024) return SHARPI_BAD_ARGUMENT;
     if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(router_top1_kernel<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(router_top1_tiled_kernel<TPB, EPP>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
     }
-    router_top1_kernel<TPB><<<(T + TPB - 1) / TPB, ROUTER_THREADS, smem, stream>>>(h, wr, T, H, E, expert_id,
-                                                                                   expert_weight, logits_out);
+    router_top1_tiled_kernel<TPB, EPP><<<(T + TPB - 1) / TPB, ROUTER_SEGMENTS * 32, smem, stream>>>(
+        h, wr, T, H, E, expert_id, expert_weight, logits_out);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -204,10 +222,10 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
         SHARPI_CHECK_LAUNCH();
         return SHARPI_OK;
     }
-    // many tokens: four share a block and a read of the router; else one block each
-    if (T >= 256 && (size_t)4 * (H + E) * sizeof(float) <= 200 * 1024)
-        return launch_router<4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
-    return launch_router<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+    // many tokens: eight share a block and its reads of the router rows; fewer: two, for more blocks
+    if (T >= 1024 && (size_t)(ROUTER_SEGMENTS + 1) * 8 * E * sizeof(float) <= 200 * 1024)
+        return launch_router<8, 4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+    return launch_router<2, 8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -218,20 +236,30 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
 // ---------------------------------------------------------------------------------------
 constexpr int SORT_THREADS = 1024;
 constexpr int SORT_MAX_E = 1024;
+constexpr int SORT_CHUNK = 4096;      // expert ids staged in shared memory at a time
 
-__global__ void moe_sort_kernel(const int* __restrict__ expert_id, int T, int E, int* __restrict__ offsets,
-                                int* __restrict__ sorted_rows) {
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_kernel(const int* __restrict__ expert_id, int T, int E, int* __restrict__ offsets,
+                int* __restrict__ sorted_rows) {
     __shared__ int cnt_s[SORT_MAX_E + 1];
+    __shared__ int ids_s[SORT_CHUNK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned lt = (1u << lane) - 1u;
-    for (int e = warp; e < E; e += SORT_THREADS / 32) {
-        int n = 0;
-        for (int base = 0; base < T; base += 32) {
-            const int t = base + lane;
-            const bool mine = (t < T) && (expert_id[t] == e);
-            n += __popc(__ballot_sync(0xffffffffu, mine));
+    for (int e = threadIdx.x; e <= E; e += SORT_THREADS) cnt_s[e] = 0;
+    for (int c0 = 0; c0 < T; c0 += SORT_CHUNK) {
+        const int n_c = min(SORT_CHUNK, T - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_c; i += SORT_THREADS) ids_s[i] = expert_id[c0 + i];
+        __syncthreads();
+        for (int e = warp; e < E; e += SORT_THREADS / 32) {
+            int n = 0;
+            for (int base = 0; base < n_c; base += 32) {
+                const int t = base + lane;
+                const bool mine = (t < n_c) && (ids_s[t] == e);
+                n += __popc(__ballot_sync(0xffffffffu, mine));
+            }
+            if (lane == 0) cnt_s[e] += n;         // expert e belongs to this warp alone
         }
-        if (lane == 0) cnt_s[e] = n;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -245,15 +273,21 @@ __global__ void moe_sort_kernel(const int* __restrict__ expert_id, int T, int E,
         cnt_s[E] = run;
         offsets[E] = run;
     }
-    __syncthreads();
-    for (int e = warp; e < E; e += SORT_THREADS / 32) {
-        int cursor = cnt_s[e];
-        for (int base = 0; base < T; base += 32) {
-            const int t = base + lane;
-            const bool mine = (t < T) && (expert_id[t] == e);
-            const unsigned mask = __ballot_sync(0xffffffffu, mine);
-            if (mine) sorted_rows[cursor + __popc(mask & lt)] = t;
-            cursor += __popc(mask);
+    for (int c0 = 0; c0 < T; c0 += SORT_CHUNK) {
+        const int n_c = min(SORT_CHUNK, T - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_c; i += SORT_THREADS) ids_s[i] = expert_id[c0 + i];
+        __syncthreads();
+        for (int e = warp; e < E; e += SORT_THREADS / 32) {
+            int cursor = cnt_s[e];
+            for (int base = 0; base < n_c; base += 32) {
+                const int t = base + lane;
+                const bool mine = (t < n_c) && (ids_s[t] == e);
+                const unsigned mask = __ballot_sync(0xffffffffu, mine);
+                if (mine) sorted_rows[cursor + __popc(mask & lt)] = c0 + t;
+                cursor += __popc(mask);
+            }
+            if (lane == 0) cnt_s[e] = cursor;
         }
     }
 }

@@ -10,7 +10,10 @@
 // not in the reference: q *= 1 + attn_scale * ln(1 + floor((pos + 1) / floor_scale)).
 //
 // Angles (pos * inv_freq), sin/cos, the norm's mean of squares and the temperature factor
-// are fp32.  One warp owns one head of one token, so no result depends on the batch.
+// are fp32.  One warp owns one head of one token, so no result depends on the batch.  Head sizes
+// that are multiples of four with interleaved pairs (or no rotation) take the kernel in which a lane
+// owns whole 16-byte pieces, two pairs each; the others take the element-wise one.  Which of the two
+// runs depends on the head size and the pairing alone.
 #include "common.cuh"
 
 enum RopePairing : int {
@@ -121,6 +124,92 @@ __global__ void qkv_post_kernel(QkvPostArgs a) {
     }
 }
 
+template <typename TO>
+__device__ __forceinline__ void store4(TO* dst, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float4 v) {
+    *reinterpret_cast<float4*>(dst) = v;
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&lo);
+    w.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = w;
+}
+
+// d % 4 == 0, pairs (2j, 2j+1) or no rotation: lane l owns the four-element pieces l, l + 32, ...
+template <typename TO>
+__global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots = a.nq + 2 * a.nkv;
+    const long long work = (long long)blockIdx.x * warps_per_block + warp;
+    if (work >= (long long)a.T * slots) return;
+    const int t = (int)(work / slots);
+    const int slot = (int)(work % slots);
+    const int d = a.d, n4 = d >> 2;
+    const float4* __restrict__ src = reinterpret_cast<const float4*>(a.qkv + (size_t)t * slots * d + (size_t)slot * d);
+    constexpr int MAX_PIECES = 4;        // head sizes up to 512
+    float4 x[MAX_PIECES];
+#pragma unroll
+    for (int r = 0; r < MAX_PIECES; ++r) {
+        const int i = lane + 32 * r;
+        x[r] = (i < n4) ? __ldg(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const int pos = a.positions[t];
+    const bool is_q = slot < a.nq;
+    const bool is_k = !is_q && slot < a.nq + a.nkv;
+
+    TO* dst;
+    if (is_q) {
+        dst = (TO*)a.q_out + ((size_t)t * a.nq + slot) * d;
+    } else {
+        if (!a.write_kv) return;
+        const int head = is_k ? slot - a.nq : slot - a.nq - a.nkv;
+        const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
+        if (page < 0) return;  // the host checks before the launch that every written position has a page
+        const size_t plane = (size_t)a.nkv * a.page_size * d;
+        dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
+              ((size_t)head * a.page_size + (pos % a.page_size)) * d;
+    }
+    float scale = 1.0f;
+    if (is_q || is_k) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < MAX_PIECES; ++r) {
+            const int i = lane + 32 * r;
+            if (i < n4) {
+                if (a.pairing != ROPE_NONE && a.inv_freq) {
+                    const float2 f = __ldg(reinterpret_cast<const float2*>(a.inv_freq) + i);   // pairs 2i, 2i + 1
+                    float sn, cs;
+                    sincosf((float)pos * f.x, &sn, &cs);
+                    const float r0 = x[r].x * cs - x[r].y * sn, r1 = x[r].x * sn + x[r].y * cs;
+                    sincosf((float)pos * f.y, &sn, &cs);
+                    const float r2 = x[r].z * cs - x[r].w * sn, r3 = x[r].z * sn + x[r].w * cs;
+                    x[r] = make_float4(r0, r1, r2, r3);
+                }
+                ss += x[r].x * x[r].x + x[r].y * x[r].y;
+                ss += x[r].z * x[r].z + x[r].w * x[r].w;
+            }
+        }
+        if (a.l2_eps >= 0.0f) {
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)d + a.l2_eps);
+        }
+        if (is_q && a.temp_floor_scale > 0.0f) {
+            const float steps = floorf(((float)pos + 1.0f) / a.temp_floor_scale);
+            scale *= 1.0f + a.temp_attn_scale * log1pf(steps);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < MAX_PIECES; ++r) {
+        const int i = lane + 32 * r;
+        if (i < n4) store4<TO>(dst + 4 * i, make_float4(x[r].x * scale, x[r].y * scale, x[r].z * scale, x[r].w * scale));
+    }
+}
+
 SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int* row_req, const int* block_table,
                                const float* inv_freq, void* q_out, void* kv_base, int out_dtype, int T, int nq,
                                int nkv, int d, int max_blocks, int page_size, int pairing, float l2_eps,
@@ -136,8 +225,22 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
     a.T = T; a.nq = nq; a.nkv = nkv; a.d = d; a.max_blocks = max_blocks; a.page_size = page_size;
     a.pairing = inv_freq ? pairing : ROPE_NONE; a.l2_eps = l2_eps;
     a.temp_attn_scale = temp_attn_scale; a.temp_floor_scale = temp_floor_scale; a.write_kv = write_kv;
-    const int warps = 4;
+    if (out_dtype != SHARPI_F32 && out_dtype != SHARPI_BF16) return SHARPI_BAD_ARGUMENT;
     const long long work = (long long)T * (nq + 2 * nkv);
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                           reinterpret_cast<uintptr_t>(kv_base) | reinterpret_cast<uintptr_t>(inv_freq);
+    if (d % 4 == 0 && a.pairing != ROPE_HALVES && (ptrs & 15) == 0) {
+        const int warps = 8;
+        const long long blocks = (work + warps - 1) / warps;
+        if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
+        if (out_dtype == SHARPI_F32)
+            qkv_post_vec_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
+        else
+            qkv_post_vec_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
+        SHARPI_CHECK_LAUNCH();
+        return SHARPI_OK;
+    }
+    const int warps = 4;
     const long long blocks = (work + warps - 1) / warps;
     if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
     if (out_dtype == SHARPI_F32)

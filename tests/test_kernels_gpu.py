@@ -90,7 +90,7 @@ def rope_ref(x, pos, inv_freq, pairing):
     return out
 
 
-@pytest.mark.parametrize("nq,nkv,d", [(6, 2, 48), (5, 5, 16), (8, 1, 128), (2, 1, 272)])
+@pytest.mark.parametrize("nq,nkv,d", [(6, 2, 48), (5, 5, 16), (8, 1, 128), (2, 1, 272), (3, 1, 512), (2, 2, 6), (1, 1, 500)])
 @pytest.mark.parametrize("variant", ["rope+l2", "halves", "nope+temp", "bare"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_qkv_post(ops, nq, nkv, d, variant, dtype):
@@ -292,7 +292,8 @@ def test_gemm_nt_grouped_gather_scatter_accumulate(ops, dtype):
 
 
 # ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("T,H,E", [(1, 77, 5), (50, 5120, 16), (9, 5120, 128), (3, 20000, 7)])
+@pytest.mark.parametrize("T,H,E", [(1, 77, 5), (50, 5120, 16), (9, 5120, 128), (3, 20000, 7), (1100, 333, 6),
+                                   (1029, 1280, 19), (40, 24, 3)])
 def test_router_top1(ops, T, H, E):
     h, wr = rnd(T, H, seed=9), rnd(E, H, scale=0.05, seed=10)
     expert, weight, logits = ops.router_top1(h, wr, want_logits=True)
@@ -311,7 +312,7 @@ def test_router_first_of_equal_experts_wins(ops):
     assert expert.tolist() == [2, 2] and float(weight[0]) == pytest.approx(1 / (1 + math.exp(-4.0)))
 
 
-@pytest.mark.parametrize("T,E", [(0, 4), (1, 1), (33, 4), (1000, 16), (5000, 128), (77, 1000)])
+@pytest.mark.parametrize("T,E", [(0, 4), (1, 1), (33, 4), (1000, 16), (5000, 128), (77, 1000), (4096, 3), (9001, 40)])
 def test_moe_sort_is_a_stable_counting_sort(ops, T, E):
     ids = torch.randint(0, E, (T,), generator=torch.Generator().manual_seed(T + E)).to(torch.int32).to(DEV)
     offsets, rows = ops.moe_sort(ids, E)
@@ -597,14 +598,18 @@ def test_fast_attention_finds_one_far_key_and_respects_edges(ops):
 
 
 def test_router_rows_do_not_depend_on_the_batch(ops):
-    """A token's router logits are the same bits alone, in a small batch and in a large one (where four
-    tokens share a block)."""
-    h, wr = rnd(600, 1000, seed=21), rnd(16, 1000, scale=0.05, seed=22)
-    e_big, w_big, l_big = ops.router_top1(h, wr, want_logits=True)
-    e_small, w_small, l_small = ops.router_top1(h[:7].contiguous(), wr, want_logits=True)
-    e_one, w_one, l_one = ops.router_top1(h[301:302].contiguous(), wr, want_logits=True)
-    assert torch.equal(l_big[:7], l_small) and torch.equal(l_big[301:302], l_one)
-    assert torch.equal(e_big[:7], e_small) and torch.equal(w_big[301:302], w_one)
+    """A token's router logits are the same bits alone, in a small batch (a block per token and expert), in
+    a middle one (two tokens share a block) and in a large one (eight do), for widths that are and are not
+    multiples of four."""
+    for H in (1000, 1001):
+        h, wr = rnd(1500, H, seed=21), rnd(16, H, scale=0.05, seed=22)
+        e_big, w_big, l_big = ops.router_top1(h, wr, want_logits=True)
+        e_mid, w_mid, l_mid = ops.router_top1(h[3:603].contiguous(), wr, want_logits=True)
+        e_small, w_small, l_small = ops.router_top1(h[:7].contiguous(), wr, want_logits=True)
+        e_one, w_one, l_one = ops.router_top1(h[301:302].contiguous(), wr, want_logits=True)
+        assert torch.equal(l_big[:7], l_small) and torch.equal(l_big[301:302], l_one)
+        assert torch.equal(l_big[3:603], l_mid) and torch.equal(e_big[3:603], e_mid) and torch.equal(w_big[3:603], w_mid)
+        assert torch.equal(e_big[:7], e_small) and torch.equal(w_big[301:302], w_one)
 
 
 @pytest.mark.parametrize("nq,nkv,d,ps", [(2, 1, 64, 64), (5, 1, 128, 64), (8, 2, 128, 128), (6, 3, 64, 256)])
