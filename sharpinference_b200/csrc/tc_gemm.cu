@@ -54,9 +54,14 @@ struct TcGemmParams {
     int k_split;
 };
 
-template <int MODE, int NT>
+// WT: weight tiles of 128 rows that share one activation tile.  MODE_SWIGLU always has two (gate and up);
+// MODE_STORE takes two adjacent ones for large activation tiles, where the activations would otherwise be
+// half of what the CTA holds in flight and the weights, which come from DRAM, the other half only.
+template <int MODE, int NT, int WT>
 struct TcConfig {
-    static constexpr int W_TILES = (MODE == MODE_SWIGLU) ? 2 : 1;
+    static_assert(WT == 1 || WT == 2, "one or two weight tiles");
+    static_assert(MODE != MODE_SWIGLU || WT == 2, "gate and up are two tiles");
+    static constexpr int W_TILES = WT;
     static constexpr int W_BYTES = TC_BM * TC_BK * 2;
     static constexpr int A_BYTES = NT * TC_BK * 2;
     static constexpr int STAGE_BYTES = W_TILES * W_BYTES + A_BYTES;
@@ -70,11 +75,11 @@ struct TcConfig {
     static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
 };
 
-template <int MODE, int NT>
+template <int MODE, int NT, int WT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                        const TcGemmParams p) {
-    using Cfg = TcConfig<MODE, NT>;
+    using Cfg = TcConfig<MODE, NT, WT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -109,8 +114,11 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int expert = tile_info[0];
     if (expert < 0) return;                       // uniform: nothing allocated yet
     const int row0 = tile_info[1], row_end = tile_info[2];
-    const int n0 = blockIdx.x * TC_BM;            // MODE_SWIGLU: index into [0, I)
+    // first weight row: MODE_SWIGLU: index into [0, I), the second tile is the matching up rows;
+    // MODE_STORE: the second tile, if there is one, is the next 128 rows
+    const int n0 = blockIdx.x * TC_BM * (MODE == MODE_SWIGLU ? 1 : WT);
     const int I = p.N / 2;                        // MODE_SWIGLU only
+    const int n1 = (MODE == MODE_SWIGLU) ? I + n0 : n0 + TC_BM;
     const int k_blocks_all = (p.K + TC_BK - 1) / TC_BK;
     const int kb_per = (k_blocks_all + p.k_split - 1) / p.k_split;
     const int kb_begin = blockIdx.z * kb_per;
@@ -140,8 +148,7 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
                 const int kx = (kb_begin + kb) * TC_BK;
                 tma_load_3d(stage, &map_w, &full_bar[s], kx, n0, expert);
-                if (MODE == MODE_SWIGLU)
-                    tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kx, I + n0, expert);
+                if (WT == 2) tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kx, n1, expert);
                 tma_load_2d(stage + Cfg::W_TILES * Cfg::W_BYTES, &map_a, &full_bar[s], kx, row0);
                 issued = kb + 1;
             }
@@ -168,7 +175,7 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     const uint32_t acc = (kb | k) != 0;
                     const uint64_t db = smem_desc_k_sw128(a_tile, k * 32);
                     mma_bf16_ss(tmem_base, smem_desc_k_sw128(stage, k * 32), db, idesc, acc);
-                    if (MODE == MODE_SWIGLU)
+                    if (WT == 2)
                         mma_bf16_ss(tmem_base + NT, smem_desc_k_sw128(stage + Cfg::W_BYTES, k * 32), db, idesc, acc);
                 }
                 mma_commit(&empty_bar[s]);      // the stage is free when these MMAs have read it
@@ -193,14 +200,16 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (p.k_split > 1) {
                     float* part = p.partial + (size_t)blockIdx.z * p.rows * p.N;
                     float u[16];
-                    if (MODE == MODE_SWIGLU) tmem_ld_16(lane_addr + NT + c0, u);
+                    if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
+                    const int nb = n1 - n0 + n;            // the row of the second tile
                     const bool n_ok = MODE == MODE_SWIGLU ? n < I : n < p.N;
+                    const bool nb_ok = WT == 2 && (MODE == MODE_SWIGLU ? n < I : nb < p.N);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int r = row0 + c0 + j;
-                        if (c0 + j < valid && n_ok) {
-                            part[(size_t)r * p.N + n] = (k_blocks > 0) ? g[j] : 0.0f;
-                            if (MODE == MODE_SWIGLU) part[(size_t)r * p.N + I + n] = (k_blocks > 0) ? u[j] : 0.0f;
+                        if (c0 + j < valid) {
+                            if (n_ok) part[(size_t)r * p.N + n] = (k_blocks > 0) ? g[j] : 0.0f;
+                            if (nb_ok) part[(size_t)r * p.N + nb] = (k_blocks > 0) ? u[j] : 0.0f;
                         }
                     }
                 } else if (MODE == MODE_SWIGLU) {
@@ -208,24 +217,42 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     tmem_ld_16(lane_addr + NT + c0, u);
                     if (n < I) {
                         bf16* act = reinterpret_cast<bf16*>(p.out);
+                        float sc[16];                    // all the row scales first: the loads do not wait for stores
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int r = row0 + c0 + j;
+                            sc[j] = (p.row_scale && c0 + j < valid) ? __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r))
+                                                                     : 1.0f;
+                        }
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int r = row0 + c0 + j;
                             if (c0 + j < valid) {
-                                const float s = p.row_scale ? p.row_scale[p.scale_rows ? p.scale_rows[r] : r] : 1.0f;
-                                const float gv = g[j] * s, uv = u[j] * s;
+                                const float gv = g[j] * sc[j], uv = u[j] * sc[j];
                                 act[(size_t)r * I + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
                             }
                         }
                     }
-                } else if (n < p.N) {
+                } else {
                     float* C = reinterpret_cast<float*>(p.out);
+                    float u[16];
+                    if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
+                    const bool n_ok = n < p.N, nb_ok = WT == 2 && n + TC_BM < p.N;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int r = row0 + c0 + j;
                         if (c0 + j < valid) {
+                            // Adding in: every output element gets exactly one addend from this launch (a row
+                            // belongs to one group), so a reduction that returns nothing gives the same sum
+                            // as load, add, store, without a round trip to memory per element.
                             float* dst = C + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
-                            *dst = p.accumulate ? *dst + g[j] : g[j];
+                            if (p.accumulate) {
+                                if (n_ok) atomicAdd(dst, g[j]);
+                                if (nb_ok) atomicAdd(dst + TC_BM, u[j]);
+                            } else {
+                                if (n_ok) *dst = g[j];
+                                if (nb_ok) dst[TC_BM] = u[j];
+                            }
                         }
                     }
                 }
@@ -243,19 +270,19 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-template <int MODE, int NT>
+template <int MODE, int NT, int WT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmParams& p, int n_tiles, int row_tiles,
                   cudaStream_t stream) {
-    using Cfg = TcConfig<MODE, NT>;
+    using Cfg = TcConfig<MODE, NT, WT>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(tc_grouped_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(tc_grouped_gemm_kernel<MODE, NT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::SMEM_BYTES) != cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
     dim3 grid(n_tiles, row_tiles, p.k_split);
-    tc_grouped_gemm_kernel<MODE, NT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, p);
+    tc_grouped_gemm_kernel<MODE, NT, WT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, p);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -305,15 +332,22 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     if (k_split < 1 || k_split > 16 || (k_split > 1 && !partial)) return SHARPI_BAD_ARGUMENT;
     p.partial = partial; p.k_split = k_split;
     const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
-    const int n_tiles = (n_out + TC_BM - 1) / TC_BM;
+    // two weight tiles per activation tile pay from about 2048 rows on (measured at 16 experts: 281 vs 315 us
+    // at 2048 rows, 658 vs 719 us at 8192; below that the larger number of CTAs of single tiles wins)
+    const int store_wt = (mode == MODE_STORE && row_tile >= 128 && rows >= 2048) ? 2 : 1;
+    const int n_tiles = (n_out + TC_BM * store_wt - 1) / (TC_BM * store_wt);
     // tiles = sum over experts of ceil(rows_e / row_tile) <= (experts with rows) + rows / row_tile, and at
     // most min(rows, E) experts have rows: no more CTAs than that are launched (empty ones cost a slot each)
     const long long row_tiles = rows / row_tile + (rows < E ? rows : E);
     if (row_tiles > 65535) return SHARPI_BAD_ARGUMENT;
     int rc = SHARPI_BAD_ARGUMENT;
-#define TC_CASE(M, T) if (mode == M && row_tile == T) rc = launch<M, T>(mw, ma, p, n_tiles, (int)row_tiles, stream);
-    TC_CASE(MODE_STORE, 16) TC_CASE(MODE_STORE, 32) TC_CASE(MODE_STORE, 64) TC_CASE(MODE_STORE, 128) TC_CASE(MODE_STORE, 256)
-    TC_CASE(MODE_SWIGLU, 16) TC_CASE(MODE_SWIGLU, 32) TC_CASE(MODE_SWIGLU, 64) TC_CASE(MODE_SWIGLU, 128) TC_CASE(MODE_SWIGLU, 256)
+#define TC_CASE(M, T, W) \
+    if (mode == M && row_tile == T && (M == MODE_SWIGLU || store_wt == W)) \
+        rc = launch<M, T, W>(mw, ma, p, n_tiles, (int)row_tiles, stream);
+    TC_CASE(MODE_STORE, 16, 1) TC_CASE(MODE_STORE, 32, 1) TC_CASE(MODE_STORE, 64, 1) TC_CASE(MODE_STORE, 128, 1)
+    TC_CASE(MODE_STORE, 128, 2) TC_CASE(MODE_STORE, 256, 1) TC_CASE(MODE_STORE, 256, 2)
+    TC_CASE(MODE_SWIGLU, 16, 2) TC_CASE(MODE_SWIGLU, 32, 2) TC_CASE(MODE_SWIGLU, 64, 2) TC_CASE(MODE_SWIGLU, 128, 2)
+    TC_CASE(MODE_SWIGLU, 256, 2)
 #undef TC_CASE
     if (rc != SHARPI_OK || k_split == 1) return rc;
     dim3 rgrid(rows, (n_out + 255) / 256);

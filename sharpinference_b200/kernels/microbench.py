@@ -57,7 +57,11 @@ def tc_gemm(ns) -> None:
     g = torch.Generator(device=DEV).manual_seed(0)
     used = min(E, ns.active) if ns.active else E
     counts = torch.zeros(E, dtype=torch.int64)
-    counts[:used] = T // used
+    if ns.skew > 0:
+        share = torch.tensor([(1.0 - ns.skew) ** e for e in range(used)], dtype=torch.float64)
+        counts[:used] = torch.floor(share / share.sum() * T).to(torch.int64)
+    else:
+        counts[:used] = T // used
     counts[: T - int(counts.sum())] += 1
     offsets = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(counts, 0)]).to(torch.int32).to(DEV)
     if ns.mode == "gate_up":
@@ -134,6 +138,8 @@ def main(argv=None) -> int:
     p.add_argument("--inter", type=int, default=8192)
     p.add_argument("--row-tile", type=int, default=None)
     p.add_argument("--k-split", type=int, default=None)
+    p.add_argument("--skew", type=float, default=0.0,
+                   help="0: equal groups; else expert e gets rows in proportion to (1 - skew)^e")
     p.set_defaults(fn=tc_gemm)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)

@@ -396,7 +396,8 @@ def grouped_case(T, E, K, seed, empty=()):
 
 @pytest.mark.parametrize("T,E,N,K,row_tile", [(8, 4, 256, 128, 16), (5, 3, 200, 72, 16), (64, 16, 384, 512, 16),
                                               (300, 5, 136, 264, 64), (700, 3, 520, 128, 128), (70, 2, 128, 64, 32),
-                                              (1500, 4, 256, 192, 256)])
+                                              (1500, 4, 256, 192, 256), (2100, 3, 520, 128, 128),
+                                              (2500, 5, 136, 72, 128), (2048, 2, 256, 64, 256)])
 def test_tc_grouped_gemm_store(ops, T, E, N, K, row_tile):
     expert, order, offsets, a = grouped_case(T, E, K, seed=T + N, empty=(1,) if E > 2 else ())
     w = rnd(E, N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
@@ -449,6 +450,15 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
                               mode=ops.TC_MODE_STORE, row_tile=16, k_split=1)
     ops.check_status(DEV)
     assert torch.equal(one[0], big[100 + 9])
+    # from 2048 rows on a CTA takes two weight tiles beside one tile of rows: the same bits again
+    a_many = torch.cat([a, rnd(2000, K, dtype=torch.bfloat16, seed=9)])
+    expert_many = torch.arange(2400) % E
+    order_many = torch.argsort(expert_many, stable=True)
+    offsets_many = torch.tensor([0, 600, 1200, 1800, 2400], dtype=torch.int32, device=DEV)
+    many = ops.tc_grouped_gemm(a_many[order_many.to(DEV)].contiguous(), w, offsets_many, mode=ops.TC_MODE_STORE,
+                               row_tile=128)
+    ops.check_status(DEV)
+    assert torch.equal(one[0], many[600 + 9])
     # with K cut over several CTAs the parts are added in another order: equal to rounding, not to the bit
     cut = ops.tc_grouped_gemm(a[t:t + 1].contiguous(), w, torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device=DEV),
                               mode=ops.TC_MODE_STORE, row_tile=16, k_split=3)
