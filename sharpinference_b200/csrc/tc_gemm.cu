@@ -91,24 +91,47 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- which tile is this CTA's ----------------------------------------------------------
-    if (threadIdx.x == 0) {
-        int tile = blockIdx.y, e = 0, start = 0, end = 0;
-        for (; e < p.E; ++e) {
-            start = p.group_offsets[e];
-            end = p.group_offsets[e + 1];
+    // Warp 0 looks the tile up: lane l reads the bounds of group e0 + l, the warp scans the tile counts, and
+    // the group whose range of tiles holds blockIdx.y is the one (all loads at once, not a walk from group 0).
+    if (warp == 0) {
+        const int tile = blockIdx.y;
+        int found = -1, f_start = 0, f_end = 0, f_tile = 0, base = 0;
+        for (int e0 = 0; e0 < p.E && found < 0; e0 += 32) {
+            const int e = e0 + lane;
+            int start = 0, end = 0;
+            if (e < p.E) {
+                start = p.group_offsets[e];
+                end = p.group_offsets[e + 1];
+            }
             const int tiles = (end - start + NT - 1) / NT;
-            if (tile < tiles) break;
-            tile -= tiles;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int first = base + incl - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, e < p.E && tile >= first && tile < first + tiles);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                found = e0 + src;
+                f_start = __shfl_sync(0xffffffffu, start, src);
+                f_end = __shfl_sync(0xffffffffu, end, src);
+                f_tile = tile - __shfl_sync(0xffffffffu, first, src);
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
         }
-        tile_info[0] = (e < p.E) ? e : -1;
-        tile_info[1] = start + tile * NT;
-        tile_info[2] = end;
-        for (int s = 0; s < Cfg::STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
+        if (lane == 0) {
+            tile_info[0] = found;
+            tile_info[1] = f_start + f_tile * NT;
+            tile_info[2] = f_end;
+            for (int s = 0; s < Cfg::STAGES; ++s) {
+                mbar_init(&full_bar[s], 1);
+                mbar_init(&empty_bar[s], 1);
+            }
+            mbar_init(accum_bar, 1);
+            fence_barrier_init();
         }
-        mbar_init(accum_bar, 1);
-        fence_barrier_init();
     }
     __syncthreads();
     const int expert = tile_info[0];
