@@ -30,6 +30,8 @@
 #include "sm100.cuh"
 #include "tensor_map.cuh"
 
+#include <type_traits>
+
 using namespace sm100;
 
 enum TcMode : int { MODE_STORE = 0, MODE_SWIGLU = 1 };
@@ -74,6 +76,63 @@ struct TcConfig {
     static constexpr int TMEM_COLS_NEEDED = W_TILES * NT;
     static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
 };
+
+// silu(g) * u with the exponential and the reciprocal as single instructions (relative error about 2^-21;
+// the result is rounded to bfloat16).  Every epilogue of this file uses this one form.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return g * rcp_approx(1.0f + ex2_approx(-1.4426950408889634f * g)) * u;
+}
+
+// The epilogue of 16 accumulator columns (sorted rows r_first .. r_first + 15, of which `count` exist) of one
+// thread's weight row(s): g from the first weight tile (row n), u from the second (MODE_SWIGLU: the matching
+// up row; MODE_STORE: row n + 128, if the CTA has a second tile).
+template <int MODE>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const float* g, const float* u, bool two_tiles,
+                                                  int n, int r_first, int count) {
+    if (MODE == MODE_SWIGLU) {
+        const int I = p.N / 2;
+        // lane j of the warp fetches the scale of column j (all threads of a warp share the 16 columns)
+        const int lane = threadIdx.x & 31;
+        float mine = 1.0f;
+        if (p.row_scale && lane < count) {
+            const int r = r_first + lane;
+            mine = __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r));
+        }
+        float sc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sc[j] = __shfl_sync(0xffffffffu, mine, j);
+        if (n < I) {
+            bf16* act = reinterpret_cast<bf16*>(p.out);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j < count) {
+                    const float gv = g[j] * sc[j], uv = u[j] * sc[j];
+                    act[(size_t)(r_first + j) * I + n] = __float2bfloat16_rn(silu_mul(gv, uv));
+                }
+            }
+        }
+    } else {
+        float* C = reinterpret_cast<float*>(p.out);
+        const bool n_ok = n < p.N, nb_ok = two_tiles && n + TC_BM < p.N;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (j < count) {
+                // Adding in: every output element gets exactly one addend from this launch (a row belongs to
+                // one group), so a reduction that returns nothing gives the same sum as load, add, store,
+                // without a round trip to memory per element.
+                const int r = r_first + j;
+                float* dst = C + (size_t)(p.out_rows ? __ldg(p.out_rows + r) : r) * p.N + n;
+                if (p.accumulate) {
+                    if (n_ok) atomicAdd(dst, g[j]);
+                    if (nb_ok) atomicAdd(dst + TC_BM, u[j]);
+                } else {
+                    if (n_ok) *dst = g[j];
+                    if (nb_ok) dst[TC_BM] = u[j];
+                }
+            }
+        }
+    }
+}
 
 template <int MODE, int NT, int WT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -235,49 +294,10 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                             if (nb_ok) part[(size_t)r * p.N + nb] = (k_blocks > 0) ? u[j] : 0.0f;
                         }
                     }
-                } else if (MODE == MODE_SWIGLU) {
-                    float u[16];
-                    tmem_ld_16(lane_addr + NT + c0, u);
-                    if (n < I) {
-                        bf16* act = reinterpret_cast<bf16*>(p.out);
-                        float sc[16];                    // all the row scales first: the loads do not wait for stores
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int r = row0 + c0 + j;
-                            sc[j] = (p.row_scale && c0 + j < valid) ? __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r))
-                                                                     : 1.0f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int r = row0 + c0 + j;
-                            if (c0 + j < valid) {
-                                const float gv = g[j] * sc[j], uv = u[j] * sc[j];
-                                act[(size_t)r * I + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
-                            }
-                        }
-                    }
                 } else {
-                    float* C = reinterpret_cast<float*>(p.out);
                     float u[16];
                     if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
-                    const bool n_ok = n < p.N, nb_ok = WT == 2 && n + TC_BM < p.N;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int r = row0 + c0 + j;
-                        if (c0 + j < valid) {
-                            // Adding in: every output element gets exactly one addend from this launch (a row
-                            // belongs to one group), so a reduction that returns nothing gives the same sum
-                            // as load, add, store, without a round trip to memory per element.
-                            float* dst = C + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
-                            if (p.accumulate) {
-                                if (n_ok) atomicAdd(dst, g[j]);
-                                if (nb_ok) atomicAdd(dst + TC_BM, u[j]);
-                            } else {
-                                if (n_ok) *dst = g[j];
-                                if (nb_ok) dst[TC_BM] = u[j];
-                            }
-                        }
-                    }
+                    tc_epilogue_chunk<MODE>(p, g, u, WT == 2, n, row0 + c0, min(16, valid - c0));
                 }
             }
         }
@@ -288,6 +308,288 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Persistent variant for steps with many rows (prompts).
+//
+// One CTA per SM walks a list of work items: (group, chunk of up to 256 of its rows, two weight tiles of 128
+// rows).  An item streams its two weight tiles over all of K once and multiplies them with one or two
+// activation tiles of 128 rows, so a group of up to 256 rows reads its weights once (the kernel above gives
+// every 128 rows a CTA of their own, which streams the weights again).  The three roles run ahead of one
+// another across items: the producer fills a ring of four weight stages and six activation slots, the MMA
+// warp accumulates into tensor memory, the epilogue warps drain it.  Tensor memory (512 columns) holds two
+// items of up to 128 rows at once, one being multiplied while the other is drained, or one of up to 256.
+// The N extent of each MMA is the number of rows rounded up to 16, so short groups cost what they hold.
+// Items go to CTAs round-robin; items next to each other share a group, so its activations stay in L2.
+// Each output element is still one accumulation over K in ascending order inside the tensor core.
+// ---------------------------------------------------------------------------------------
+constexpr int PS_W_STAGES = 4;
+constexpr int PS_A_SLOTS = 6;
+constexpr int PS_W_BYTES = 2 * TC_BM * TC_BK * 2;   // two weight tiles: 32 KB
+constexpr int PS_A_BYTES = 128 * TC_BK * 2;         // 128 activation rows: 16 KB
+constexpr int PS_CHUNK = 256;                       // rows per item
+constexpr int PS_MAX_E = 256;                       // groups whose bounds fit the shared-memory table
+constexpr int PS_TABLE_BYTES = 2 * (PS_MAX_E + 1) * 4;
+constexpr int PS_SMEM = PS_W_STAGES * PS_W_BYTES + PS_A_SLOTS * PS_A_BYTES + 256 + PS_TABLE_BYTES;
+static_assert(PS_SMEM <= 227 * 1024, "the persistent kernel's rings must fit one CTA");
+
+struct PsItem {
+    int expert, row0, nrows, n_tile;
+};
+
+// Item w of the list: groups in order, their chunks in order, the weight tiles of a chunk next to each other.
+// `e` is a cursor that only moves forward (a CTA's items ascend).
+__device__ __forceinline__ PsItem ps_decode(int w, int& e, const int* first_s, const int* off_s, int n_tiles) {
+    while (w >= first_s[e + 1]) ++e;
+    const int local = w - first_s[e];
+    PsItem it;
+    it.expert = e;
+    it.n_tile = local % n_tiles;
+    it.row0 = off_s[e] + (local / n_tiles) * PS_CHUNK;
+    it.nrows = min(PS_CHUNK, off_s[e + 1] - it.row0);
+    return it;
+}
+
+constexpr int PS_EPI_WARPS = 8;                     // two per quarter of the tensor-memory lanes
+constexpr int PS_THREADS = (PS_EPI_WARPS + 2) * 32;  // then the producer warp and the MMA warp
+
+template <int MODE>
+__global__ void __launch_bounds__(PS_THREADS, 1)
+tc_grouped_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                                  const TcGemmParams p) {
+    extern __shared__ __align__(1024) uint8_t ps_smem[];
+    if (smem_u32(ps_smem) & 1023u) {             // the swizzled tiles need it; nothing has been set up yet
+        if (threadIdx.x == 0) atomicExch(p.status, 6);
+        return;
+    }
+    uint8_t* w_ring = ps_smem;
+    uint8_t* a_ring = w_ring + PS_W_STAGES * PS_W_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(a_ring + PS_A_SLOTS * PS_A_BYTES);
+    uint64_t* full_w = bars;                      // [4]
+    uint64_t* empty_w = full_w + PS_W_STAGES;     // [4]
+    uint64_t* full_a = empty_w + PS_W_STAGES;     // [6]
+    uint64_t* empty_a = full_a + PS_A_SLOTS;      // [6]
+    uint64_t* full_t = empty_a + PS_A_SLOTS;      // [2] accumulators of a half of tensor memory complete
+    uint64_t* empty_t = full_t + 2;               // [2] ... drained (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_t + 2);
+    int* first_s = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);   // [E + 1] first item of a group
+    int* off_s = first_s + PS_MAX_E + 1;                                              // [E + 1] first row of a group
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int I = p.N / 2;
+    const int n_tiles = (MODE == MODE_SWIGLU) ? (I + TC_BM - 1) / TC_BM : (p.N + 2 * TC_BM - 1) / (2 * TC_BM);
+    const int k_blocks = (p.K + TC_BK - 1) / TC_BK;
+
+    if (warp == 0) {
+        int base = 0;
+        for (int e0 = 0; e0 < p.E; e0 += 32) {
+            const int e = e0 + lane;
+            int start = 0, end = 0;
+            if (e < p.E) {
+                start = p.group_offsets[e];
+                end = p.group_offsets[e + 1];
+            }
+            const int items = ((end - start + PS_CHUNK - 1) / PS_CHUNK) * n_tiles;
+            int incl = items;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e < p.E) {
+                first_s[e] = base + incl - items;
+                off_s[e] = start;
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            first_s[p.E] = base;
+            off_s[p.E] = p.group_offsets[p.E];
+            for (int i = 0; i < PS_W_STAGES; ++i) { mbar_init(&full_w[i], 1); mbar_init(&empty_w[i], 1); }
+            for (int i = 0; i < PS_A_SLOTS; ++i) { mbar_init(&full_a[i], 1); mbar_init(&empty_a[i], 1); }
+            for (int i = 0; i < 2; ++i) { mbar_init(&full_t[i], 1); mbar_init(&empty_t[i], PS_EPI_WARPS * 32); }
+            fence_barrier_init();
+        }
+    }
+    if (warp == PS_EPI_WARPS + 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total = first_s[p.E];
+
+    if (warp == PS_EPI_WARPS) {
+        // ---- TMA producer ------------------------------------------------------------------
+        if (lane == 0) {
+            prefetch_tensormap(&map_w);
+            prefetch_tensormap(&map_a);
+            uint32_t cw = 0, ca = 0;          // weight stages and activation slots filled so far
+            int e = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                const PsItem it = ps_decode(w, e, first_s, off_s, n_tiles);
+                const int n0 = it.n_tile * TC_BM * (MODE == MODE_SWIGLU ? 1 : 2);
+                const int n1 = (MODE == MODE_SWIGLU) ? I + n0 : n0 + TC_BM;
+                const int subs = (it.nrows + 127) >> 7;
+                for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                    const int kx = kb * TC_BK;
+                    const int ws = cw % PS_W_STAGES;
+                    if (cw >= PS_W_STAGES) ok = mbar_wait(&empty_w[ws], ((cw / PS_W_STAGES) - 1) & 1);
+                    if (!ok) { atomicExch(p.status, 1); break; }
+                    uint8_t* wt = w_ring + ws * PS_W_BYTES;
+                    mbar_arrive_expect_tx(&full_w[ws], PS_W_BYTES);
+                    tma_load_3d(wt, &map_w, &full_w[ws], kx, n0, it.expert);
+                    tma_load_3d(wt + PS_W_BYTES / 2, &map_w, &full_w[ws], kx, n1, it.expert);
+                    ++cw;
+                    for (int sub = 0; sub < subs; ++sub) {
+                        const int as = ca % PS_A_SLOTS;
+                        if (ca >= PS_A_SLOTS) ok = mbar_wait(&empty_a[as], ((ca / PS_A_SLOTS) - 1) & 1);
+                        if (!ok) { atomicExch(p.status, 1); break; }
+                        mbar_arrive_expect_tx(&full_a[as], PS_A_BYTES);
+                        tma_load_2d(a_ring + as * PS_A_BYTES, &map_a, &full_a[as], kx, it.row0 + sub * 128);
+                        ++ca;
+                    }
+                }
+            }
+            if (!ok) {
+                // let the copies that were started land before the block goes away
+                for (uint32_t c = cw > PS_W_STAGES ? cw - PS_W_STAGES : 0; c < cw; ++c)
+                    mbar_wait(&full_w[c % PS_W_STAGES], (c / PS_W_STAGES) & 1, 1u << 16);
+                for (uint32_t c = ca > PS_A_SLOTS ? ca - PS_A_SLOTS : 0; c < ca; ++c)
+                    mbar_wait(&full_a[c % PS_A_SLOTS], (c / PS_A_SLOTS) & 1, 1u << 16);
+            }
+        }
+    } else if (warp == PS_EPI_WARPS + 1) {
+        // ---- MMA issuer --------------------------------------------------------------------
+        // One thread issues every MMA of the CTA, so its instruction stream is kept short: ring positions and
+        // parities advance by increments, descriptors are a base plus the position times the slot size.
+        if (lane == 0) {
+            uint32_t ws = 0, pw = 0, as = 0, pa = 0;       // weight stage / activation slot and their parities
+            uint32_t use0 = 0, use1 = 0;
+            int e = 0, next_half = 0;
+            bool ok = true;
+            const uint64_t wdesc = smem_desc_k_sw128(w_ring, 0), adesc = smem_desc_k_sw128(a_ring, 0);
+            auto run_item = [&](auto subs_tag, const PsItem& it, uint32_t acc_base) {
+                constexpr int SUBS = decltype(subs_tag)::value;
+                const uint32_t idesc0 = instr_desc_bf16(TC_BM, (min(128, it.nrows) + 15) & ~15);
+                const uint32_t idesc1 = SUBS == 2 ? instr_desc_bf16(TC_BM, (it.nrows - 128 + 15) & ~15) : 0u;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_w[ws], pw)) return false;
+                    const uint32_t as1 = (as + 1 == PS_A_SLOTS) ? 0 : as + 1;
+                    if (!mbar_wait(&full_a[as], pa)) return false;
+                    if (SUBS == 2 && !mbar_wait(&full_a[as1], as1 == 0 ? pa ^ 1 : pa)) return false;
+                    tcgen05_fence_after();
+                    const uint64_t dw0 = wdesc + (uint64_t)(ws * (PS_W_BYTES >> 4));
+                    const uint64_t dw1 = dw0 + (uint64_t)(PS_W_BYTES >> 5);
+                    const uint64_t da0 = adesc + (uint64_t)(as * (PS_A_BYTES >> 4));
+                    const uint64_t da1 = adesc + (uint64_t)(as1 * (PS_A_BYTES >> 4));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        const uint32_t acc = (kb | k) != 0;
+                        // alternate the accumulators: back-to-back MMAs into one accumulator wait for each other
+                        mma_bf16_ss(acc_base, dw0 + 2 * k, da0 + 2 * k, idesc0, acc);
+                        mma_bf16_ss(acc_base + 128, dw1 + 2 * k, da0 + 2 * k, idesc0, acc);
+                        if (SUBS == 2) {          // the second 128 rows accumulate in the other half
+                            mma_bf16_ss(acc_base + 256, dw0 + 2 * k, da1 + 2 * k, idesc1, acc);
+                            mma_bf16_ss(acc_base + 256 + 128, dw1 + 2 * k, da1 + 2 * k, idesc1, acc);
+                        }
+                    }
+                    mma_commit(&empty_w[ws]);         // free when these MMAs have read them
+                    mma_commit(&empty_a[as]);
+                    if (SUBS == 2) mma_commit(&empty_a[as1]);
+                    ws = (ws + 1) & (PS_W_STAGES - 1);
+                    pw ^= (ws == 0);
+                    as += SUBS;
+                    if (as >= PS_A_SLOTS) { as -= PS_A_SLOTS; pa ^= 1; }
+                }
+                return true;
+            };
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                const PsItem it = ps_decode(w, e, first_s, off_s, n_tiles);
+                const bool big = it.nrows > 128;
+                // an item of up to 128 rows takes one half of tensor memory (the halves alternate), a larger one both
+                const int h0 = big ? 0 : next_half;
+                next_half = big ? 0 : next_half ^ 1;
+                if ((big || h0 == 0) && use0 > 0) ok = mbar_wait(&empty_t[0], (use0 - 1) & 1);
+                if (ok && (big || h0 == 1) && use1 > 0) ok = mbar_wait(&empty_t[1], (use1 - 1) & 1);
+                if (!ok) { atomicExch(p.status, 7); break; }
+                tcgen05_fence_after();
+                const uint32_t acc_base = tmem_base + h0 * 256;
+                ok = big ? run_item(std::integral_constant<int, 2>{}, it, acc_base)
+                         : run_item(std::integral_constant<int, 1>{}, it, acc_base);
+                if (!ok) { atomicExch(p.status, 2); break; }
+                if (big || h0 == 0) { mma_commit(&full_t[0]); ++use0; }     // the item's accumulators are complete
+                if (big || h0 == 1) { mma_commit(&full_t[1]); ++use1; }
+            }
+        }
+    } else {
+        // ---- epilogue: warps 0..7; warp w reads lanes 32 (w % 4) .. (thread = weight row) and every second
+        // 16-column piece, starting at piece w / 4.  A half of tensor memory is handed back as soon as its 128
+        // rows are out, so the next item can start while the second half of a large item is still drained.
+        uint32_t uses[2] = {0, 0};
+        int e = 0, next_half = 0;
+        bool ok = true;
+        const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            const PsItem it = ps_decode(w, e, first_s, off_s, n_tiles);
+            const int subs = (it.nrows + 127) >> 7;
+            const int h0 = (subs == 2) ? 0 : next_half;
+            next_half = (subs == 2) ? 0 : next_half ^ 1;
+            const int n = it.n_tile * TC_BM * (MODE == MODE_SWIGLU ? 1 : 2) + (warp & 3) * 32 + lane;
+            for (int sub = 0; sub < subs && ok; ++sub) {
+                const int h = h0 + sub;
+                ok = mbar_wait(&full_t[h], uses[h] & 1);
+                if (!ok) {
+                    if (lane == 0) atomicExch(p.status, 3);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t acc = lane_base + h * 256;
+                const int valid = min(128, it.nrows - sub * 128);
+#pragma unroll 1
+                for (int c0 = (warp >> 2) * 16; c0 < valid; c0 += 32) {
+                    float g[16], u[16];
+                    tmem_ld_16(acc + c0, g);
+                    tmem_ld_16(acc + 128 + c0, u);
+                    tc_epilogue_chunk<MODE>(p, g, u, true, n, it.row0 + sub * 128 + c0, min(16, valid - c0));
+                }
+                tcgen05_fence_before();
+                mbar_arrive(&empty_t[h]);
+                ++uses[h];
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == PS_EPI_WARPS + 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <int MODE>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmParams& p, long long max_items,
+                             cudaStream_t stream) {
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            return SHARPI_LAUNCH_FAILED;
+        if (cudaFuncSetAttribute(tc_grouped_gemm_persistent_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PS_SMEM) != cudaSuccess)
+            return SHARPI_LAUNCH_FAILED;
+        configured = true;
+    }
+    const int grid = (int)(max_items < sms ? max_items : sms);
+    tc_grouped_gemm_persistent_kernel<MODE><<<grid, PS_THREADS, PS_SMEM, stream>>>(mw, ma, p);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -327,7 +629,7 @@ __global__ void tc_split_reduce_kernel(const TcGemmParams p) {
     if (MODE == MODE_SWIGLU) {
         const float s = p.row_scale ? p.row_scale[p.scale_rows ? p.scale_rows[r] : r] : 1.0f;
         const float gv = g * s, uv = u * s;
-        reinterpret_cast<bf16*>(p.out)[(size_t)r * n_out + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+        reinterpret_cast<bf16*>(p.out)[(size_t)r * n_out + n] = __float2bfloat16_rn(silu_mul(gv, uv));
     } else {
         float* dst = reinterpret_cast<float*>(p.out) + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
         *dst = p.accumulate ? *dst + g : g;
@@ -335,7 +637,8 @@ __global__ void tc_split_reduce_kernel(const TcGemmParams p) {
 }
 
 // A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
-// `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes.
+// `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes; 0 asks for the
+// persistent kernel (up to 256 groups, no K split).
 // `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch) cuts K over that many CTAs per tile.
 SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
                                       const int* out_rows, const float* row_scale, const int* scale_rows,
@@ -348,13 +651,22 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     if (!status || !group_offsets) return SHARPI_BAD_ARGUMENT;
     CUtensorMap mw, ma;
     if (!tmap::make_bf16_map(&mw, W, (uint64_t)K, (uint64_t)N, (uint64_t)E, TC_BK, TC_BM)) return SHARPI_LAUNCH_FAILED;
-    if (!tmap::make_bf16_map(&ma, A, (uint64_t)K, (uint64_t)rows, 0, TC_BK, (uint32_t)row_tile)) return SHARPI_LAUNCH_FAILED;
+    if (!tmap::make_bf16_map(&ma, A, (uint64_t)K, (uint64_t)rows, 0, TC_BK, (uint32_t)(row_tile ? row_tile : 128)))
+        return SHARPI_LAUNCH_FAILED;
     TcGemmParams p;
     p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
     if (k_split < 1 || k_split > 16 || (k_split > 1 && !partial)) return SHARPI_BAD_ARGUMENT;
     p.partial = partial; p.k_split = k_split;
     const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
+    if (row_tile == 0) {
+        // the persistent kernel: 128-row activation boxes, two weight tiles per item
+        if (k_split != 1 || E > PS_MAX_E || rows < 128) return SHARPI_BAD_ARGUMENT;
+        const long long tiles = (mode == MODE_SWIGLU) ? (n_out + TC_BM - 1) / TC_BM : (N + 2 * TC_BM - 1) / (2 * TC_BM);
+        const long long max_items = ((long long)rows / PS_CHUNK + (rows < E ? rows : E)) * tiles;
+        return mode == MODE_SWIGLU ? launch_persistent<MODE_SWIGLU>(mw, ma, p, max_items, stream)
+                                   : launch_persistent<MODE_STORE>(mw, ma, p, max_items, stream);
+    }
     // two weight tiles per activation tile pay from about 2048 rows on (measured at 16 experts: 281 vs 315 us
     // at 2048 rows, 658 vs 719 us at 8192; below that the larger number of CTAs of single tiles wins)
     const int store_wt = (mode == MODE_STORE && row_tile >= 128 && rows >= 2048) ? 2 : 1;

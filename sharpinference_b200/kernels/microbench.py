@@ -80,7 +80,7 @@ def tc_gemm(ns) -> None:
                                          row_tile=ns.row_tile, k_split=ns.k_split)
         weight_bytes, flops = used * H * I * 2, 2 * T * H * I
     ms = _time(fn, ns.iters)
-    print(f"tc_gemm {ns.mode} rows={T} experts={used}/{E} row_tile={ns.row_tile or ops.tc_row_tile(T)}: {ms * 1e3:.1f} us, "
+    print(f"tc_gemm {ns.mode} rows={T} experts={used}/{E} row_tile={ops.tc_row_tile(T, ops.TC_MODE_SWIGLU if ns.mode == "gate_up" else ops.TC_MODE_STORE, E) if ns.row_tile is None else ns.row_tile}: {ms * 1e3:.1f} us, "
           f"weights {weight_bytes / ms / 1e6:.0f} GB/s, {flops / ms / 1e9:.0f} TFLOP/s")
 
 

@@ -397,7 +397,8 @@ def grouped_case(T, E, K, seed, empty=()):
 @pytest.mark.parametrize("T,E,N,K,row_tile", [(8, 4, 256, 128, 16), (5, 3, 200, 72, 16), (64, 16, 384, 512, 16),
                                               (300, 5, 136, 264, 64), (700, 3, 520, 128, 128), (70, 2, 128, 64, 32),
                                               (1500, 4, 256, 192, 256), (2100, 3, 520, 128, 128),
-                                              (2500, 5, 136, 72, 128), (2048, 2, 256, 64, 256)])
+                                              (2500, 5, 136, 72, 128), (2048, 2, 256, 64, 256),
+                                              (700, 3, 520, 128, 0), (2500, 5, 136, 72, 0), (1100, 40, 264, 192, 0)])
 def test_tc_grouped_gemm_store(ops, T, E, N, K, row_tile):
     expert, order, offsets, a = grouped_case(T, E, K, seed=T + N, empty=(1,) if E > 2 else ())
     w = rnd(E, N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
@@ -416,7 +417,8 @@ def test_tc_grouped_gemm_store(ops, T, E, N, K, row_tile):
 
 
 @pytest.mark.parametrize("T,E,I,K,row_tile", [(8, 4, 128, 128, 16), (7, 3, 40, 88, 16), (64, 16, 256, 320, 16),
-                                              (300, 5, 72, 264, 64), (900, 3, 200, 128, 128), (600, 2, 136, 64, 256)])
+                                              (300, 5, 72, 264, 64), (900, 3, 200, 128, 128), (600, 2, 136, 64, 256),
+                                              (900, 3, 200, 128, 0), (2300, 7, 136, 320, 0)])
 def test_tc_grouped_gemm_swiglu(ops, T, E, I, K, row_tile):
     expert, order, offsets, a = grouped_case(T, E, K, seed=T + I, empty=(0,) if E > 2 else ())
     w = rnd(E, 2 * I, K, dtype=torch.bfloat16, scale=0.1, seed=5)
@@ -459,6 +461,11 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
                                row_tile=128)
     ops.check_status(DEV)
     assert torch.equal(one[0], many[600 + 9])
+    # the persistent kernel (items of up to 256 rows, MMA extents cut to the rows there are): the same bits
+    walked = ops.tc_grouped_gemm(a_many[order_many.to(DEV)].contiguous(), w, offsets_many, mode=ops.TC_MODE_STORE,
+                                 row_tile=0)
+    ops.check_status(DEV)
+    assert torch.equal(walked, many)
     # with K cut over several CTAs the parts are added in another order: equal to rounding, not to the bit
     cut = ops.tc_grouped_gemm(a[t:t + 1].contiguous(), w, torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device=DEV),
                               mode=ops.TC_MODE_STORE, row_tile=16, k_split=3)
