@@ -267,6 +267,7 @@ def main() -> int:
     engine = Engine(model, dtype="bfloat16", device=dev,
                     options=EngineOptions(page_size=page, max_cache_tokens=cache_tokens, max_batch=max_b,
                                           max_tokens_per_step=max(ns.prefill_tokens, max_b)))
+    torch.manual_seed(0)                   # the cache content decides the routing of the timed steps: keep it fixed
     for g in engine.cache.groups:          # keys and values as a prefill would have left them: unit-scale numbers
         g.kv.normal_(0.0, 1.0)
     print(f"[bench] model and cache ready in {time.time() - t0:.1f} s, "

@@ -170,9 +170,10 @@ static int launch_router(const float* h, const float* wr, int T, int H, int E, i
 __global__ void __launch_bounds__(ROUTER_SEGMENTS * 32)
 router_top1_small_kernel(const float* __restrict__ h, const float* __restrict__ wr, int H, int E,
                          int* __restrict__ expert_id, float* __restrict__ expert_weight,
-                         float* __restrict__ logits, int* __restrict__ tickets) {
+                         float* __restrict__ logits, int* __restrict__ tickets, int* __restrict__ offsets,
+                         int* __restrict__ sorted_rows) {
     __shared__ float seg_s[ROUTER_SEGMENTS];
-    __shared__ int last_s;
+    __shared__ int last_s, sort_s;
     const int t = blockIdx.x, e = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
@@ -206,26 +207,61 @@ router_top1_small_kernel(const float* __restrict__ h, const float* __restrict__ 
             expert_weight[t] = best_p;
         }
     }
+    if (!sorted_rows) return;
+    // The block that picks the step's last expert also sorts the step's (at most 32) rows by expert: a second
+    // ticket counts the tokens that have theirs.  The same stable counting sort as moe_sort_kernel.
+    if (threadIdx.x == 0) {
+        sort_s = 0;
+        if (last_s) {
+            __threadfence();
+            sort_s = (atomicAdd(&tickets[32], 1) == (int)gridDim.x - 1);
+            if (sort_s) tickets[32] = 0;
+        }
+    }
+    __syncthreads();
+    if (!sort_s || warp != 0) return;
+    __threadfence();
+    const int T = gridDim.x;
+    const int id = (lane < T) ? __ldcg(expert_id + lane) : -1;
+    const unsigned lt = (1u << lane) - 1u;
+    int run = 0;
+    for (int x = 0; x < E; ++x) {
+        const unsigned mask = __ballot_sync(0xffffffffu, id == x);
+        if (lane == 0) offsets[x] = run;
+        if (id == x) sorted_rows[run + __popc(mask & lt)] = lane;
+        run += __popc(mask);
+    }
+    if (lane == 0) offsets[E] = run;
 }
 
-// `scratch`, optional: [32 * E] floats then [32] zero-initialised ints (the tickets, left zero again).
+static int launch_sort(const int* expert_id, int T, int E, int* offsets, int* sorted_rows, cudaStream_t stream);
+
+// `scratch`, optional: [32 * E] floats then [33] zero-initialised ints (the tickets, left zero again).
 // With it, steps of up to 32 tokens take the kernel that gives every (token, expert) pair a block.
+// `offsets` [E + 1] and `sorted_rows` [T], optional (both or none): the rows sorted by expert as sharpi_moe_sort
+// gives them, from the same launch when the step is small, from a second one otherwise.
 SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H, int E, int gate, int* expert_id,
-                                  float* expert_weight, float* logits_out, void* scratch, cudaStream_t stream) {
-    if (T <= 0) return SHARPI_OK;
+                                  float* expert_weight, float* logits_out, void* scratch, int* offsets,
+                                  int* sorted_rows, cudaStream_t stream) {
+    if ((offsets == nullptr) != (sorted_rows == nullptr)) return SHARPI_BAD_ARGUMENT;
+    if (T <= 0) return offsets ? launch_sort(expert_id, 0, E, offsets, sorted_rows, stream) : SHARPI_OK;
     if (H <= 0 || E <= 0 || gate != ROUTER_GATE_SIGMOID) return SHARPI_BAD_ARGUMENT;
     if (T <= 32 && scratch && E <= 65535) {
         float* logits = logits_out ? logits_out : reinterpret_cast<float*>(scratch);
         int* tickets = reinterpret_cast<int*>(reinterpret_cast<float*>(scratch) + (size_t)32 * E);
         router_top1_small_kernel<<<dim3(T, E), ROUTER_SEGMENTS * 32, 0, stream>>>(h, wr, H, E, expert_id, expert_weight,
-                                                                                 logits, tickets);
+                                                                                 logits, tickets, offsets, sorted_rows);
         SHARPI_CHECK_LAUNCH();
         return SHARPI_OK;
     }
     // many tokens: eight share a block and its reads of the router rows; fewer: two, for more blocks
+    int rc;
     if (T >= 1024 && (size_t)(ROUTER_SEGMENTS + 1) * 8 * E * sizeof(float) <= 200 * 1024)
-        return launch_router<8, 4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
-    return launch_router<2, 8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+        rc = launch_router<8, 4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+    else
+        rc = launch_router<2, 8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
+    if (rc != SHARPI_OK || !offsets) return rc;
+    return launch_sort(expert_id, T, E, offsets, sorted_rows, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -292,10 +328,14 @@ moe_sort_kernel(const int* __restrict__ expert_id, int T, int E, int* __restrict
     }
 }
 
-SHARPI_API int sharpi_moe_sort(const int* expert_id, int T, int E, int* offsets, int* sorted_rows,
-                               cudaStream_t stream) {
+static int launch_sort(const int* expert_id, int T, int E, int* offsets, int* sorted_rows, cudaStream_t stream) {
     if (E <= 0 || E > SORT_MAX_E || T < 0) return SHARPI_BAD_ARGUMENT;
     moe_sort_kernel<<<1, SORT_THREADS, 0, stream>>>(expert_id, T, E, offsets, sorted_rows);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
+}
+
+SHARPI_API int sharpi_moe_sort(const int* expert_id, int T, int E, int* offsets, int* sorted_rows,
+                               cudaStream_t stream) {
+    return launch_sort(expert_id, T, E, offsets, sorted_rows, stream);
 }

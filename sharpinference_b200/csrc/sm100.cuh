@@ -174,6 +174,23 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// A barrier of `threads` threads (a multiple of 32) other than __syncthreads' own, which also tells whether
+// `mine` holds for all of them.
+__device__ __forceinline__ bool named_barrier_all(int id, int threads, bool mine) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %3, 0;\n\t"
+        "barrier.cta.red.and.pred q, %1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}"
+        : "=r"(all)
+        : "r"(id), "r"(threads), "r"((uint32_t)mine)
+        : "memory");
+    return all != 0;
+}
+
 __device__ __forceinline__ float rcp_approx(float x) {
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -50,10 +50,11 @@ struct TcGemmParams {
     int rows, N, K, E;          // N: weight rows per expert (MODE_SWIGLU: 2 I)
     int accumulate;
     // K split over gridDim.z CTAs (few rows and few experts: not enough tiles to fill the GPU otherwise).
-    // Each CTA then leaves its raw fp32 accumulators in partial[z][sorted row][N] and a second kernel adds
-    // the parts in a fixed order and applies the epilogue.
+    // Each CTA then leaves its raw fp32 accumulators in partial[z][sorted row][N]; the one that finishes last
+    // adds the parts in the order of z and applies the epilogue.
     float* partial;
     int k_split;
+    int* tickets;               // K split: one counter per tile, zero before the launch and again after it
 };
 
 // WT: weight tiles of 128 rows that share one activation tile.  MODE_SWIGLU always has two (gate and up);
@@ -73,6 +74,8 @@ struct TcConfig {
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static_assert(STAGES >= 2, "a tile configuration must leave room for two stages");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    // registers are capped so that the two CTAs that fit an SM by shared memory also fit by registers
+    static constexpr int MIN_CTAS = (2 * SMEM_BYTES <= 224 * 1024) ? 2 : 1;
     static constexpr int TMEM_COLS_NEEDED = W_TILES * NT;
     static constexpr int TMEM_COLS = TMEM_COLS_NEEDED <= 32 ? 32 : TMEM_COLS_NEEDED <= 64 ? 64 : TMEM_COLS_NEEDED <= 128 ? 128 : TMEM_COLS_NEEDED <= 256 ? 256 : 512;
 };
@@ -135,7 +138,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
 }
 
 template <int MODE, int NT, int WT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, TcConfig<MODE, NT, WT>::MIN_CTAS)
 tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                        const TcGemmParams p) {
     using Cfg = TcConfig<MODE, NT, WT>;
@@ -267,25 +270,25 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else {
         // ---- epilogue: warps 0..3, thread = TMEM lane = weight row ---------------------------
         const bool ok = mbar_wait(accum_bar, 0);
+        const int n = n0 + warp * 32 + lane;
+        const int nb = n1 - n0 + n;                    // the row of the second tile
+        const int valid = min(NT, row_end - row0);
+        const size_t plane = (size_t)p.rows * p.N;
+        const bool n_ok = MODE == MODE_SWIGLU ? n < I : n < p.N;
+        const bool nb_ok = WT == 2 && (MODE == MODE_SWIGLU ? n < I : nb < p.N);
         if (!ok) {
             if (lane == 0) atomicExch(p.status, 3);
         } else {
             tcgen05_fence_after();
-            const int n = n0 + warp * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-            const int valid = min(NT, row_end - row0);
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 16) {
                 if (c0 >= valid) break;               // uniform over the warp
-                float g[16];
+                float g[16], u[16];
                 tmem_ld_16(lane_addr + c0, g);
+                if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
                 if (p.k_split > 1) {
-                    float* part = p.partial + (size_t)blockIdx.z * p.rows * p.N;
-                    float u[16];
-                    if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
-                    const int nb = n1 - n0 + n;            // the row of the second tile
-                    const bool n_ok = MODE == MODE_SWIGLU ? n < I : n < p.N;
-                    const bool nb_ok = WT == 2 && (MODE == MODE_SWIGLU ? n < I : nb < p.N);
+                    float* part = p.partial + (size_t)blockIdx.z * plane;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int r = row0 + c0 + j;
@@ -295,9 +298,46 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                         }
                     }
                 } else {
-                    float u[16];
-                    if (WT == 2) tmem_ld_16(lane_addr + NT + c0, u);
                     tc_epilogue_chunk<MODE>(p, g, u, WT == 2, n, row0 + c0, min(16, valid - c0));
+                }
+            }
+        }
+        if (p.k_split > 1) {
+            // The CTA that finishes last of the tile's K parts adds them, in the order of the parts, and applies
+            // the epilogue.  All 128 threads meet at a barrier of their own that also tells whether all of them
+            // have their part (a wait that gave up must not leave the others waiting here).
+            __threadfence();
+            if (named_barrier_all(1, 128, ok)) {
+                if (threadIdx.x == 0) {
+                    int* ticket = p.tickets + (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+                    const int last = atomicAdd(ticket, 1) == p.k_split - 1;
+                    if (last) *ticket = 0;
+                    tile_info[3] = last;
+                }
+                named_barrier_all(1, 128, true);
+                if (tile_info[3]) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < valid; c0 += 16) {
+                        float g[16], u[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            g[j] = 0.0f;
+                            u[j] = 0.0f;
+                        }
+                        for (int z = 0; z < p.k_split; ++z) {
+                            const float* part = p.partial + (size_t)z * plane;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int r = row0 + c0 + j;
+                                if (c0 + j < valid) {
+                                    if (n_ok) g[j] += __ldcg(part + (size_t)r * p.N + n);
+                                    if (nb_ok) u[j] += __ldcg(part + (size_t)r * p.N + nb);
+                                }
+                            }
+                        }
+                        tc_epilogue_chunk<MODE>(p, g, u, WT == 2, n, row0 + c0, min(16, valid - c0));
+                    }
                 }
             }
         }
@@ -612,37 +652,14 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmPara
     return SHARPI_OK;
 }
 
-// Second half of a K-split product: add the parts in the order z = 0, 1, ... and apply the epilogue.
-template <int MODE>
-__global__ void tc_split_reduce_kernel(const TcGemmParams p) {
-    const int r = blockIdx.x;
-    const int n = blockIdx.y * blockDim.x + threadIdx.x;
-    const int n_out = (MODE == MODE_SWIGLU) ? p.N / 2 : p.N;
-    if (n >= n_out) return;
-    const size_t plane = (size_t)p.rows * p.N;
-    const float* part = p.partial + (size_t)r * p.N;
-    float g = 0.0f, u = 0.0f;
-    for (int z = 0; z < p.k_split; ++z) {
-        g += part[z * plane + n];
-        if (MODE == MODE_SWIGLU) u += part[z * plane + n_out + n];
-    }
-    if (MODE == MODE_SWIGLU) {
-        const float s = p.row_scale ? p.row_scale[p.scale_rows ? p.scale_rows[r] : r] : 1.0f;
-        const float gv = g * s, uv = u * s;
-        reinterpret_cast<bf16*>(p.out)[(size_t)r * n_out + n] = __float2bfloat16_rn(silu_mul(gv, uv));
-    } else {
-        float* dst = reinterpret_cast<float*>(p.out) + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
-        *dst = p.accumulate ? *dst + g : g;
-    }
-}
-
 // A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
 // `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes; 0 asks for the
 // persistent kernel (up to 256 groups, no K split).
-// `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch) cuts K over that many CTAs per tile.
+// `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch, and `tickets`, one zero int per tile of the
+// launch grid) cuts K over that many CTAs per tile.
 SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
                                       const int* out_rows, const float* row_scale, const int* scale_rows,
-                                      int* status, float* partial, int rows, int N, int K, int E, int mode,
+                                      int* status, float* partial, int* tickets, int rows, int N, int K, int E, int mode,
                                       int row_tile, int accumulate, int k_split, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return SHARPI_OK;
     if (K <= 0 || E <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;          // TMA: rows 16-byte aligned
@@ -656,8 +673,8 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     TcGemmParams p;
     p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
-    if (k_split < 1 || k_split > 16 || (k_split > 1 && !partial)) return SHARPI_BAD_ARGUMENT;
-    p.partial = partial; p.k_split = k_split;
+    if (k_split < 1 || k_split > 16 || (k_split > 1 && (!partial || !tickets))) return SHARPI_BAD_ARGUMENT;
+    p.partial = partial; p.k_split = k_split; p.tickets = tickets;
     const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
     if (row_tile == 0) {
         // the persistent kernel: 128-row activation boxes, two weight tiles per item
@@ -684,14 +701,7 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     TC_CASE(MODE_SWIGLU, 16, 2) TC_CASE(MODE_SWIGLU, 32, 2) TC_CASE(MODE_SWIGLU, 64, 2) TC_CASE(MODE_SWIGLU, 128, 2)
     TC_CASE(MODE_SWIGLU, 256, 2)
 #undef TC_CASE
-    if (rc != SHARPI_OK || k_split == 1) return rc;
-    dim3 rgrid(rows, (n_out + 255) / 256);
-    if (mode == MODE_SWIGLU)
-        tc_split_reduce_kernel<MODE_SWIGLU><<<rgrid, 256, 0, stream>>>(p);
-    else
-        tc_split_reduce_kernel<MODE_STORE><<<rgrid, 256, 0, stream>>>(p);
-    SHARPI_CHECK_LAUNCH();
-    return SHARPI_OK;
+    return rc;
 }
 
 // out[r, :] = in[rows[r], :] for bf16 rows of width K (a multiple of 8): the activations sorted by

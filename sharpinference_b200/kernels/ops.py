@@ -169,6 +169,21 @@ FAST_ATTENTION_HEAD_SIZES = (16, 32, 48, 64, 80, 96, 112, 128)
 DECODE_SPLIT = 256
 
 
+_ticket_buffers = {}
+
+
+def zeroed_tickets(device, count: int) -> torch.Tensor:
+    """``count`` int32 zeros for kernels whose last CTA finishes a piece of work (it counts arrivals there and
+    leaves the counters at zero).  One buffer per device and stream, so that launches that may overlap on two
+    streams never share counters; it grows when a launch needs more."""
+    key = (torch.device(device), torch.cuda.current_stream(device).cuda_stream)
+    buf = _ticket_buffers.get(key)
+    if buf is None or buf.numel() < count:
+        buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _ticket_buffers[key] = buf
+    return buf
+
+
 def decode_splits(max_context: int, mask_kind: int, mask_span: int) -> int:
     """An upper bound on the 256-key splits a decode row needs (the kernel skips the empty ones)."""
     full = (max_context + DECODE_SPLIT - 1) // DECODE_SPLIT
@@ -309,6 +324,8 @@ def check_status(device) -> None:
         code = int(w.item())
         if code != 0:
             w.zero_()
+            for buf in _ticket_buffers.values():      # a kernel that gave up may have left counters behind
+                buf.zero_()
             raise KernelError(f"a tensor-core kernel gave up (code {code}: 1 = wait for a free stage, 2 = for a loaded "
                               f"stage, 3 = for the accumulator, 4 = for a key/value copy, 5 = misaligned staging "
                               f"buffer, 6 = misaligned shared memory, 7 = for drained tensor memory, 11-18 = "
@@ -396,9 +413,12 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     partial = torch.empty((k_split, rows, N), dtype=torch.float32, device=a.device) if k_split > 1 else None
     if row_tile is None:
         row_tile = tc_row_tile(rows, mode, E)
+    tickets = None
+    if k_split > 1:           # one counter per (weight tile, row tile) of the launch grid
+        tickets = zeroed_tickets(a.device, ((N + 127) // 128) * (rows // max(row_tile, 1) + min(rows, E)))
     check(kernel("sharpi_tc_grouped_gemm")(a.data_ptr(), w.data_ptr(), group_offsets.data_ptr(), out.data_ptr(),
                                            _ptr(out_rows), _ptr(row_scale), _ptr(scale_rows), status.data_ptr(),
-                                           _ptr(partial), rows, N, K, E, mode, row_tile,
+                                           _ptr(partial), _ptr(tickets), rows, N, K, E, mode, row_tile,
                                            int(accumulate), k_split, _stream()), "sharpi_tc_grouped_gemm")
     return out
 
@@ -425,8 +445,10 @@ def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Opt
                            row_tile=row_tile, k_split=k_split)
 
 
-def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False):
-    """Top-1 sigmoid routing.  Returns ``(expert_id int32 [T], weight fp32 [T], logits or None)``."""
+def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False, sort: bool = False):
+    """Top-1 sigmoid routing.  Returns ``(expert_id int32 [T], weight fp32 [T], logits or None)``; with
+    ``sort`` also ``offsets`` and ``sorted_rows`` as :func:`moe_sort` gives them (from the same launch for
+    steps of up to 32 tokens)."""
     _need(h32, "h32", torch.float32)
     _need(router_weight, "router_weight", torch.float32)
     T, H = h32.shape
@@ -437,8 +459,15 @@ def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: 
     weight = torch.empty((T,), dtype=torch.float32, device=h32.device)
     logits = torch.empty((T, E), dtype=torch.float32, device=h32.device) if want_logits else None
     scratch = _router_scratch(h32.device, E) if T <= 32 else None
+    offsets = sorted_rows = None
+    if sort:
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=h32.device)
+        sorted_rows = torch.empty((T,), dtype=torch.int32, device=h32.device)
     check(kernel("sharpi_router_top1")(h32.data_ptr(), router_weight.data_ptr(), T, H, E, 0, expert.data_ptr(),
-                                       weight.data_ptr(), _ptr(logits), _ptr(scratch), _stream()), "sharpi_router_top1")
+                                       weight.data_ptr(), _ptr(logits), _ptr(scratch), _ptr(offsets), _ptr(sorted_rows),
+                                       _stream()), "sharpi_router_top1")
+    if sort:
+        return expert, weight, logits, offsets, sorted_rows
     return expert, weight, logits
 
 
@@ -452,7 +481,7 @@ def _router_scratch(device, num_experts: int) -> torch.Tensor:
     key = (torch.device(device), num_experts)
     buf = _router_scratches.get(key)
     if buf is None:
-        buf = torch.zeros(32 * num_experts + 32, dtype=torch.float32, device=device)
+        buf = torch.zeros(32 * num_experts + 33, dtype=torch.float32, device=device)
         _router_scratches[key] = buf
     return buf
 

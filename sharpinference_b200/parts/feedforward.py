@@ -89,8 +89,7 @@ class MoESigmoidTop1(FeedForward):
                 self.shared.forward(ctx, h, out=y)
         else:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-        expert, weight, _ = ops.router_top1(h32, self.router)
-        offsets, sorted_rows = ops.moe_sort(expert, self.num_experts)
+        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
         if "router_choices" in ctx.extras:          # tracing: which expert every row went to
             ctx.extras["router_choices"].append(expert)
         if self._tensor_core and h.dtype == torch.bfloat16:

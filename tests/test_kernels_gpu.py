@@ -304,6 +304,18 @@ def test_router_top1(ops, T, H, E):
     assert torch.allclose(weight, p.max(dim=1).values, rtol=1e-6)
 
 
+@pytest.mark.parametrize("T,E", [(1, 16), (8, 16), (32, 128), (7, 3), (33, 5), (1200, 16)])
+def test_router_sorts_in_the_same_call(ops, T, E):
+    """With sort=True the rows come back sorted by expert: from the router's own launch for up to 32 tokens
+    (three calls in a row: the counters are left at zero), from the sort kernel otherwise."""
+    for seed in range(3):
+        h, wr = rnd(T, 640, seed=40 + seed), rnd(E, 640, scale=0.05, seed=50 + seed)
+        expert, weight, _, offsets, rows = ops.router_top1(h, wr, sort=True)
+        ref_offsets, ref_rows = ops.moe_sort(expert, E)
+        assert torch.equal(offsets, ref_offsets) and torch.equal(rows, ref_rows)
+        assert rows.cpu().tolist() == torch.argsort(expert.long().cpu(), stable=True).tolist()
+
+
 def test_router_first_of_equal_experts_wins(ops):
     h = torch.ones(2, 16, device=DEV)
     wr = torch.zeros(6, 16, device=DEV)
