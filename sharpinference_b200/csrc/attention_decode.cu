@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
     uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 16 * QLD);            // [warps][2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
     const int G = a.nq / a.nkv;
     const int groups = (G + 15) / 16;
     const int kvh = blockIdx.y / groups, hg = blockIdx.y % groups;
@@ -327,6 +328,7 @@ template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(DecodeArgs a) {
     __shared__ float w_s[MERGE_THREADS];
     __shared__ float scratch[32];
+    pdl_wait();
     const int ri = blockIdx.x, head = blockIdx.y;
     const int r = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[r];
@@ -369,8 +371,8 @@ static int launch_split(const CUtensorMap& map, const DecodeArgs& a, int R, int 
     }
     const int G = a.nq / a.nkv;
     dim3 grid(splits, a.nkv * ((G + 15) / 16), R);
-    attn_decode_split_kernel<D, TMA><<<grid, DEC_THREADS, SMEM, stream>>>(map, a);
-    SHARPI_CHECK_LAUNCH();
+    auto kern = attn_decode_split_kernel<D, TMA>;
+    SHARPI_LAUNCH_PDL(kern, grid, DEC_THREADS, SMEM, stream, map, a);
     return SHARPI_OK;
 }
 
@@ -387,8 +389,7 @@ static int launch_decode(const DecodeArgs& a, int R, int splits, long long pool_
         rc = launch_split<D, false>(map, a, R, splits, stream);
     }
     if (rc != SHARPI_OK) return rc;
-    attn_decode_merge_kernel<D><<<dim3(R, a.nq), MERGE_THREADS, 0, stream>>>(a);
-    SHARPI_CHECK_LAUNCH();
+    SHARPI_LAUNCH_PDL(attn_decode_merge_kernel<D>, dim3(R, a.nq), MERGE_THREADS, 0, stream, a);
     return SHARPI_OK;
 }
 

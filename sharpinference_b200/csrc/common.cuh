@@ -7,6 +7,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 #include <stdint.h>
 
 enum SharpiStatus : int {
@@ -27,6 +28,41 @@ enum SharpiDtype : int {
     do {                                                            \
         cudaError_t err__ = cudaGetLastError();                     \
         if (err__ != cudaSuccess) return SHARPI_LAUNCH_FAILED;      \
+    } while (0)
+
+// Programmatic dependent launch.  A kernel launched with SHARPI_LAUNCH_PDL may be started while the kernel
+// before it in the stream is still running, so that its launch and set-up overlap that kernel's tail; it
+// must call pdl_wait() before it reads or writes anything that an earlier kernel touches (every such kernel
+// calls it on every path, before any return, so completion of a kernel implies completion of those before
+// it).  Launched the plain way, pdl_wait() does nothing.  SHARPI_PDL=0 in the environment turns the
+// attribute off.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+static inline int sharpi_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("SHARPI_PDL");
+        enabled = (v && v[0] == '0') ? 0 : 1;
+    }
+    return enabled;
+}
+
+#define SHARPI_LAUNCH_PDL(kernel, grid, block, smem, stream, ...)                                  \
+    do {                                                                                           \
+        cudaLaunchConfig_t cfg__ = {};                                                             \
+        cfg__.gridDim = (grid);                                                                    \
+        cfg__.blockDim = (block);                                                                  \
+        cfg__.dynamicSmemBytes = (smem);                                                           \
+        cfg__.stream = (stream);                                                                   \
+        cudaLaunchAttribute attr__[1];                                                             \
+        attr__[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                         \
+        attr__[0].val.programmaticStreamSerializationAllowed = 1;                                  \
+        cfg__.attrs = attr__;                                                                      \
+        cfg__.numAttrs = sharpi_pdl_enabled() ? 1 : 0;                                             \
+        if (cudaLaunchKernelEx(&cfg__, kernel, __VA_ARGS__) != cudaSuccess) return SHARPI_LAUNCH_FAILED; \
     } while (0)
 
 typedef __nv_bfloat16 bf16;

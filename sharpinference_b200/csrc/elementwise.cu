@@ -47,49 +47,94 @@ SHARPI_API int sharpi_embed_gather(const int* ids, const void* table, int table_
 // ---------------------------------------------------------------------------------------
 constexpr int NORM_THREADS = 256;
 
-template <typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                   const float* __restrict__ w, float eps, const int* __restrict__ rows,
-                                   int H, TO* __restrict__ out, float* __restrict__ out32) {
+// The row is read in pieces of NORM_UNROLL elements per thread whose loads are all issued before the first
+// of them is used (a step of few rows is one block per row waiting for memory, nothing else), and kept in
+// shared memory for the second pass when it fits (CACHED).  A thread still adds its squares in ascending
+// order of the index, as a plain loop would.
+constexpr int NORM_UNROLL = 8;
+constexpr int NORM_CACHE_FLOATS = 12288;     // 48 KB
+
+template <typename TO, bool CACHED>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
+                   const int* __restrict__ rows, int H, TO* __restrict__ out, float* __restrict__ out32) {
     __shared__ float scratch[32];
+    extern __shared__ float row_s[];
+    pdl_wait();
     const int t = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[t] : t) * H;
     float* xr = x + src;
     const float* dr = delta ? delta + src : nullptr;
+    const bool write_back = dr && !rows;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
-        float v = xr[i];
-        if (dr) {
-            v += dr[i];
-            if (!rows) xr[i] = v;
+    for (int i0 = threadIdx.x; i0 < H; i0 += NORM_UNROLL * NORM_THREADS) {
+        float v[NORM_UNROLL], d[NORM_UNROLL];
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            v[k] = (i < H) ? xr[i] : 0.0f;
+            d[k] = (dr && i < H) ? dr[i] : 0.0f;
         }
-        ss += v * v;
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            if (i < H) {
+                if (dr) v[k] += d[k];
+                if (write_back) xr[i] = v[k];
+                if (CACHED) row_s[i] = v[k];
+                ss += v[k] * v[k];
+            }
+        }
     }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)H + eps);
     TO* orow = out + (size_t)t * H;
     float* o32 = out32 ? out32 + (size_t)t * H : nullptr;
-    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
-        float v = xr[i];
-        if (dr && rows) v += dr[i];
-        const float y = v * scale * w[i];
-        orow[i] = from_float<TO>(y);
-        if (o32) o32[i] = y;
+    for (int i0 = threadIdx.x; i0 < H; i0 += NORM_UNROLL * NORM_THREADS) {
+        float v[NORM_UNROLL], ww[NORM_UNROLL];
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            ww[k] = (i < H) ? w[i] : 0.0f;
+            if (CACHED) {
+                v[k] = (i < H) ? row_s[i] : 0.0f;      // this thread wrote it
+            } else {
+                v[k] = (i < H) ? xr[i] : 0.0f;
+                if (dr && rows && i < H) v[k] += dr[i];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NORM_UNROLL; ++k) {
+            const int i = i0 + k * NORM_THREADS;
+            if (i < H) {
+                const float y = v[k] * scale * ww[k];
+                orow[i] = from_float<TO>(y);
+                if (o32) o32[i] = y;
+            }
+        }
     }
+}
+
+template <typename TO>
+static int launch_norm(float* x, const float* delta, const float* w, float eps, const int* rows, int T, int H, TO* out,
+                       float* out32, cudaStream_t stream) {
+    if (H <= NORM_CACHE_FLOATS) {
+        auto kern = add_rmsnorm_kernel<TO, true>;
+        SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, (size_t)H * sizeof(float), stream, x, delta, w, eps, rows, H, out, out32);
+    } else {
+        auto kern = add_rmsnorm_kernel<TO, false>;
+        SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, 0, stream, x, delta, w, eps, rows, H, out, out32);
+    }
+    return SHARPI_OK;
 }
 
 SHARPI_API int sharpi_add_rmsnorm(float* x, const float* delta, const float* w, float eps, const int* rows,
                                   int T, int H, void* out, int out_dtype, float* out32, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0) return SHARPI_BAD_ARGUMENT;
-    if (out_dtype == SHARPI_F32)
-        add_rmsnorm_kernel<float><<<T, NORM_THREADS, 0, stream>>>(x, delta, w, eps, rows, H, (float*)out, out32);
-    else if (out_dtype == SHARPI_BF16)
-        add_rmsnorm_kernel<bf16><<<T, NORM_THREADS, 0, stream>>>(x, delta, w, eps, rows, H, (bf16*)out, out32);
-    else
-        return SHARPI_BAD_ARGUMENT;
-    SHARPI_CHECK_LAUNCH();
-    return SHARPI_OK;
+    if (out_dtype == SHARPI_F32) return launch_norm<float>(x, delta, w, eps, rows, T, H, (float*)out, out32, stream);
+    if (out_dtype == SHARPI_BF16) return launch_norm<bf16>(x, delta, w, eps, rows, T, H, (bf16*)out, out32, stream);
+    return SHARPI_BAD_ARGUMENT;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -115,6 +160,7 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, const float* __
 template <typename TO>
 __global__ void swiglu_vec4_kernel(const float* __restrict__ gate_up, const float* __restrict__ row_scale,
                                    const int* __restrict__ scale_rows, TO* __restrict__ out, int I) {
+    pdl_wait();
     const int m = blockIdx.x;
     const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (i >= I) return;
@@ -135,9 +181,9 @@ SHARPI_API int sharpi_swiglu(const float* gate_up, const float* row_scale, const
     if (I % 4 == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0) {
         dim3 grid4(M, (I / 4 + 255) / 256);
         if (out_dtype == SHARPI_F32)
-            swiglu_vec4_kernel<float><<<grid4, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (float*)out, I);
+            SHARPI_LAUNCH_PDL(swiglu_vec4_kernel<float>, grid4, 256, 0, stream, gate_up, row_scale, scale_rows, (float*)out, I);
         else if (out_dtype == SHARPI_BF16)
-            swiglu_vec4_kernel<bf16><<<grid4, 256, 0, stream>>>(gate_up, row_scale, scale_rows, (bf16*)out, I);
+            SHARPI_LAUNCH_PDL(swiglu_vec4_kernel<bf16>, grid4, 256, 0, stream, gate_up, row_scale, scale_rows, (bf16*)out, I);
         else
             return SHARPI_BAD_ARGUMENT;
         SHARPI_CHECK_LAUNCH();
@@ -170,6 +216,21 @@ SHARPI_API int sharpi_add(const float* a, const float* b, float* y, long long n,
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     add_kernel<<<(int)blocks, 256, 0, stream>>>(a, b, y, (size_t)n);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// The GPU's nanosecond clock into slot[index]: a marker between the launches of a stream, for timelines of a
+// step taken inside a captured graph, where host-side timing sees nothing.
+__global__ void timestamp_kernel(unsigned long long* slots, int index) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    slots[index] = t;
+}
+
+SHARPI_API int sharpi_timestamp(unsigned long long* slots, int index, cudaStream_t stream) {
+    if (!slots || index < 0) return SHARPI_BAD_ARGUMENT;
+    timestamp_kernel<<<1, 1, 0, stream>>>(slots, index);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }

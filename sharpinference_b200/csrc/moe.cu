@@ -174,6 +174,7 @@ router_top1_small_kernel(const float* __restrict__ h, const float* __restrict__ 
                          int* __restrict__ sorted_rows) {
     __shared__ float seg_s[ROUTER_SEGMENTS];
     __shared__ int last_s, sort_s;
+    pdl_wait();
     const int t = blockIdx.x, e = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
@@ -249,9 +250,8 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
     if (T <= 32 && scratch && E <= 65535) {
         float* logits = logits_out ? logits_out : reinterpret_cast<float*>(scratch);
         int* tickets = reinterpret_cast<int*>(reinterpret_cast<float*>(scratch) + (size_t)32 * E);
-        router_top1_small_kernel<<<dim3(T, E), ROUTER_SEGMENTS * 32, 0, stream>>>(h, wr, H, E, expert_id, expert_weight,
-                                                                                 logits, tickets, offsets, sorted_rows);
-        SHARPI_CHECK_LAUNCH();
+        SHARPI_LAUNCH_PDL(router_top1_small_kernel, dim3(T, E), ROUTER_SEGMENTS * 32, 0, stream, h, wr, H, E, expert_id,
+                          expert_weight, logits, tickets, offsets, sorted_rows);
         return SHARPI_OK;
     }
     // many tokens: eight share a block and its reads of the router rows; fewer: two, for more blocks

@@ -142,6 +142,7 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
 // d % 4 == 0, pairs (2j, 2j+1) or no rotation: lane l owns the four-element pieces l, l + 32, ...
 template <typename TO>
 __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
+    pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots = a.nq + 2 * a.nkv;
@@ -234,10 +235,9 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
         const long long blocks = (work + warps - 1) / warps;
         if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
         if (out_dtype == SHARPI_F32)
-            qkv_post_vec_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
+            SHARPI_LAUNCH_PDL(qkv_post_vec_kernel<float>, (unsigned)blocks, warps * 32, 0, stream, a);
         else
-            qkv_post_vec_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(a);
-        SHARPI_CHECK_LAUNCH();
+            SHARPI_LAUNCH_PDL(qkv_post_vec_kernel<bf16>, (unsigned)blocks, warps * 32, 0, stream, a);
         return SHARPI_OK;
     }
     const int warps = 4;

@@ -78,16 +78,71 @@ __device__ int row_argmax(const float* __restrict__ row, int V, ArgBest* scratch
 
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     __shared__ ArgBest scratch[32];
+    pdl_wait();
     const int r = blockIdx.x;
     const int best = row_argmax(logits + (size_t)r * V, V, scratch);
     if (threadIdx.x == 0) out[r] = best;
 }
 
-SHARPI_API int sharpi_argmax_rows(const float* logits, int R, int V, int* out, cudaStream_t stream) {
+// Few rows: one block per row would leave the GPU to a handful of blocks that wait for memory.  Then a row
+// is cut into ARGMAX_SLICES slices with a block each; the block that finishes last for a row (a ticket,
+// left at zero again) picks among the slices' candidates.  Ties still go to the lowest index.
+constexpr int ARGMAX_SLICES = 32;
+
+__global__ void argmax_rows_sliced_kernel(const float* __restrict__ logits, int V, int* __restrict__ out,
+                                          ArgBest* __restrict__ cand, int* __restrict__ tickets) {
+    __shared__ ArgBest scratch[32];
+    __shared__ int last_s;
+    pdl_wait();
+    const int r = blockIdx.y, sl = blockIdx.x;
+    const int per = (((V + ARGMAX_SLICES - 1) / ARGMAX_SLICES) + 3) & ~3;
+    const int begin = min(V, sl * per), end = min(V, begin + per);
+    const float* row = logits + (size_t)r * V;
+    ArgBest mine;
+    mine.v = -INFINITY;
+    mine.i = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (v > mine.v) {  // ascending i per thread: strict > keeps the lowest index
+            mine.v = v;
+            mine.i = i;
+        }
+    }
+    const ArgBest best = block_argmax(mine, scratch);
+    if (threadIdx.x == 0) {
+        cand[(size_t)r * ARGMAX_SLICES + sl] = best;
+        __threadfence();
+        last_s = (atomicAdd(&tickets[r], 1) == ARGMAX_SLICES - 1);
+        if (last_s) tickets[r] = 0;
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    ArgBest c;
+    c.v = -INFINITY;
+    c.i = 0x7fffffff;
+    if (threadIdx.x < ARGMAX_SLICES) {
+        const ArgBest* p = cand + (size_t)r * ARGMAX_SLICES + threadIdx.x;
+        c.v = __ldcg(&p->v);
+        c.i = __ldcg(&p->i);
+    }
+    const ArgBest all = block_argmax(c, scratch);
+    if (threadIdx.x == 0) out[r] = all.i == 0x7fffffff ? 0 : all.i;
+}
+
+// `scratch` (optional): 64 ints that are zero before the call (and after it), then 64 * 32 pairs of (float, int);
+// with it, calls for up to 64 rows cut every row over 32 blocks.
+SHARPI_API int sharpi_argmax_rows(const float* logits, int R, int V, int* out, void* scratch, cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (V <= 0) return SHARPI_BAD_ARGUMENT;
-    argmax_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, out);
-    SHARPI_CHECK_LAUNCH();
+    if (scratch && R <= 64 && V >= 4096) {
+        int* tickets = reinterpret_cast<int*>(scratch);
+        ArgBest* cand = reinterpret_cast<ArgBest*>(tickets + 64);
+        SHARPI_LAUNCH_PDL(argmax_rows_sliced_kernel, dim3(ARGMAX_SLICES, R), SAMPLE_THREADS, 0, stream, logits, V, out, cand,
+                          tickets);
+        return SHARPI_OK;
+    }
+    SHARPI_LAUNCH_PDL(argmax_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, out);
     return SHARPI_OK;
 }
 

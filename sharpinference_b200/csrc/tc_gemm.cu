@@ -151,6 +151,7 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);   // [0] expert, [1] first sorted row, [2] end row
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
 
     // ---- which tile is this CTA's ----------------------------------------------------------
     // Warp 0 looks the tile up: lane l reads the bounds of group e0 + l, the warp scans the tile counts, and
@@ -647,8 +648,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmPara
         configured = true;
     }
     dim3 grid(n_tiles, row_tiles, p.k_split);
-    tc_grouped_gemm_kernel<MODE, NT, WT><<<grid, TC_THREADS, Cfg::SMEM_BYTES, stream>>>(mw, ma, p);
-    SHARPI_CHECK_LAUNCH();
+    auto kern = tc_grouped_gemm_kernel<MODE, NT, WT>;
+    SHARPI_LAUNCH_PDL(kern, grid, TC_THREADS, Cfg::SMEM_BYTES, stream, mw, ma, p);
     return SHARPI_OK;
 }
 
@@ -708,6 +709,7 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
 // expert, so that TMA can fetch an expert's rows as one tile.
 __global__ void gather_rows_bf16_kernel(const uint4* __restrict__ in, const int* __restrict__ rows,
                                         uint4* __restrict__ out, int vec_per_row) {
+    pdl_wait();
     const int r = blockIdx.x;
     const uint4* src = in + (size_t)rows[r] * vec_per_row;
     uint4* dst = out + (size_t)r * vec_per_row;
@@ -718,7 +720,6 @@ SHARPI_API int sharpi_gather_rows_bf16(const void* in, const int* rows, void* ou
     if (R <= 0) return SHARPI_OK;
     if (K <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return SHARPI_UNALIGNED;
-    gather_rows_bf16_kernel<<<R, 128, 0, stream>>>((const uint4*)in, rows, (uint4*)out, K / 8);
-    SHARPI_CHECK_LAUNCH();
+    SHARPI_LAUNCH_PDL(gather_rows_bf16_kernel, R, 128, 0, stream, (const uint4*)in, rows, (uint4*)out, K / 8);
     return SHARPI_OK;
 }

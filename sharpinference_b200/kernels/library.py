@@ -32,6 +32,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_add_rmsnorm": ("elementwise", [P, P, P, F, P, I, I, P, I, P, P]),
     "sharpi_swiglu": ("elementwise", [P, P, P, P, I, I, I, P]),
     "sharpi_add": ("elementwise", [P, P, P, LL, P]),
+    "sharpi_timestamp": ("elementwise", [P, I, P]),
     "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, P]),
     "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
@@ -42,7 +43,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_moe_sort": ("moe", [P, I, I, P, P, P]),
     "sharpi_tc_grouped_gemm": ("tc_gemm", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
     "sharpi_gather_rows_bf16": ("tc_gemm", [P, P, P, I, I, P]),
-    "sharpi_argmax_rows": ("sampling", [P, I, I, P, P]),
+    "sharpi_argmax_rows": ("sampling", [P, I, I, P, P, P]),
     "sharpi_apply_penalties": ("sampling", [P, I, P, P, P, P, P, P, I, P]),
     "sharpi_add_logit_bias": ("sampling", [P, I, P, P, P, I, P]),
     "sharpi_sample_rows": ("sampling", [P, I, I, P, P, P, P, P, P, P, P]),

@@ -103,6 +103,14 @@ def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype, *, row_scale: Optional
     return out
 
 
+def timestamp(slots: torch.Tensor, index: int) -> None:
+    """Write the GPU's nanosecond clock into ``slots[index]`` (int64) at this point of the current stream."""
+    _need(slots, "slots", torch.int64)
+    if not 0 <= index < slots.numel():
+        raise KernelError(f"timestamp slot {index} outside 0 .. {slots.numel() - 1}")
+    check(kernel("sharpi_timestamp")(slots.data_ptr(), index, _stream()), "sharpi_timestamp")
+
+
 def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(a, "a", torch.float32)
     _need(b, "b", torch.float32)
@@ -324,8 +332,8 @@ def check_status(device) -> None:
         code = int(w.item())
         if code != 0:
             w.zero_()
-            for buf in _ticket_buffers.values():      # a kernel that gave up may have left counters behind
-                buf.zero_()
+            for buf in list(_ticket_buffers.values()) + list(_argmax_scratches.values()):
+                buf.zero_()               # a kernel that gave up may have left counters behind
             raise KernelError(f"a tensor-core kernel gave up (code {code}: 1 = wait for a free stage, 2 = for a loaded "
                               f"stage, 3 = for the accumulator, 4 = for a key/value copy, 5 = misaligned staging "
                               f"buffer, 6 = misaligned shared memory, 7 = for drained tensor memory, 11-18 = "
@@ -497,12 +505,23 @@ def moe_sort(expert_id: torch.Tensor, num_experts: int):
     return offsets, sorted_rows
 
 
+_argmax_scratches = {}
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the largest entry of every row (the lowest index among equals), int32 [R]."""
     _need(logits, "logits", torch.float32)
     R, V = logits.shape
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    check(kernel("sharpi_argmax_rows")(logits.data_ptr(), R, V, out.data_ptr(), _stream()), "sharpi_argmax_rows")
+    scratch = None
+    if R <= 64:       # few rows: every row is cut over 32 blocks; 64 counters (kept at zero), then the slices' candidates
+        key = (logits.device, torch.cuda.current_stream(logits.device).cuda_stream)
+        scratch = _argmax_scratches.get(key)
+        if scratch is None:
+            scratch = _argmax_scratches[key] = torch.zeros(64 + 64 * 32 * 2, dtype=torch.int32, device=logits.device)
+    check(kernel("sharpi_argmax_rows")(logits.data_ptr(), R, V, out.data_ptr(), _ptr(scratch), _stream()),
+          "sharpi_argmax_rows")
     return out
 
 

@@ -76,10 +76,15 @@ class MoESigmoidTop1(FeedForward):
         T = h.shape[0]
         if h32 is None:
             h32 = h.to(torch.float32)
-        # The shared expert and the routed ones meet only where the routed outputs are added: the shared
-        # expert runs on a second stream beside routing, sorting and the routed gate|up product (short
-        # kernels bound by latency beside long ones bound by memory), and the streams join before the
-        # routed down product adds into y.  Inside a graph capture this becomes a fork and a join.
+        # Routing, sorting and gathering are short kernels that everything routed waits for: they go first.
+        # Then the shared expert runs on a second stream beside the routed gate|up product (two streams of
+        # weights keep the memory system busier than one), and the streams join before the routed down
+        # product adds into the shared expert's output.  Inside a graph capture: a fork and a join.
+        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
+        if "router_choices" in ctx.extras:          # tracing: which expert every row went to
+            ctx.extras["router_choices"].append(expert)
+        tensor_core = self._tensor_core and h.dtype == torch.bfloat16
+        h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
         main = side = None
         if self.shared is not None:
             y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
@@ -89,11 +94,7 @@ class MoESigmoidTop1(FeedForward):
                 self.shared.forward(ctx, h, out=y)
         else:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
-        if "router_choices" in ctx.extras:          # tracing: which expert every row went to
-            ctx.extras["router_choices"].append(expert)
-        if self._tensor_core and h.dtype == torch.bfloat16:
-            h_sorted = ops.gather_rows_bf16(h, sorted_rows)
+        if tensor_core:
             act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                       row_scale=weight, scale_rows=sorted_rows)
             if side is not None:
