@@ -207,6 +207,74 @@ def long_context_run(ns, cfg, pk, pk_kind) -> int:
     return 0
 
 
+def timeline_run(ns, cfg) -> int:
+    """Where a decode step's time goes, measured inside the captured graph: every kernel wrapper and library
+    product of the step is bracketed by two marker kernels that write the GPU's clock; the table gives the
+    mean time between the markers per kind of call (a marker pair itself costs about 2 us, and calls on the
+    second stream overlap those on the first)."""
+    import collections
+
+    import torch
+
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams, StepEntry, build_random_model
+    from sharpinference_b200.kernels import ops
+    from sharpinference_b200.parts import linear as linear_mod
+
+    dev = torch.device("cuda:0")
+    B = ns.batch
+    model = build_random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
+    engine = Engine(model, dtype="bfloat16", device=dev,
+                    options=EngineOptions(page_size=64, max_cache_tokens=B * (ns.context + 128) + 256, max_batch=B,
+                                          max_tokens_per_step=max(B, 64)))
+    torch.manual_seed(0)
+    for g in engine.cache.groups:
+        g.kv.normal_(0.0, 1.0)
+    gen = torch.Generator().manual_seed(0)
+    greedy = SamplingParams(temperature=0.0, max_new_tokens=1 << 30)
+    ids = [inject_prefilled(engine, torch.randint(0, cfg.vocab_size, (ns.context - 20,), generator=gen).tolist(), greedy)
+           for _ in range(B)]
+    reqs = [engine._requests[i] for i in ids]
+    slots = torch.zeros(8192, dtype=torch.int64, device=dev)
+    events, state = [], {"n": 0}
+
+    def bracket(name, fn):
+        def inner(*a, **k):
+            i = state["n"]
+            state["n"] += 2
+            ops.timestamp(slots, i)
+            r = fn(*a, **k)
+            ops.timestamp(slots, i + 1)
+            events.append((name, i, i + 1))
+            return r
+        return inner
+
+    for name in ("embed_gather", "add_rmsnorm", "swiglu", "qkv_post", "attention_decode", "router_top1",
+                 "gather_rows_bf16", "tc_grouped_gemm"):
+        setattr(ops, name, bracket(name, getattr(ops, name)))
+    plain_call = linear_mod.Linear.__call__
+    linear_mod.Linear.__call__ = lambda self, a, out=None: bracket(
+        f"library product [{self.out_features} x {self.in_features}]", lambda: plain_call(self, a, out=out))()
+    last = [r.tokens[-1] for r in reqs]
+    per_step = []
+    for _ in range(6):                               # the first step runs eagerly, the second is captured, then replays
+        n0 = len(events)
+        logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
+        last = engine.sampler.sample(logits, [r.sampler for r in reqs])
+        per_step.append(events[n0:])
+    torch.cuda.synchronize()
+    t = slots.cpu().tolist()
+    captured = max(per_step[1:], key=len)            # the markers of the captured step hold the last replay's clocks
+    table = collections.OrderedDict()
+    for name, a, b in sorted(captured, key=lambda e: t[e[1]]):
+        table.setdefault(name, []).append((t[b] - t[a]) / 1e3)
+    first, final = min(t[a] for _, a, _ in captured), max(t[b] for _, _, b in captured)
+    print(f"decode step, batch {B}, context {ns.context}, {ns.layers} layers: {(final - first) / 1e3:.1f} us from the "
+          f"first marker to the last")
+    for name, v in table.items():
+        print(f"  {name:40s} calls {len(v):3d}   mean {sum(v) / len(v):7.1f} us   sum {sum(v):8.1f} us")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -223,6 +291,9 @@ def main() -> int:
                          "Maverick-sized layers (dense / 128 experts alternating), batch 64 at context 4096; long: 8 "
                          "Scout-sized layers, one 65536-token prompt prefilled in 2048-token portions, then 256 "
                          "decoded tokens")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the benchmark: a table of where one decode step's time goes, from clock "
+                         "markers inside the captured graph (use a few layers)")
     ns = ap.parse_args()
     if ns.preset == "maverick":
         defaults = ap.parse_args([])
@@ -253,6 +324,8 @@ def main() -> int:
     cfg = Llama4TextConfig.from_dict(dict(base, num_hidden_layers=ns.layers,
                                           no_rope_layers=[i for i in range(ns.layers) if (i + 1) % 4 == 0]))
     pk, pk_kind = peaks()
+    if ns.timeline:
+        return timeline_run(ns, cfg)
     if ns.preset == "long":
         return long_context_run(ns, cfg, pk, pk_kind)
     dev = torch.device("cuda:0")
