@@ -1,7 +1,8 @@
-"""Generality of the parts: a toy mixer with state of its own, defined here, is registered, built
-into a toy architecture and stepped through the unchanged framework; and a schedule that names a
-layer twice and lets a layer read another's cache (needs a GPU).  Nothing here is a model of
-anyone's: the toy parts exist to exercise the interfaces."""
+"""Generality of the parts: a toy mixer with state of its own, a toy feed-forward that routes rows
+between two sub-networks and a toy position encoding that is no rotation, all defined here, are
+registered, built into toy architectures and stepped through the unchanged framework; and a schedule
+that names a layer twice and lets a layer read another's cache (needs a GPU).  Nothing here is a
+model of anyone's: the toy parts exist to exercise the interfaces."""
 import json
 import os
 from dataclasses import asdict, dataclass
@@ -164,6 +165,155 @@ def test_toy_generation_through_the_scheduler(toy_folder):
         for tok in g:
             assert plain.greedy(toy_plain(toy_folder, seq)[-1]) == tok
             seq.append(tok)
+
+
+# ---------------------------------------------------------------------------------------
+# a feed-forward that routes, and a position encoding that adds instead of rotating
+# ---------------------------------------------------------------------------------------
+def define_routed_toy():
+    from sharpinference_b200.models.model import DecoderModel
+    from sharpinference_b200.parts import DenseSwiGLU, Linear, PagedAttention, PreNormBlock, RMSNorm
+    from sharpinference_b200.parts.base import FeedForward, PositionEncoding, make_part, register_part
+    from sharpinference_b200.registry import register_architecture
+
+    @register_part("position", "toy_additive")
+    class AdditiveWaves(PositionEncoding):
+        """q += amp * sin(pos * f), k += amp * cos(pos * f): positions enter by addition, not rotation."""
+        def __init__(self, freqs, amp):
+            self.freqs, self.amp = freqs, float(amp)
+
+        def apply(self, ctx, q, k):
+            angle = ctx.positions.to(torch.float32)[:, None] * self.freqs[None, :]          # [T, d]
+            q.add_(self.amp * torch.sin(angle)[:, None, :])
+            k.add_(self.amp * torch.cos(angle)[:, None, :])
+
+    @register_part("feed_forward", "toy_sign_route")
+    class SignRouted(FeedForward):
+        """Rows whose projection on a direction is positive go through one network, the others through
+        another; the output is scaled by tanh of the projection."""
+        wants_fp32_input = True
+
+        def __init__(self, *, direction, positive, negative):
+            self.direction, self.positive, self.negative = direction, positive, negative
+
+        def forward(self, ctx, h, h32=None):
+            h32 = h.float() if h32 is None else h32
+            score = h32 @ self.direction.float()
+            out = torch.zeros((h.shape[0], self.positive.down.out_features), dtype=torch.float32, device=h.device)
+            for net, rows in ((self.positive, (score > 0).nonzero().flatten()), (self.negative, (score <= 0).nonzero().flatten())):
+                if rows.numel():
+                    out[rows] = net.forward(ctx, h[rows].contiguous())
+            return out * torch.tanh(score)[:, None]
+
+    @dataclass(frozen=True)
+    class RoutedToyConfig:
+        vocab_size: int = 37
+        hidden_size: int = 24
+        intermediate_size: int = 40
+        num_heads: int = 3
+        num_kv_heads: int = 1
+        head_dim: int = 16
+        num_layers: int = 2
+        amp: float = 0.4
+        eps: float = 1e-4
+        architecture = "ToyRoutedForCausalLM"
+
+        @classmethod
+        def from_dict(cls, obj, where="config.json"):
+            return cls(**{k: obj[k] for k in cls.__dataclass_fields__ if k in obj})
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], **asdict(self)}
+
+    def build(c, weights):
+        act, H, I, d = weights.compute_dtype, c.hidden_size, c.intermediate_size, c.head_dim
+        freqs = 0.3 * torch.arange(1, d + 1, dtype=torch.float32)
+        freqs = freqs if weights.device.type == "meta" else freqs.to(weights.device)
+
+        def ffn(p):
+            return DenseSwiGLU(gate_up=Linear(weights.matrix(p + "gate_up.weight", (2 * I, H))),
+                               down=Linear(weights.matrix(p + "down.weight", (H, I))), act_dtype=act)
+
+        def norm(name):
+            return RMSNorm(weights.vector(name, (H,)), c.eps)
+
+        blocks = []
+        for i in range(c.num_layers):
+            p = f"l{i}."
+            mixer = PagedAttention(qkv=Linear(weights.matrix(p + "qkv.weight", ((c.num_heads + 2 * c.num_kv_heads) * d, H))),
+                                   out=Linear(weights.matrix(p + "o.weight", (H, c.num_heads * d))),
+                                   num_heads=c.num_heads, num_kv_heads=c.num_kv_heads, head_dim=d, mask="full",
+                                   position=make_part("position", "toy_additive", freqs=freqs, amp=c.amp), act_dtype=act)
+            routed = make_part("feed_forward", "toy_sign_route", direction=weights.vector(p + "route", (H,)),
+                               positive=ffn(p + "pos."), negative=ffn(p + "neg."))
+            blocks.append(PreNormBlock(mixer_norm=norm(p + "n1"), ffn_norm=norm(p + "n2"), ffn=routed, act_dtype=act, mixer=mixer))
+        return DecoderModel(embedding=weights.matrix("embed.weight", (c.vocab_size, H)), blocks=blocks,
+                            final_norm=norm("final.weight"), head=Linear(weights.matrix("head.weight", (c.vocab_size, H))),
+                            act_dtype=act, config=c)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedToyConfig, build)
+    return RoutedToyConfig
+
+
+def routed_toy_plain(folder, toks, amp=None):
+    """Whole-sequence statement of the routed toy model in float64; also the smallest |routing score|."""
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as fh:
+        c = json.load(fh)
+    if amp is not None:
+        c["amp"] = amp
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    nq, nkv, d, S, I = c["num_heads"], c["num_kv_heads"], c["head_dim"], len(toks), c["intermediate_size"]
+    x = w["embed.weight"][torch.tensor(toks)]
+    angle = torch.arange(S, dtype=torch.float64)[:, None] * (0.3 * torch.arange(1, d + 1, dtype=torch.float32)).double()[None, :]
+    margin = float("inf")
+    for i in range(c["num_layers"]):
+        p = f"l{i}."
+        h = plain.rms_norm(x, w[p + "n1"], c["eps"])
+        qkv = h @ w[p + "qkv.weight"].T
+        q = qkv[:, : nq * d].reshape(S, nq, d) + c["amp"] * torch.sin(angle)[:, None, :]
+        k = qkv[:, nq * d: (nq + nkv) * d].reshape(S, nkv, d) + c["amp"] * torch.cos(angle)[:, None, :]
+        v = qkv[:, (nq + nkv) * d:].reshape(S, nkv, d)
+        x = x + plain.attention_scores(q, k, v, plain.visible("full", 0, S)) @ w[p + "o.weight"].T
+        h = plain.rms_norm(x, w[p + "n2"], c["eps"])
+        score = h @ w[p + "route"]
+        margin = min(margin, float(score.abs().min()))
+        y = torch.zeros_like(x)
+        for name, rows in (("pos.", score > 0), ("neg.", score <= 0)):
+            gu = h[rows] @ w[p + name + "gate_up.weight"].T
+            y[rows] = (plain.silu(gu[:, :I]) * gu[:, I:]) @ w[p + name + "down.weight"].T
+        x = x + y * torch.tanh(score)[:, None]
+    return plain.rms_norm(x, w["final.weight"], c["eps"]) @ w["head.weight"].T, margin
+
+
+def test_toy_routing_feed_forward_and_additive_positions(tmp_path):
+    """A feed-forward that routes rows and a position encoding that is no rotation, defined in this file,
+    run through the unchanged engine: whole, in portions and mixed with page reuse, against the plain
+    statement.  (float32: a routing score near zero may fall the other way in bfloat16.)"""
+    from sharpinference_b200 import Engine, EngineOptions, write_random_model
+    from sharpinference_b200.registry import unregister_architecture
+    Cfg = define_routed_toy()
+    try:
+        folder = str(tmp_path / "routed")
+        write_random_model(Cfg(), folder, seed=5, std=0.2, norm_std=0.1)
+        reqs = {f"q{i}": traces.random_tokens(37, n, seed=3 * n) for i, n in enumerate([33, 6, 45, 12])}
+        ref, margins = {}, []
+        for rid, toks in reqs.items():
+            ref[rid], m = routed_toy_plain(folder, toks)
+            margins.append(m)
+        assert min(margins) > 1e-4          # no row sits on the routing boundary
+        for cut in (traces.whole, traces.portions, lambda r: traces.mixed(r, max_live=3)):
+            steps = cut(reqs)
+            eng = Engine(folder, dtype="float32", device=DEV,
+                         options=EngineOptions(page_size=4, max_cache_tokens=traces.max_tokens(steps), max_batch=3))
+            got = traces.replay(eng, steps)
+            err, where = traces.worst_error(got, ref)
+            assert err < 2e-5, (err, where)
+        # the encoding is really applied: without it the plain statement gives other logits
+        without, _ = routed_toy_plain(folder, reqs["q0"], amp=0.0)
+        assert float((without - ref["q0"]).abs().max()) > 1e-3
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
 
 
 # ---------------------------------------------------------------------------------------
