@@ -224,8 +224,8 @@ def timeline_run(ns, cfg) -> int:
     B = ns.batch
     model = build_random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
     engine = Engine(model, dtype="bfloat16", device=dev,
-                    options=EngineOptions(page_size=64, max_cache_tokens=B * (ns.context + 128) + 256, max_batch=B,
-                                          max_tokens_per_step=max(B, 64)))
+                    options=EngineOptions(page_size=64, max_cache_tokens=B * (ns.context + 128) + 256 + ns.prefill_tokens, max_batch=B + 1,
+                                          max_tokens_per_step=max(B, 64, ns.prefill_tokens)))
     torch.manual_seed(0)
     for g in engine.cache.groups:
         g.kv.normal_(0.0, 1.0)
@@ -270,6 +270,27 @@ def timeline_run(ns, cfg) -> int:
     first, final = min(t[a] for _, a, _ in captured), max(t[b] for _, _, b in captured)
     print(f"decode step, batch {B}, context {ns.context}, {ns.layers} layers: {(final - first) / 1e3:.1f} us from the "
           f"first marker to the last")
+    for name, v in table.items():
+        print(f"  {name:40s} calls {len(v):3d}   mean {sum(v) / len(v):7.1f} us   sum {sum(v):8.1f} us")
+
+    # a prompt portion (not captured: the host launches every kernel, and is ahead of the device after the first few)
+    for name in ("attention_prefill", "attention_prefill_tc"):
+        setattr(ops, name, bracket(name, getattr(ops, name)))
+    prompt = torch.randint(0, cfg.vocab_size, (ns.prefill_tokens,), generator=gen).tolist()
+    for _ in range(3):
+        n0 = len(events)
+        engine.open_request("p")
+        engine.forward_step([StepEntry("p", prompt, [len(prompt) - 1])])
+        engine.close_request("p")
+        torch.cuda.synchronize()
+        last_events = events[n0:]
+    t = slots.cpu().tolist()
+    table = collections.OrderedDict()
+    for name, a, b in sorted(last_events, key=lambda e: t[e[1]]):
+        table.setdefault(name, []).append((t[b] - t[a]) / 1e3)
+    first, final = min(t[a] for _, a, _ in last_events), max(t[b] for _, _, b in last_events)
+    print(f"prompt portion of {ns.prefill_tokens} tokens, {ns.layers} layers: {(final - first) / 1e3:.1f} us from the first "
+          f"marker to the last")
     for name, v in table.items():
         print(f"  {name:40s} calls {len(v):3d}   mean {sum(v) / len(v):7.1f} us   sum {sum(v):8.1f} us")
     return 0

@@ -254,7 +254,8 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
                           expert_weight, logits, tickets, offsets, sorted_rows);
         return SHARPI_OK;
     }
-    // many tokens: eight share a block and its reads of the router rows; fewer: two, for more blocks
+    // many tokens: eight share a block and its reads of the router rows (four with sixteen experts to a pass
+    // measured slower: the rows are re-read from L2 once per block); fewer: two, for more blocks
     int rc;
     if (T >= 1024 && (size_t)(ROUTER_SEGMENTS + 1) * 8 * E * sizeof(float) <= 200 * 1024)
         rc = launch_router<8, 4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);

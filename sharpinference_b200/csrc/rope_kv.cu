@@ -139,75 +139,101 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float4 v) {
     *reinterpret_cast<uint2*>(dst) = w;
 }
 
-// d % 4 == 0, pairs (2j, 2j+1) or no rotation: lane l owns the four-element pieces l, l + 32, ...
-template <typename TO>
+// d % 4 == 0, pairs (2j, 2j+1) or no rotation: lane l owns the four-element pieces l, l + 32, ... of a head.
+// A warp serves QKV_SLOTS consecutive heads (q, k or v) of one token: their loads are issued together, and
+// the sines and cosines of the lane's pairs, which depend on the token alone, are taken once.
+constexpr int QKV_SLOTS = 4;
+
+template <typename TO, int MAX_PIECES>      // MAX_PIECES * 128 >= head size
 __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
     pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots = a.nq + 2 * a.nkv;
+    const int groups = (slots + QKV_SLOTS - 1) / QKV_SLOTS;
     const long long work = (long long)blockIdx.x * warps_per_block + warp;
-    if (work >= (long long)a.T * slots) return;
-    const int t = (int)(work / slots);
-    const int slot = (int)(work % slots);
+    if (work >= (long long)a.T * groups) return;
+    const int t = (int)(work / groups);
+    const int slot0 = (int)(work % groups) * QKV_SLOTS;
     const int d = a.d, n4 = d >> 2;
-    const float4* __restrict__ src = reinterpret_cast<const float4*>(a.qkv + (size_t)t * slots * d + (size_t)slot * d);
-    constexpr int MAX_PIECES = 4;        // head sizes up to 512
-    float4 x[MAX_PIECES];
+    float4 x[QKV_SLOTS][MAX_PIECES];
 #pragma unroll
-    for (int r = 0; r < MAX_PIECES; ++r) {
-        const int i = lane + 32 * r;
-        x[r] = (i < n4) ? __ldg(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < QKV_SLOTS; ++s) {
+        const float4* __restrict__ src =
+            reinterpret_cast<const float4*>(a.qkv + (size_t)t * slots * d + (size_t)(slot0 + s) * d);
+#pragma unroll
+        for (int r = 0; r < MAX_PIECES; ++r) {
+            const int i = lane + 32 * r;
+            x[s][r] = (slot0 + s < slots && i < n4) ? __ldg(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
     }
     const int pos = a.positions[t];
-    const bool is_q = slot < a.nq;
-    const bool is_k = !is_q && slot < a.nq + a.nkv;
-
-    TO* dst;
-    if (is_q) {
-        dst = (TO*)a.q_out + ((size_t)t * a.nq + slot) * d;
-    } else {
-        if (!a.write_kv) return;
-        const int head = is_k ? slot - a.nq : slot - a.nq - a.nkv;
-        const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
-        if (page < 0) return;  // the host checks before the launch that every written position has a page
-        const size_t plane = (size_t)a.nkv * a.page_size * d;
-        dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
-              ((size_t)head * a.page_size + (pos % a.page_size)) * d;
-    }
-    float scale = 1.0f;
-    if (is_q || is_k) {
-        float ss = 0.0f;
+    const bool rotate = a.pairing != ROPE_NONE && a.inv_freq;
+    float cs0[MAX_PIECES], sn0[MAX_PIECES], cs1[MAX_PIECES], sn1[MAX_PIECES];
+    if (rotate && slot0 < a.nq + a.nkv) {               // the group holds at least one q or k head
 #pragma unroll
         for (int r = 0; r < MAX_PIECES; ++r) {
             const int i = lane + 32 * r;
             if (i < n4) {
-                if (a.pairing != ROPE_NONE && a.inv_freq) {
-                    const float2 f = __ldg(reinterpret_cast<const float2*>(a.inv_freq) + i);   // pairs 2i, 2i + 1
-                    float sn, cs;
-                    sincosf((float)pos * f.x, &sn, &cs);
-                    const float r0 = x[r].x * cs - x[r].y * sn, r1 = x[r].x * sn + x[r].y * cs;
-                    sincosf((float)pos * f.y, &sn, &cs);
-                    const float r2 = x[r].z * cs - x[r].w * sn, r3 = x[r].z * sn + x[r].w * cs;
-                    x[r] = make_float4(r0, r1, r2, r3);
-                }
-                ss += x[r].x * x[r].x + x[r].y * x[r].y;
-                ss += x[r].z * x[r].z + x[r].w * x[r].w;
+                const float2 f = __ldg(reinterpret_cast<const float2*>(a.inv_freq) + i);   // pairs 2i, 2i + 1
+                sincosf((float)pos * f.x, &sn0[r], &cs0[r]);
+                sincosf((float)pos * f.y, &sn1[r], &cs1[r]);
             }
         }
-        if (a.l2_eps >= 0.0f) {
-            ss = warp_sum(ss);
-            scale = 1.0f / sqrtf(ss / (float)d + a.l2_eps);
-        }
-        if (is_q && a.temp_floor_scale > 0.0f) {
-            const float steps = floorf(((float)pos + 1.0f) / a.temp_floor_scale);
-            scale *= 1.0f + a.temp_attn_scale * log1pf(steps);
-        }
+    }
+    // where this token's keys and values go
+    int page = -1;
+    if (a.write_kv && slot0 + QKV_SLOTS > a.nq)
+        page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
+    const size_t plane = (size_t)a.nkv * a.page_size * d;
+    float temp = 1.0f;
+    if (a.temp_floor_scale > 0.0f && slot0 < a.nq) {
+        const float steps = floorf(((float)pos + 1.0f) / a.temp_floor_scale);
+        temp = 1.0f + a.temp_attn_scale * log1pf(steps);
     }
 #pragma unroll
-    for (int r = 0; r < MAX_PIECES; ++r) {
-        const int i = lane + 32 * r;
-        if (i < n4) store4<TO>(dst + 4 * i, make_float4(x[r].x * scale, x[r].y * scale, x[r].z * scale, x[r].w * scale));
+    for (int s = 0; s < QKV_SLOTS; ++s) {
+        const int slot = slot0 + s;
+        if (slot >= slots) break;
+        const bool is_q = slot < a.nq;
+        const bool is_k = !is_q && slot < a.nq + a.nkv;
+        TO* dst;
+        if (is_q) {
+            dst = (TO*)a.q_out + ((size_t)t * a.nq + slot) * d;
+        } else {
+            if (page < 0) continue;      // no cache write for this layer (the host checks that written positions have pages)
+            const int head = is_k ? slot - a.nq : slot - a.nq - a.nkv;
+            dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
+                  ((size_t)head * a.page_size + (pos % a.page_size)) * d;
+        }
+        float scale = 1.0f;
+        if (is_q || is_k) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int r = 0; r < MAX_PIECES; ++r) {
+                const int i = lane + 32 * r;
+                if (i < n4) {
+                    if (rotate) {
+                        const float4 v = x[s][r];
+                        x[s][r] = make_float4(v.x * cs0[r] - v.y * sn0[r], v.x * sn0[r] + v.y * cs0[r],
+                                              v.z * cs1[r] - v.w * sn1[r], v.z * sn1[r] + v.w * cs1[r]);
+                    }
+                    ss += x[s][r].x * x[s][r].x + x[s][r].y * x[s][r].y;
+                    ss += x[s][r].z * x[s][r].z + x[s][r].w * x[s][r].w;
+                }
+            }
+            if (a.l2_eps >= 0.0f) {
+                ss = warp_sum(ss);
+                scale = 1.0f / sqrtf(ss / (float)d + a.l2_eps);
+            }
+            if (is_q) scale *= temp;
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_PIECES; ++r) {
+            const int i = lane + 32 * r;
+            if (i < n4)
+                store4<TO>(dst + 4 * i, make_float4(x[s][r].x * scale, x[s][r].y * scale, x[s][r].z * scale, x[s][r].w * scale));
+        }
     }
 }
 
@@ -228,16 +254,24 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
     a.temp_attn_scale = temp_attn_scale; a.temp_floor_scale = temp_floor_scale; a.write_kv = write_kv;
     if (out_dtype != SHARPI_F32 && out_dtype != SHARPI_BF16) return SHARPI_BAD_ARGUMENT;
     const long long work = (long long)T * (nq + 2 * nkv);
+    const long long vec_work = (long long)T * ((nq + 2 * nkv + QKV_SLOTS - 1) / QKV_SLOTS);
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                            reinterpret_cast<uintptr_t>(kv_base) | reinterpret_cast<uintptr_t>(inv_freq);
     if (d % 4 == 0 && a.pairing != ROPE_HALVES && (ptrs & 15) == 0) {
         const int warps = 8;
-        const long long blocks = (work + warps - 1) / warps;
+        const long long blocks = (vec_work + warps - 1) / warps;
         if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
-        if (out_dtype == SHARPI_F32)
-            SHARPI_LAUNCH_PDL(qkv_post_vec_kernel<float>, (unsigned)blocks, warps * 32, 0, stream, a);
-        else
-            SHARPI_LAUNCH_PDL(qkv_post_vec_kernel<bf16>, (unsigned)blocks, warps * 32, 0, stream, a);
+#define QKV_CASE(TO, P)                                                                     \
+    do {                                                                                    \
+        auto kern = qkv_post_vec_kernel<TO, P>;                                             \
+        SHARPI_LAUNCH_PDL(kern, (unsigned)blocks, warps * 32, 0, stream, a);                \
+    } while (0)
+        if (out_dtype == SHARPI_F32) {
+            if (d <= 128) QKV_CASE(float, 1); else if (d <= 256) QKV_CASE(float, 2); else QKV_CASE(float, 4);
+        } else {
+            if (d <= 128) QKV_CASE(bf16, 1); else if (d <= 256) QKV_CASE(bf16, 2); else QKV_CASE(bf16, 4);
+        }
+#undef QKV_CASE
         return SHARPI_OK;
     }
     const int warps = 4;

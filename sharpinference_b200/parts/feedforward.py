@@ -53,6 +53,9 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
 class MoESigmoidTop1(FeedForward):
     wants_fp32_input = True
     graph_safe = True
+    # Steps of up to this many rows run the shared expert on a second stream beside the routed experts.  In
+    # larger steps every product fills the GPU by itself.
+    FORK_UP_TO = 256
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
                  shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):
@@ -86,7 +89,9 @@ class MoESigmoidTop1(FeedForward):
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
         h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
         main = side = None
-        if self.shared is not None:
+        if self.shared is not None and T > self.FORK_UP_TO:
+            y = self.shared.forward(ctx, h)
+        elif self.shared is not None:
             y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
             main, side = torch.cuda.current_stream(h.device), _side_stream(h.device)
             side.wait_stream(main)
