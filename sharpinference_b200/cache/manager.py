@@ -104,6 +104,8 @@ class RequestCache:
     length: int = 0                                             # positions committed so far
     tables: Dict[int, List[int]] = field(default_factory=dict)  # group -> page per logical block (-1: none)
     reserved_until: int = 0                                     # positions covered by pages (>= length)
+    version: int = 0                                            # changes with every change of the tables; never repeats
+    released: Dict[int, int] = field(default_factory=dict)      # group -> blocks below this were given back
 
 
 class CacheManager:
@@ -182,9 +184,13 @@ class CacheManager:
         slot = self.state_slots.take()
         for state in self._entry_state.values():
             state[slot].zero_()
-        rc = RequestCache(request_id, slot, tables={g.index: [] for g in self.groups})
+        rc = RequestCache(request_id, slot, tables={g.index: [] for g in self.groups}, version=self._next_version())
         self.requests[request_id] = rc
         return rc
+
+    def _next_version(self) -> int:
+        self._versions = getattr(self, "_versions", 0) + 1
+        return self._versions
 
     def get(self, request_id: Hashable) -> RequestCache:
         try:
@@ -244,9 +250,11 @@ class CacheManager:
                 table = rc.tables[g.index]
                 while len(table) < blocks_end:
                     table.append(-1)
+                    rc.version = self._next_version()
                 for b in range(first, blocks_end):
                     if table[b] < 0:
                         table[b] = g.pages.take()
+                        rc.version = self._next_version()
             rc.reserved_until = max(rc.reserved_until, end)
 
     def commit(self, request_id: Hashable, n_new: int) -> None:
@@ -261,10 +269,14 @@ class CacheManager:
                 continue
             lo = g.lowest_needed(rc.length)
             table = rc.tables[g.index]
-            for b in range(min(lo // self.page_size, len(table))):
+            upto = min(lo // self.page_size, len(table))
+            for b in range(rc.released.get(g.index, 0), upto):       # what lies below was given back before
                 if table[b] >= 0:
                     g.pages.give_back(table[b])
                     table[b] = -1
+                    rc.version = self._next_version()
+            if upto > rc.released.get(g.index, 0):
+                rc.released[g.index] = upto
 
     # -- accounting ----------------------------------------------------------------------
     def free_pages(self) -> Dict[int, int]:

@@ -144,6 +144,8 @@ class Engine:
             self.stats["decode_tokens" if e.count == 1 and e.start >= len(e.request.prompt) else "prefill_tokens"] += e.count
         logits = self.runner.run(entries)
         sampled = self.sampler.sample(logits, [r.sampler for r in wanting]) if wanting else []
+        if wanting:
+            self.runner.flush_status()        # the sampled tokens are on the host, so the step is over: no wait
         self.stats["steps"] += 1
         for req in self.scheduler.complete(plan, sampled):
             outputs.append(self._output(req))
@@ -168,6 +170,7 @@ class Engine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         while self.has_unfinished:
             self.step()
+        self.runner.flush_status()
         outs = [self._requests[i] for i in ids]
         for r in outs:
             if r.finish_reason == "cache_full":

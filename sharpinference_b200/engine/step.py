@@ -60,6 +60,7 @@ class StepRunner:
         # after every step, read the word in which a tensor-core kernel records a wait that gave up
         # (a 4-byte copy; the step's result is read by the host right after anyway)
         self.check_kernel_status = True
+        self._status_host, self._status_event, self._status_pending = None, None, False
         self.last_router_choices: List[torch.Tensor] = []
         # Decode-only steps are launch-bound at small batches, so they are captured once per shape
         # (requests, wanted rows, block-table width) as a CUDA graph and replayed; the step's metadata
@@ -200,11 +201,35 @@ class StepRunner:
             decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
         )
 
+    # The word in which a tensor-core kernel records a wait that gave up is copied to pinned host memory
+    # behind every step and looked at when the next step begins (or when flush_status is called): by then
+    # the caller has read the step's result, so the copy is there and nobody waits for it.  A kernel that
+    # gave up therefore raises at the next step, or at the flush that ends a run.
+    def _note_status(self) -> None:
+        if self.device.type != "cuda":
+            return
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(ops.status_word(self.device), non_blocking=True)
+        self._status_event.record()
+        self._status_pending = True
+
+    def flush_status(self) -> None:
+        """Raise if a kernel of an earlier step gave up on a wait (waits for that step to finish)."""
+        if not self._status_pending:
+            return
+        self._status_pending = False
+        self._status_event.synchronize()
+        if int(self._status_host[0]) != 0:
+            ops.check_status(self.device)           # raises, and puts the word and the counters back to zero
+
     @torch.no_grad()
     def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step.  Returns float32 logits ``[wanted, vocab]`` on the device, in the order of
         the entries and of each entry's ``want`` (None if nothing was wanted).  Raises
         :class:`OutOfPages` before anything ran if the pages for the step cannot all be had."""
+        self.flush_status()
         self.validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
         logits, done, num_tokens = None, False, sum(len(e.tokens) for e in entries)
@@ -217,7 +242,7 @@ class StepRunner:
             logits = self.model.forward(ctx)
             self.last_router_choices = ctx.extras.get("router_choices", [])
         if self.check_kernel_status:
-            ops.check_status(self.device)
+            self._note_status()
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
@@ -247,13 +272,45 @@ class StepRunner:
             self._graphs[key] = rec
         else:
             rec["copied"].synchronize()              # the previous copy out of the pinned buffer is over
-            self.build_context(entries, width=width, buffers=(rec["host"], rec["dev"]))
+            self._refresh_decode(rec, entries, width)
             rec["copied"].record()
         rec["graph"].replay()
         library.launch_count += rec["launches"]     # the replay launches what the capture recorded
         self.graph_replays += 1
         self.last_router_choices = []
         return True, rec["logits"]
+
+    def _refresh_decode(self, rec: dict, entries: Sequence[StepEntry], width: int) -> None:
+        """The static buffer of a captured decode step, brought up to date.  While the same requests decode
+        with the same wanted places, only what moves is rewritten: token ids, positions, and the block-table
+        rows of requests whose tables changed (a new page, a page given back).  Anything else lays the whole
+        buffer out again."""
+        cache = self.cache
+        ids = tuple(e.request_id for e in entries)
+        wants = tuple(tuple(e.want) for e in entries)
+        if rec.get("ids") != ids or rec.get("wants") != wants:
+            self.build_context(entries, width=width, buffers=(rec["host"], rec["dev"]))
+            rec["ids"], rec["wants"] = ids, wants
+            rec["versions"] = [cache.requests[i].version for i in ids]
+            return
+        hv, offsets, B = rec["host"].numpy(), rec["offsets"], len(ids)
+        starts = [cache.requests[i].length for i in ids]
+        hv[offsets[0]:offsets[0] + B] = [e.tokens[0] for e in entries]
+        hv[offsets[1]:offsets[1] + B] = starts                    # a decode row's position is its request's length
+        hv[offsets[3]:offsets[3] + B] = starts
+        versions = rec["versions"]
+        for b, rid in enumerate(ids):
+            rc = cache.requests[rid]
+            if rc.version != versions[b]:
+                versions[b] = rc.version
+                for gi, g in enumerate(cache.groups):
+                    t = rc.tables[g.index]
+                    if len(t) > width:
+                        raise StepError(f"block tables need {len(t)} columns, the buffer has {width}")
+                    o = int(offsets[7 + gi]) + b * width
+                    hv[o:o + len(t)] = t
+                    hv[o + len(t):o + width] = -1
+        rec["dev"].copy_(rec["host"], non_blocking=True)
 
     def _capture(self, entries: Sequence[StepEntry], width: int) -> dict:
         B, R = len(entries), sum(len(e.want) for e in entries)
@@ -272,5 +329,8 @@ class StepRunner:
         library.launch_count = before                # recorded, not run: replays do the counting
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
+        ids = tuple(e.request_id for e in entries)
         return {"graph": graph, "host": host, "dev": dev, "ctx": ctx, "logits": logits, "copied": copied,
-                "launches": launches}
+                "launches": launches, "offsets": [int(o) for o in self._layout(B, B, R, width, 0, B)],
+                "ids": ids, "wants": tuple(tuple(e.want) for e in entries),
+                "versions": [self.cache.requests[i].version for i in ids]}
