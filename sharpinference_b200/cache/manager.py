@@ -213,6 +213,9 @@ class CacheManager:
         """Pages each group must still take so that positions ``[length, length + n_new)`` can be written."""
         rc = self.get(request_id)
         end = rc.length + n_new
+        if rc.length % self.page_size and (end - 1) // self.page_size == (rc.length - 1) // self.page_size:
+            # everything falls into the block that holds the last committed position, which has its pages
+            return dict.fromkeys((g.index for g in self.groups), 0)
         need = {}
         blocks_end = (end + self.page_size - 1) // self.page_size
         for g in self.groups:
@@ -244,6 +247,9 @@ class CacheManager:
         for request_id, n_new in wants:
             rc = self.get(request_id)
             end = rc.length + n_new
+            if rc.length % self.page_size and (end - 1) // self.page_size == (rc.length - 1) // self.page_size:
+                rc.reserved_until = max(rc.reserved_until, end)      # the pages are there already
+                continue
             blocks_end = (end + self.page_size - 1) // self.page_size
             first = rc.length // self.page_size
             for g in self.groups:

@@ -137,7 +137,7 @@ class Engine:
             return outputs
         entries, wanting = [], []
         for e in plan.entries:
-            toks = e.request.tokens[e.start:e.start + e.count]
+            toks = e.request.token_slice(e.start, e.count)
             entries.append(StepEntry(e.request.request_id, toks, [e.count - 1] if e.want_last else []))
             if e.want_last:
                 wanting.append(e.request)

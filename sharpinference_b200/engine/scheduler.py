@@ -51,6 +51,16 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.generated
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """``tokens[start:start + count]`` without building the whole list (a decode step asks for one token
+        of a sequence that may be very long)."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.generated[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.generated[:start + count - n]
+
     @property
     def pending(self) -> int:
         """Tokens not yet run: the rest of the prompt, or the one token sampled last."""
