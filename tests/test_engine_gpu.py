@@ -85,6 +85,56 @@ def test_logits_equal_the_plain_implementation(model_dirs, expected, name, cut, 
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
 
 
+# The shapes of the large models in small: head size 128 with five query heads to a kv head, pages of 64
+# positions, a chunk of 512, the Scout rope scaling, and a prompt long enough (1400 rows in one step) for the
+# kernels that only large steps reach: attention tiles of 128 rows on tcgen05, the persistent grouped product,
+# two weight tiles per CTA in the down product.
+LARGE_SHAPES = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 1000, "hidden_size": 640, "num_hidden_layers": 4, "num_attention_heads": 10,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 384, "intermediate_size_mlp": 512,
+    "num_local_experts": 4, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
+                     "original_max_position_embeddings": 8192},
+    "no_rope_layers": [3], "attention_chunk_size": 512, "use_qk_norm": True, "attn_temperature_tuning": True,
+    "floor_scale": 512, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+
+
+@pytest.fixture(scope="module")
+def large_shapes(tmp_path_factory):
+    from sharpinference_b200.weights import write_random_model
+    folder = str(tmp_path_factory.mktemp("large_shapes"))
+    write_random_model(dict(LARGE_SHAPES), folder, 4, std=0.03, norm_std=0.1)
+    reqs = {f"L{i}": traces.random_tokens(1000, n, seed=31 * i + n) for i, n in enumerate([1400, 300, 77, 650])}
+    return folder, reqs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "mixed"])
+def test_large_model_shapes_in_small(large_shapes, cut, dtype):
+    from sharpinference_b200 import Engine, EngineOptions
+    folder, reqs = large_shapes
+    steps = CUTS[cut](reqs)
+    engine = Engine(folder, dtype=dtype, device="cuda:0",
+                    options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8))
+    if dtype == "bfloat16":
+        assert engine.runner.attention_tile == 128          # the tcgen05 attention kernel serves the prompts
+    routing = {} if dtype == "bfloat16" else None
+    got = traces.replay(engine, steps, routing)
+    if routing is None:
+        cfg, w = plain.load_folder(folder)
+        ref, flips = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}, 0
+    else:
+        ref, flips = plain_under_engine_routing(folder, reqs, routing)
+    err, where = traces.worst_error(got, ref)
+    print(f"large shapes {cut} {dtype}: worst relative error {err:.3e} at {where}; near-tie expert choices: {flips}")
+    assert err < TOL[dtype], f"worst error {err:.3e} at {where}"
+    engine.cache.check_invariants()
+    assert all(g.pages.held_count == 0 for g in engine.cache.groups)
+
+
 @pytest.mark.parametrize("name", list(TINY))
 def test_float32_cuts_agree_with_each_other_tightly(model_dirs, name):
     """In 32-bit every kernel sums in an order that depends on the row alone, so a row's logits
