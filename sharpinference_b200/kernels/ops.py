@@ -332,7 +332,7 @@ def check_status(device) -> None:
         code = int(w.item())
         if code != 0:
             w.zero_()
-            for buf in list(_ticket_buffers.values()) + list(_argmax_scratches.values()):
+            for buf in list(_ticket_buffers.values()) + list(_argmax_scratches.values()) + list(_sliced_work.values()):
                 buf.zero_()               # a kernel that gave up may have left counters behind
             raise KernelError(f"a tensor-core kernel gave up (code {code}: 1 = wait for a free stage, 2 = for a loaded "
                               f"stage, 3 = for the accumulator, 4 = for a key/value copy, 5 = misaligned staging "
@@ -549,10 +549,20 @@ def add_logit_bias(logits: torch.Tensor, entry_row: torch.Tensor, entry_token: t
                                           _stream()), "sharpi_add_logit_bias")
 
 
+_sliced_work = {}
+SLICED_SAMPLER_FROM = 4096        # vocabularies from this size on take the sampler that cuts rows over 32 blocks
+_SLICED_ROW_BYTES = 56 + 32 * 16 + 2048 * 12
+
+
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
                 min_p: torch.Tensor, uniform: torch.Tensor, *, probs: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One token per row: greedy where ``temperature <= 0``, else filtered temperature sampling."""
+                out: Optional[torch.Tensor] = None, any_top_k: bool = True, any_top_p: bool = True,
+                sliced: Optional[bool] = None) -> torch.Tensor:
+    """One token per row: greedy where ``temperature <= 0``, else filtered temperature sampling.
+
+    Large vocabularies take the sampler that cuts every row over 32 blocks and finds the thresholds by
+    radix selection (``sliced``; ``any_top_k`` / ``any_top_p`` = False skip the rounds of a filter that no
+    row uses); small ones the one-block-per-row sampler with its ``probs`` work area."""
     _need(logits, "logits", torch.float32)
     R, V = logits.shape
     _need(temperature, "temperature", torch.float32)
@@ -560,10 +570,24 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     _need(top_p, "top_p", torch.float32)
     _need(min_p, "min_p", torch.float32)
     _need(uniform, "uniform", torch.float32)
-    if probs is None:
-        probs = torch.empty((R, V), dtype=torch.float32, device=logits.device)
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    if sliced is None:
+        sliced = V >= SLICED_SAMPLER_FROM and probs is None
+    if sliced:
+        key = (logits.device, torch.cuda.current_stream(logits.device).cuda_stream)
+        work = _sliced_work.get(key)
+        need = R * _SLICED_ROW_BYTES + 256
+        if work is None or work.numel() < need:        # all zero before the first call; every call leaves it so
+            work = _sliced_work[key] = torch.zeros(max(need, 64 * _SLICED_ROW_BYTES), dtype=torch.uint8,
+                                                   device=logits.device)
+        check(kernel("sharpi_sample_rows_sliced")(logits.data_ptr(), R, V, temperature.data_ptr(), top_k.data_ptr(),
+                                                  top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(),
+                                                  work.data_ptr(), int(any_top_k), int(any_top_p), out.data_ptr(),
+                                                  _stream()), "sharpi_sample_rows_sliced")
+        return out
+    if probs is None:
+        probs = torch.empty((R, V), dtype=torch.float32, device=logits.device)
     check(kernel("sharpi_sample_rows")(logits.data_ptr(), R, V, temperature.data_ptr(), top_k.data_ptr(),
                                        top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(), probs.data_ptr(),
                                        out.data_ptr(), _stream()), "sharpi_sample_rows")

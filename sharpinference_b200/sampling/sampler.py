@@ -97,7 +97,9 @@ class Sampler:
                   0.0 if st.params.greedy else uniform01(st.seed, st.draws)] for st in states],
                 dtype=torch.float32).t().contiguous().to(dev)
             top_k = torch.tensor([st.params.top_k for st in states], dtype=torch.int32, device=dev)
-            picked = ops.sample_rows(logits, host[0], top_k, host[1], host[2], host[3])
+            picked = ops.sample_rows(logits, host[0], top_k, host[1], host[2], host[3],
+                                     any_top_k=any(0 < st.params.top_k for st in states),
+                                     any_top_p=any(0.0 < st.params.top_p < 1.0 for st in states))
         tokens = picked.tolist()
         for st, tok in zip(states, tokens):
             if not st.params.greedy:

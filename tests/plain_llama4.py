@@ -324,7 +324,8 @@ def sample_distribution(logits: torch.Tensor, temperature: float, top_k: int = 0
     if 0 < top_p < 1:
         order = torch.argsort(p, descending=True)
         csum = torch.cumsum(p[order], dim=0)
-        cut = int((csum >= top_p).nonzero()[0].item()) + 1
+        reached = (csum >= top_p).nonzero()
+        cut = int(reached[0].item()) + 1 if reached.numel() else p.shape[0]      # never reached: everything stays
         keep = torch.zeros_like(p)
         keep[order[:cut]] = p[order[:cut]]
         p = keep

@@ -382,6 +382,51 @@ def test_sampling_follows_the_filtered_distribution(ops):
     assert greedy == [int(torch.argmax(row))] * 3
 
 
+@pytest.mark.parametrize("V", [4096, 50021, 202048])
+def test_sliced_sampler_follows_the_filtered_distribution(ops, V):
+    """Large vocabularies: every row cut over 32 blocks, thresholds by radix selection, mass in fixed point.
+    Against the plain statement, for every filter alone and all together."""
+    import plain_llama4 as plain
+    R = 128
+    row = rnd(V, scale=2.5, seed=17)
+    u = ((torch.arange(R, dtype=torch.float32) + 0.5) / R).to(DEV)
+    for temp, k, p, mp in ((0.8, 0, 1.0, 0.0), (1.0, 40, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
+                           (0.7, 40, 0.95, 0.05), (1.0, 1, 1.0, 0.0), (0.9, 5000, 0.5, 0.0)):
+        dist = plain.sample_distribution(row.cpu(), temp, top_k=k, top_p=p, min_p=mp)
+        got = ops.sample_rows(row.expand(R, V).contiguous(), torch.full((R,), temp, device=DEV),
+                              torch.full((R,), k, dtype=torch.int32, device=DEV), torch.full((R,), p, device=DEV),
+                              torch.full((R,), mp, device=DEV), u, any_top_k=k > 0, any_top_p=p < 1.0).tolist()
+        csum = torch.cumsum(dist, 0)                          # plain.draw, for all draws at once
+        want = torch.searchsorted(csum, u.cpu().double()).clamp(max=V - 1).tolist()
+        differ = sum(a != b for a, b in zip(got, want))
+        assert differ <= 3, (temp, k, p, mp, differ)          # a draw may sit on a boundary of the cumulative sum
+        assert all(dist[t] > 0 for t in got), (temp, k, p, mp)  # never a token outside the kept set
+
+
+def test_sliced_sampler_rows_are_independent_and_repeatable(ops):
+    """Rows with different settings in one call (greedy, plain temperature, top-k, top-p, both): each row gets
+    what it gets alone, twice in a row, and ties at a threshold stay together."""
+    V = 30011
+    logits = rnd(6, V, scale=3.0, seed=23)
+    logits[4, 100] = logits[4, 20000] = logits[4, 7] = 50.0              # a three-way tie at the top
+    temp = torch.tensor([0.0, 0.9, 1.0, 0.7, 1.0, 0.8], device=DEV)
+    k = torch.tensor([0, 0, 20, 0, 2, 50], dtype=torch.int32, device=DEV)
+    p = torch.tensor([1.0, 1.0, 1.0, 0.8, 1.0, 0.9], device=DEV)
+    mp = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.02], device=DEV)
+    for u0 in (0.03, 0.5, 0.97):
+        u = torch.full((6,), u0, device=DEV)
+        both = ops.sample_rows(logits, temp, k, p, mp, u).tolist()
+        again = ops.sample_rows(logits, temp, k, p, mp, u).tolist()
+        alone = [ops.sample_rows(logits[r:r + 1].contiguous(), temp[r:r + 1], k[r:r + 1], p[r:r + 1], mp[r:r + 1],
+                                 u[r:r + 1]).tolist()[0] for r in range(6)]
+        assert both == again == alone
+        assert both[0] == int(torch.argmax(logits[0]))
+        assert both[4] in (7, 100, 20000)                   # top-k 2 with three equal leaders keeps all three
+    picks = {ops.sample_rows(logits[4:5].contiguous(), temp[4:5], k[4:5], p[4:5], mp[4:5],
+                             torch.tensor([x], device=DEV)).tolist()[0] for x in (0.1, 0.5, 0.9)}
+    assert picks == {7, 100, 20000}
+
+
 def test_penalties_and_bias(ops):
     logits = torch.tensor([[2.0, -1.0, 0.5, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
     ops.add_logit_bias(logits, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
