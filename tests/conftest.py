@@ -80,6 +80,23 @@ TINY_D = {
 }
 TINY_D_INIT = {"seed": 3, "std": 0.04, "norm_std": 0.1}
 
+# The shapes of the large models in small: head size 128 with five query heads to a kv head, pages of 64
+# positions, a chunk of 512, the Scout rope scaling, and a prompt long enough (1400 rows in one step) for the
+# kernels that only large steps reach: attention tiles of 128 rows on tcgen05, the persistent grouped product,
+# two weight tiles per CTA in the down product.
+LARGE_SHAPES = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 1000, "hidden_size": 640, "num_hidden_layers": 4, "num_attention_heads": 10,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 384, "intermediate_size_mlp": 512,
+    "num_local_experts": 4, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
+                     "original_max_position_embeddings": 8192},
+    "no_rope_layers": [3], "attention_chunk_size": 512, "use_qk_norm": True, "attn_temperature_tuning": True,
+    "floor_scale": 512, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+
+
 TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT)}
 
 

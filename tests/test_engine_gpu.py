@@ -7,7 +7,7 @@ import torch
 
 import plain_llama4 as plain
 import traces
-from conftest import TINY
+from conftest import LARGE_SHAPES, TINY
 
 pytestmark = pytest.mark.gpu
 
@@ -83,23 +83,6 @@ def test_logits_equal_the_plain_implementation(model_dirs, expected, name, cut, 
     engine.cache.check_invariants()
     assert not engine.cache.requests
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
-
-
-# The shapes of the large models in small: head size 128 with five query heads to a kv head, pages of 64
-# positions, a chunk of 512, the Scout rope scaling, and a prompt long enough (1400 rows in one step) for the
-# kernels that only large steps reach: attention tiles of 128 rows on tcgen05, the persistent grouped product,
-# two weight tiles per CTA in the down product.
-LARGE_SHAPES = {
-    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
-    "vocab_size": 1000, "hidden_size": 640, "num_hidden_layers": 4, "num_attention_heads": 10,
-    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 384, "intermediate_size_mlp": 512,
-    "num_local_experts": 4, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
-                     "original_max_position_embeddings": 8192},
-    "no_rope_layers": [3], "attention_chunk_size": 512, "use_qk_norm": True, "attn_temperature_tuning": True,
-    "floor_scale": 512, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
-}
 
 
 @pytest.fixture(scope="module")
