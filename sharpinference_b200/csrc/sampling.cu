@@ -131,11 +131,11 @@ __global__ void argmax_rows_sliced_kernel(const float* __restrict__ logits, int 
 }
 
 // `scratch` (optional): 64 ints that are zero before the call (and after it), then 64 * 32 pairs of (float, int);
-// with it, calls for up to 64 rows cut every row over 32 blocks.
+// with it, calls for up to 16 rows cut every row over 32 blocks.
 SHARPI_API int sharpi_argmax_rows(const float* logits, int R, int V, int* out, void* scratch, cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (V <= 0) return SHARPI_BAD_ARGUMENT;
-    if (scratch && R <= 64 && V >= 4096) {
+    if (scratch && R <= 16 && V >= 4096) {      // more rows fill the GPU with a block each
         int* tickets = reinterpret_cast<int*>(scratch);
         ArgBest* cand = reinterpret_cast<ArgBest*>(tickets + 64);
         SHARPI_LAUNCH_PDL(argmax_rows_sliced_kernel, dim3(ARGMAX_SLICES, R), SAMPLE_THREADS, 0, stream, logits, V, out, cand,
