@@ -163,6 +163,93 @@ static int launch_router(const float* h, const float* wr, int T, int H, int E, i
     return SHARPI_OK;
 }
 
+// Very many tokens (prompts): a warp keeps its segment of four router rows in registers and streams the
+// block's tokens past them, so the router is read once per block of STREAM_TPB tokens and a token's loads do
+// not wait for another token's.  NI = four-element pieces of a segment per lane (the width is at most
+// 1024 * NI).  The sums are formed exactly as in router_segment_dot.
+constexpr int STREAM_TPB = 16;
+constexpr int STREAM_EPP = 4;
+
+template <int NI>
+__global__ void __launch_bounds__(ROUTER_SEGMENTS * 32)
+router_top1_stream_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
+                          int* __restrict__ expert_id, float* __restrict__ expert_weight,
+                          float* __restrict__ logits_out) {
+    extern __shared__ __align__(16) float smem[];
+    float* seg_s = smem;                                         // [segments][STREAM_TPB][E]
+    float* r_s = smem + ROUTER_SEGMENTS * STREAM_TPB * E;        // [STREAM_TPB][E]
+    const int t0 = blockIdx.x * STREAM_TPB;
+    const int n_tok = min(STREAM_TPB, T - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = router_segment_len(H);
+    const int begin = min(H, warp * seg), end = min(H, begin + seg);
+    const int n4 = (end - begin) >> 2;                           // H % 4 == 0 here
+    for (int e0 = 0; e0 < E; e0 += STREAM_EPP) {
+        float4 b[STREAM_EPP][NI];
+#pragma unroll
+        for (int ee = 0; ee < STREAM_EPP; ++ee)
+#pragma unroll
+            for (int k = 0; k < NI; ++k) {
+                const int i = lane + 32 * k;
+                b[ee][k] = (e0 + ee < E && i < n4)
+                               ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)(e0 + ee) * H + begin) + i)
+                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll 2
+        for (int tt = 0; tt < n_tok; ++tt) {
+            const float4* a4 = reinterpret_cast<const float4*>(h + (size_t)(t0 + tt) * H + begin);
+            float4 a[NI];
+#pragma unroll
+            for (int k = 0; k < NI; ++k) {
+                const int i = lane + 32 * k;
+                a[k] = i < n4 ? a4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int ee = 0; ee < STREAM_EPP; ++ee) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int k = 0; k < NI; ++k) {
+                    if (lane + 32 * k < n4) {                    // a lane adds only the pieces it has, in order
+                        acc = fmaf(a[k].x, b[ee][k].x, acc);
+                        acc = fmaf(a[k].y, b[ee][k].y, acc);
+                        acc = fmaf(a[k].z, b[ee][k].z, acc);
+                        acc = fmaf(a[k].w, b[ee][k].w, acc);
+                    }
+                }
+                const float part = warp_sum(acc);
+                if (lane == 0 && e0 + ee < E) seg_s[(warp * STREAM_TPB + tt) * E + e0 + ee] = part;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_SEGMENTS * 32) {
+        float total = 0.0f;
+#pragma unroll
+        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) total += seg_s[sgm * STREAM_TPB * E + i];
+        r_s[i] = total;
+    }
+    __syncthreads();
+    if (logits_out)
+        for (int i = threadIdx.x; i < n_tok * E; i += ROUTER_SEGMENTS * 32) logits_out[(size_t)t0 * E + i] = r_s[i];
+    if (threadIdx.x < n_tok)
+        router_pick(r_s + threadIdx.x * E, E, expert_id + t0 + threadIdx.x, expert_weight + t0 + threadIdx.x);
+}
+
+template <int NI>
+static int launch_router_stream(const float* h, const float* wr, int T, int H, int E, int* expert_id,
+                                float* expert_weight, float* logits_out, cudaStream_t stream) {
+    const size_t smem = (size_t)(ROUTER_SEGMENTS + 1) * STREAM_TPB * E * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(router_top1_stream_kernel<NI>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
+    }
+    router_top1_stream_kernel<NI><<<(T + STREAM_TPB - 1) / STREAM_TPB, ROUTER_SEGMENTS * 32, smem, stream>>>(
+        h, wr, T, H, E, expert_id, expert_weight, logits_out);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
 // Few tokens: what costs time is the chain of dependent loads of one block walking every expert, so each
 // (token, expert) pair gets a block of its own whose eight warps take one segment each; every load of the
 // step is then in flight at once.  The logits go to `logits`; the block that finishes last for a token (a
@@ -257,7 +344,21 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
     // many tokens: eight share a block and its reads of the router rows (four with sixteen experts to a pass
     // measured slower: the rows are re-read from L2 once per block); fewer: two, for more blocks
     int rc;
-    if (T >= 1024 && (size_t)(ROUTER_SEGMENTS + 1) * 8 * E * sizeof(float) <= 200 * 1024)
+    const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(h) & 15) == 0);
+    const int pieces = (router_segment_len(H) / 4 + 31) / 32;          // per lane and segment
+    if (T >= 1024 && vec && pieces <= 8 && (size_t)(ROUTER_SEGMENTS + 1) * STREAM_TPB * E * sizeof(float) <= 200 * 1024) {
+        switch (pieces) {
+            case 1: rc = launch_router_stream<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 2: rc = launch_router_stream<2>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 3: rc = launch_router_stream<3>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 4: rc = launch_router_stream<4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 5: rc = launch_router_stream<5>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 6: rc = launch_router_stream<6>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 7: rc = launch_router_stream<7>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            default: rc = launch_router_stream<8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+        }
+    } else if (T >= 1024 && (size_t)(ROUTER_SEGMENTS + 1) * 8 * E * sizeof(float) <= 200 * 1024)
         rc = launch_router<8, 4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);
     else
         rc = launch_router<2, 8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream);

@@ -53,8 +53,8 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
 class MoESigmoidTop1(FeedForward):
     wants_fp32_input = True
     graph_safe = True
-    # Steps of up to this many rows run the shared expert on a second stream beside the routed experts.  In
-    # larger steps every product fills the GPU by itself.
+    # Steps of up to this many rows run the shared expert beside the routed gate|up product; larger steps run
+    # it beside the routing only (see forward).
     FORK_UP_TO = 256
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
@@ -79,26 +79,39 @@ class MoESigmoidTop1(FeedForward):
         T = h.shape[0]
         if h32 is None:
             h32 = h.to(torch.float32)
-        # Routing, sorting and gathering are short kernels that everything routed waits for: they go first.
-        # Then the shared expert runs on a second stream beside the routed gate|up product (two streams of
-        # weights keep the memory system busier than one), and the streams join before the routed down
-        # product adds into the shared expert's output.  Inside a graph capture: a fork and a join.
-        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
-        if "router_choices" in ctx.extras:          # tracing: which expert every row went to
-            ctx.extras["router_choices"].append(expert)
+        # The shared expert and the routed ones meet only where the routed outputs are added, so the shared
+        # expert runs on a second stream (inside a graph capture: a fork and a join).  Small steps: routing,
+        # sorting and gathering are short kernels that everything routed waits for, so they go first, and the
+        # shared expert then runs beside the routed gate|up product (two streams of weights keep the memory
+        # system busier than one).  Large steps: every product fills the GPU by itself, so what is worth
+        # hiding is the routing: the shared expert is forked off first and the streams join before the
+        # routed products.
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
-        h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
         main = side = None
-        if self.shared is not None and T > self.FORK_UP_TO:
-            y = self.shared.forward(ctx, h)
-        elif self.shared is not None:
+        y = None
+        large = T > self.FORK_UP_TO
+
+        def fork_shared():
+            nonlocal main, side, y
             y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
             main, side = torch.cuda.current_stream(h.device), _side_stream(h.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 self.shared.forward(ctx, h, out=y)
-        else:
+
+        if self.shared is not None and large:
+            fork_shared()
+        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
+        if "router_choices" in ctx.extras:          # tracing: which expert every row went to
+            ctx.extras["router_choices"].append(expert)
+        h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
+        if self.shared is None:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        elif large:
+            main.wait_stream(side)
+            side = None
+        else:
+            fork_shared()
         if tensor_core:
             act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                       row_scale=weight, scale_rows=sorted_rows)
