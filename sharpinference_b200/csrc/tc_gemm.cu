@@ -151,12 +151,60 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     int* tile_info = reinterpret_cast<int*>(tmem_slot + 1);   // [0] expert, [1] first sorted row, [2] end row
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- set-up that touches nothing an earlier kernel writes: it may overlap that kernel's tail ----------
+    const int n0 = blockIdx.x * TC_BM * (MODE == MODE_SWIGLU ? 1 : WT);    // first weight row (MODE_SWIGLU: in [0, I))
+    const int I = p.N / 2;                                                 // MODE_SWIGLU only
+    // the second tile: MODE_SWIGLU: the matching up rows; MODE_STORE: the next 128 rows, if the CTA has two
+    const int n1 = (MODE == MODE_SWIGLU) ? I + n0 : n0 + TC_BM;
+    const int k_blocks_all = (p.K + TC_BK - 1) / TC_BK;
+    const int kb_per = (k_blocks_all + p.k_split - 1) / p.k_split;
+    const int kb_begin = blockIdx.z * kb_per;
+    const int k_blocks = max(0, min(k_blocks_all, kb_begin + kb_per) - kb_begin);   // this CTA's share
+    // One group (a dense product): the tile follows from the block index alone, and the weights, which no
+    // kernel writes, can be on their way into the first stages before the kernel ahead has finished.
+    const bool dense = p.E == 1;
+    const bool dense_tile = dense && (int)blockIdx.y * NT < p.rows;
+    const int early = dense_tile ? min(k_blocks, Cfg::STAGES) : 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(accum_bar, 1);
+        fence_barrier_init();
+        if (dense) {
+            tile_info[0] = dense_tile ? 0 : -1;
+            tile_info[1] = blockIdx.y * NT;
+            tile_info[2] = p.rows;
+        }
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (warp == 4 && lane == 0) {
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
+        for (int kb = 0; kb < early; ++kb) {
+            uint8_t* stage = smem + kb * Cfg::STAGE_BYTES;
+            mbar_arrive_expect_tx(&full_bar[kb], Cfg::STAGE_BYTES);       // the activations' bytes follow below
+            const int kx = (kb_begin + kb) * TC_BK;
+            tma_load_3d(stage, &map_w, &full_bar[kb], kx, n0, 0);
+            if (WT == 2) tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[kb], kx, n1, 0);
+        }
+    }
     pdl_wait();
 
     // ---- which tile is this CTA's ----------------------------------------------------------
-    // Warp 0 looks the tile up: lane l reads the bounds of group e0 + l, the warp scans the tile counts, and
-    // the group whose range of tiles holds blockIdx.y is the one (all loads at once, not a walk from group 0).
-    if (warp == 0) {
+    // Several groups: warp 0 looks the tile up: lane l reads the bounds of group e0 + l, the warp scans the tile
+    // counts, and the group whose range of tiles holds blockIdx.y is the one (all loads at once, not a walk
+    // from group 0).
+    if (!dense && warp == 0) {
         const int tile = blockIdx.y;
         int found = -1, f_start = 0, f_end = 0, f_tile = 0, base = 0;
         for (int e0 = 0; e0 < p.E && found < 0; e0 += 32) {
@@ -188,42 +236,18 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             tile_info[0] = found;
             tile_info[1] = f_start + f_tile * NT;
             tile_info[2] = f_end;
-            for (int s = 0; s < Cfg::STAGES; ++s) {
-                mbar_init(&full_bar[s], 1);
-                mbar_init(&empty_bar[s], 1);
-            }
-            mbar_init(accum_bar, 1);
-            fence_barrier_init();
         }
     }
-    __syncthreads();
+    if (!dense) __syncthreads();
     const int expert = tile_info[0];
-    if (expert < 0) return;                       // uniform: nothing allocated yet
+    const bool has_tile = expert >= 0;            // uniform over the CTA; without a tile only the exit is left
     const int row0 = tile_info[1], row_end = tile_info[2];
-    // first weight row: MODE_SWIGLU: index into [0, I), the second tile is the matching up rows;
-    // MODE_STORE: the second tile, if there is one, is the next 128 rows
-    const int n0 = blockIdx.x * TC_BM * (MODE == MODE_SWIGLU ? 1 : WT);
-    const int I = p.N / 2;                        // MODE_SWIGLU only
-    const int n1 = (MODE == MODE_SWIGLU) ? I + n0 : n0 + TC_BM;
-    const int k_blocks_all = (p.K + TC_BK - 1) / TC_BK;
-    const int kb_per = (k_blocks_all + p.k_split - 1) / p.k_split;
-    const int kb_begin = blockIdx.z * kb_per;
-    const int k_blocks = max(0, min(k_blocks_all, kb_begin + kb_per) - kb_begin);   // this CTA's share
 
-    if (warp == 5) {
-        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-        tmem_relinquish();
-    }
-    tcgen05_fence_before();
-    __syncthreads();
-    tcgen05_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 4) {
+    if (!has_tile) {
+        // nothing to do but to leave together
+    } else if (warp == 4) {
         // ---- TMA producer ------------------------------------------------------------------
         if (lane == 0) {
-            prefetch_tensormap(&map_w);
-            prefetch_tensormap(&map_a);
             int issued = 0;
             bool ok = true;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
@@ -231,10 +255,12 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (kb >= Cfg::STAGES) ok = mbar_wait(&empty_bar[s], ((kb / Cfg::STAGES) - 1) & 1);
                 if (!ok) { atomicExch(p.status, 1); break; }
                 uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
-                mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
                 const int kx = (kb_begin + kb) * TC_BK;
-                tma_load_3d(stage, &map_w, &full_bar[s], kx, n0, expert);
-                if (WT == 2) tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kx, n1, expert);
+                if (kb >= early) {                    // else the weights of this stage are on their way already
+                    mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                    tma_load_3d(stage, &map_w, &full_bar[s], kx, n0, expert);
+                    if (WT == 2) tma_load_3d(stage + Cfg::W_BYTES, &map_w, &full_bar[s], kx, n1, expert);
+                }
                 tma_load_2d(stage + Cfg::W_TILES * Cfg::W_BYTES, &map_a, &full_bar[s], kx, row0);
                 issued = kb + 1;
             }
