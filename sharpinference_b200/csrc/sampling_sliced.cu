@@ -2,7 +2,7 @@
 //
 // The one-block-per-row sampler (sampling.cu) walks a row of 202048 logits some seventy times (two
 // thirty-one-step searches for the top-k and top-p thresholds): 0.7 ms a step on one SM.  Here a row's
-// work is spread over SLICES blocks and the thresholds are found by radix selection: three rounds of
+// work is spread over SLICES blocks and the thresholds are found by radix selection: three passes of
 // histograms over the bits of the unnormalised probability e = exp(x / T - max) (11, 11 and 9 bits from
 // the top), first by count for top-k, then by mass for top-p.  Probability mass is kept in fixed point
 // (e * 2^40 in 64-bit integers), so every sum is exact, the order of the additions does not matter, and
@@ -34,7 +34,7 @@ struct SampleRow {
     unsigned prefix;                  // radix selection: the bits settled so far
     unsigned above_count;             // ... elements above the bin that is being refined
     unsigned long long above_mass;    // ... and their mass
-    unsigned long long target;        // mass rounds: the mass to reach
+    unsigned long long target;        // mass passes: the mass to reach
     int ticket;                       // blocks of the row that finished the running kernel
     int pad;
 };
@@ -127,11 +127,11 @@ __device__ __forceinline__ void row_max(const SlicedArgs& a, int r, float& best,
     }
 }
 
-// ---- kernels 2 .. 7: one round of radix selection ---------------------------------------------------
-// round 0, 1, 2 take bits 30..20, 19..9, 8..0 of e's pattern.  by_mass = 0: towards the k-th largest
+// ---- kernels 2 .. 7: one pass of radix selection ---------------------------------------------------
+// pass 0, 1, 2 take bits 30..20, 19..9, 8..0 of e's pattern.  by_mass = 0: towards the k-th largest
 // (count); 1: towards the top-p cut (mass of the elements that top-k and min-p keep).
 
-__global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, int round, int by_mass) {
+__global__ void __launch_bounds__(SL_THREADS) sliced_pass_kernel(SlicedArgs a, int pass, int by_mass) {
     __shared__ unsigned count_s[BINS];
     __shared__ unsigned long long mass_s[BINS];
     __shared__ unsigned long long part_mass_s[SL_THREADS];
@@ -145,12 +145,12 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
     const bool wants_k = k > 0 && k < a.V;
     const bool wants_p = tp > 0.0f && tp < 1.0f;
     SampleRow* st = a.rows + r;
-    // rows that do not take part in this kind of round leave at once (uniform over the row's blocks);
-    // the first count round also runs for rows with top-p alone: it gives the row's whole mass
+    // rows that do not take part in this kind of pass leave at once (uniform over the row's blocks);
+    // the first counting pass also runs for rows with top-p alone: it gives the row's whole mass
     if (temp <= 0.0f) return;
-    if (by_mass ? !wants_p : (round > 0 ? !wants_k : !(wants_k || wants_p))) return;
+    if (by_mass ? !wants_p : (pass > 0 ? !wants_k : !(wants_k || wants_p))) return;
 
-    const int shift = round == 0 ? 20 : round == 1 ? 9 : 0, bits = round == 2 ? 9 : 11, bins = 1 << bits;
+    const int shift = pass == 0 ? 20 : pass == 1 ? 9 : 0, bits = pass == 2 ? 9 : 11, bins = 1 << bits;
     for (int b = threadIdx.x; b < bins; b += SL_THREADS) {
         count_s[b] = 0;
         mass_s[b] = 0;
@@ -159,8 +159,8 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
     int arg;
     row_max(a, r, mx, arg);
     const float inv_t = 1.0f / temp, m = mx * inv_t;
-    const unsigned prefix = round == 0 ? 0u : st->prefix;          // settled bits, in place
-    const unsigned settled_mask = round == 0 ? 0u : (0x7fffffffu >> (shift + bits)) << (shift + bits);
+    const unsigned prefix = pass == 0 ? 0u : st->prefix;          // settled bits, in place
+    const unsigned settled_mask = pass == 0 ? 0u : (0x7fffffffu >> (shift + bits)) << (shift + bits);
     const unsigned floor_bits = by_mass ? max(st->kth, __float_as_uint(fmaxf(a.min_p[r], 0.0f))) : 0u;
     __syncthreads();
     int begin, end;
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
     part_count_s[threadIdx.x] = my_count;
     part_mass_s[threadIdx.x] = my_mass;
     __syncthreads();
-    // what lies above this thread's bins, inside this round's histogram: a suffix sum over the threads,
+    // what lies above this thread's bins, inside this pass's histogram: a suffix sum over the threads,
     // first inside each warp, then over the warps' totals
     unsigned up_count = my_count;
     unsigned long long up_mass = my_mass;
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
         part_mass_s[wrp] = up_mass;
     }
     __syncthreads();
-    unsigned long long all_mass = 0;       // the whole histogram's mass (the row's mass in the first count round)
+    unsigned long long all_mass = 0;       // the whole histogram's mass (the row's mass in the first counting pass)
     for (int w = 0; w < SL_THREADS / 32; ++w) all_mass += part_mass_s[w];
     for (int w = wrp + 1; w < SL_THREADS / 32; ++w) {
         up_count += part_count_s[w];
@@ -244,11 +244,11 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
     }
     up_count -= my_count;                  // strictly above this thread's bins
     up_mass -= my_mass;
-    const unsigned base_count = round == 0 ? 0u : st->above_count;
-    const unsigned long long base_mass = round == 0 ? 0ull : st->above_mass;
+    const unsigned base_count = pass == 0 ? 0u : st->above_count;
+    const unsigned long long base_mass = pass == 0 ? 0ull : st->above_mass;
     unsigned long long target = 0;
     if (by_mass) {
-        if (round == 0) {
+        if (pass == 0) {
             const double want = (double)tp * (double)st->kept_mass;
             target = (unsigned long long)want;
             if (target < 1) target = 1;
@@ -265,8 +265,8 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
         if (below && reach) found_s = threadIdx.x;
     }
     __syncthreads();
-    // the first count round always leaves the row's whole mass (rows without top-k: what top-p refers to)
-    if (!by_mass && round == 0 && threadIdx.x == 0 && !wants_k) {
+    // the first counting pass always leaves the row's whole mass (rows without top-k: what top-p refers to)
+    if (!by_mass && pass == 0 && threadIdx.x == 0 && !wants_k) {
         st->kept_mass = all_mass;
         st->kth = 0;
     }
@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_round_kernel(SlicedArgs a, 
         if (reach || j == 0) {          // j == 0 without reach: nothing crosses, the lowest bin keeps everything
             pick = threadIdx.x * per_thread + j;
             const unsigned new_prefix = prefix | ((unsigned)pick << shift);
-            if (round == 2) {
+            if (pass == 2) {
                 if (by_mass) {
                     st->cut = new_prefix;
                 } else {
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(SL_THREADS) sliced_draw_kernel(SlicedArgs a) {
 
 // `work`: scratch that is all zero before the first call and is left so by every call (its size:
 // sharpi_sample_rows_sliced_work_bytes(R)).  `any_top_k` / `any_top_p`: whether any row uses the filter
-// (the rounds of a filter that no row uses are not launched).
+// (the passes of a filter that no row uses are not launched).
 SHARPI_API long long sharpi_sample_rows_sliced_work_bytes(int R) {
     if (R <= 0) return 0;
     return (long long)R * (sizeof(SampleRow) + SLICES * (sizeof(float) + sizeof(int) + sizeof(unsigned long long)) +
@@ -419,15 +419,15 @@ SHARPI_API int sharpi_sample_rows_sliced(const float* logits, int R, int V, cons
     a.slice_arg = reinterpret_cast<int*>(p);
     const dim3 grid(SLICES, R);
     SHARPI_LAUNCH_PDL(sliced_max_kernel, grid, SL_THREADS, 0, stream, a);
-    if (any_top_k || any_top_p) SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 0, 0);
+    if (any_top_k || any_top_p) SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 0, 0);
     if (any_top_k) {
-        SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 1, 0);
-        SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 2, 0);
+        SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 1, 0);
+        SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 2, 0);
     }
     if (any_top_p) {
-        SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 0, 1);
-        SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 1, 1);
-        SHARPI_LAUNCH_PDL(sliced_round_kernel, grid, SL_THREADS, 0, stream, a, 2, 1);
+        SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 0, 1);
+        SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 1, 1);
+        SHARPI_LAUNCH_PDL(sliced_pass_kernel, grid, SL_THREADS, 0, stream, a, 2, 1);
     }
     SHARPI_LAUNCH_PDL(sliced_draw_kernel, grid, SL_THREADS, 0, stream, a);
     return SHARPI_OK;

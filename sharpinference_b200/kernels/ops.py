@@ -561,7 +561,7 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     """One token per row: greedy where ``temperature <= 0``, else filtered temperature sampling.
 
     Large vocabularies take the sampler that cuts every row over 32 blocks and finds the thresholds by
-    radix selection (``sliced``; ``any_top_k`` / ``any_top_p`` = False skip the rounds of a filter that no
+    radix selection (``sliced``; ``any_top_k`` / ``any_top_p`` = False skip the passes of a filter that no
     row uses); small ones the one-block-per-row sampler with its ``probs`` work area."""
     _need(logits, "logits", torch.float32)
     R, V = logits.shape
