@@ -16,7 +16,9 @@ architecture's safetensors checkpoints: per-layer ``self_attn.{q,k,v,o}_proj.wei
 ``input_layernorm.weight``, ``post_attention_layernorm.weight``; mixture layers
 ``feed_forward.router.weight [E, H]``, ``feed_forward.experts.gate_up_proj [E, H, 2I]`` (input-major:
 ``x @ W``; the first I columns are the gate, the last I the up projection),
-``feed_forward.experts.down_proj [E, I, H]``, ``feed_forward.shared_expert.{gate,up,down}_proj.weight``;
+``feed_forward.experts.down_proj [E, I, H]`` (or, where a folder keeps the experts apart,
+``feed_forward.experts.<e>.{gate,up,down}_proj.weight`` as ``[out, in]`` matrices),
+``feed_forward.shared_expert.{gate,up,down}_proj.weight``;
 dense layers ``feed_forward.{gate,up,down}_proj.weight``; ``model.embed_tokens.weight``,
 ``model.norm.weight``, ``lm_head.weight``.  Q, K and V are concatenated for one product, gate and up
 likewise, and the expert tensors are transposed once to ``[E, out, in]``.
@@ -71,8 +73,17 @@ def build_llama4(config: Llama4TextConfig, weights: WeightSource) -> DecoderMode
         if c.layer_is_moe(i):
             E, I = c.num_local_experts, c.intermediate_size
             router = weights.vector(p + "feed_forward.router.weight", (E, H), init="normal")
-            gate_up = weights.matrix(p + "feed_forward.experts.gate_up_proj", (E, H, 2 * I))
-            down = weights.matrix(p + "feed_forward.experts.down_proj", (E, I, H))
+            if weights.stored(p + "feed_forward.experts.0.gate_proj.weight"):
+                # one set of [out, in] matrices per expert
+                e_gate_up = torch.stack([_cat([weights.matrix(f"{p}feed_forward.experts.{e}.gate_proj.weight", (I, H)),
+                                               weights.matrix(f"{p}feed_forward.experts.{e}.up_proj.weight", (I, H))])
+                                         for e in range(E)])
+                e_down = torch.stack([weights.matrix(f"{p}feed_forward.experts.{e}.down_proj.weight", (H, I))
+                                      for e in range(E)])
+            else:
+                # the fused, input-major tensors
+                e_gate_up = weights.matrix(p + "feed_forward.experts.gate_up_proj", (E, H, 2 * I)).transpose(1, 2).contiguous()
+                e_down = weights.matrix(p + "feed_forward.experts.down_proj", (E, I, H)).transpose(1, 2).contiguous()
             shared = DenseSwiGLU(
                 gate_up=Linear(_cat([weights.matrix(p + "feed_forward.shared_expert.gate_proj.weight", (I, H)),
                                      weights.matrix(p + "feed_forward.shared_expert.up_proj.weight", (I, H))]),
@@ -80,8 +91,8 @@ def build_llama4(config: Llama4TextConfig, weights: WeightSource) -> DecoderMode
                 down=Linear(weights.matrix(p + "feed_forward.shared_expert.down_proj.weight", (H, I)), p + "shared.down"),
                 act_dtype=act)
             ffn = MoESigmoidTop1(router=router,
-                                 experts_gate_up=GroupedLinear(gate_up.transpose(1, 2).contiguous(), p + "experts.gate_up"),
-                                 experts_down=GroupedLinear(down.transpose(1, 2).contiguous(), p + "experts.down"),
+                                 experts_gate_up=GroupedLinear(e_gate_up, p + "experts.gate_up"),
+                                 experts_down=GroupedLinear(e_down, p + "experts.down"),
                                  shared=shared, act_dtype=act)
         else:
             I = c.intermediate_size_mlp

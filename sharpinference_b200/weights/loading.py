@@ -32,9 +32,12 @@ def parse_dtype(dtype) -> torch.dtype:
         raise ValueError(f"dtype must be 'bfloat16' or 'float32', found {dtype!r}") from None
 
 
-def declared_tensors(arch: Architecture, config, compute_dtype: torch.dtype = torch.bfloat16) -> List[TensorDecl]:
-    """Every tensor a model folder of this configuration must hold, in file order."""
-    decl = DeclaringWeights(compute_dtype)
+def declared_tensors(arch: Architecture, config, compute_dtype: torch.dtype = torch.bfloat16,
+                     stored_names=None) -> List[TensorDecl]:
+    """Every tensor a model folder of this configuration must hold, in file order.  ``stored_names``: the
+    names a folder does hold, for architectures that accept two layouts of the same weights (the declaration
+    then asks for the layout that is there)."""
+    decl = DeclaringWeights(compute_dtype, stored_names=stored_names, prefixes=("", "language_model."))
     arch.build(config, decl)
     return decl.decls
 
@@ -45,7 +48,7 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0"):
     obj = read_config_json(model_dir)
     arch, config = resolve(obj, os.path.join(model_dir, "config.json"))
     source = FileWeights(model_dir, compute, device)
-    decls = declared_tensors(arch, config, compute)
+    decls = declared_tensors(arch, config, compute, stored_names=list(source.entries))
     source.choose_prefix(decls)
     source.check(decls)
     with torch.no_grad():

@@ -62,16 +62,31 @@ class WeightSource:
         """Whether an optional tensor is there (a declaring source answers for the layout it declares)."""
         return True
 
+    def stored(self, name: str) -> Optional[bool]:
+        """Whether a folder holds ``name``: for builders that accept two layouts of the same weights and must
+        ask for the one that is there.  None where there is no folder to look into (random weights, a bare
+        declaration): the builder then takes its first layout."""
+        return None
+
 
 class DeclaringWeights(WeightSource):
     """Hands out shape-only tensors and remembers what was asked for."""
 
-    def __init__(self, compute_dtype: torch.dtype = torch.bfloat16, optional_present: bool = True):
+    def __init__(self, compute_dtype: torch.dtype = torch.bfloat16, optional_present: bool = True,
+                 stored_names: Optional[Sequence[str]] = None, prefixes: Sequence[str] = ("",)):
         self.compute_dtype = compute_dtype
         self.device = torch.device("meta")
         self.decls: List[TensorDecl] = []
         self._names: Dict[str, TensorDecl] = {}
         self._optional_present = optional_present
+        # the names a folder holds, when the declaration is made to check that folder
+        self._stored = None if stored_names is None else set(stored_names)
+        self._prefixes = tuple(prefixes)
+
+    def stored(self, name):
+        if self._stored is None:
+            return None
+        return any(pre + name in self._stored for pre in self._prefixes)
 
     def _declare(self, name: str, shape: Sequence[int], role: str, init: str, dtype: torch.dtype) -> torch.Tensor:
         decl = TensorDecl(name, tuple(int(s) for s in shape), role, init)
@@ -105,6 +120,9 @@ class FileWeights(WeightSource):
         self.model_dir = model_dir
         self.entries = safetensors_io.open_model(model_dir)
         self.prefix = prefix if prefix is not None else ""
+
+    def stored(self, name):
+        return self.prefix + name in self.entries
 
     # -- checking ----------------------------------------------------------------------
     def choose_prefix(self, decls: Sequence[TensorDecl], candidates=("", "language_model.")) -> str:

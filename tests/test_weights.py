@@ -91,6 +91,43 @@ def test_language_model_prefix_is_found(model_dirs, tmp_path):
     assert fw.prefix == "language_model."
 
 
+def test_experts_kept_apart_load_like_the_fused_tensors(model_dirs, tmp_path):
+    """A folder may hold one [out, in] matrix per expert and projection instead of the fused input-major
+    tensors: the builder asks for what is there, the check accepts it, and the model gets the same weights;
+    a folder that lacks one of the per-expert matrices is told so."""
+    import json
+    import shutil
+    from sharpinference_b200.weights.loading import load_model
+    fused = load_file(os.path.join(model_dirs["A"], "model.safetensors"))
+    E, I = TINY_A["num_local_experts"], TINY_A["intermediate_size"]
+    apart = {}
+    for name, t in fused.items():
+        if name.endswith("feed_forward.experts.gate_up_proj"):
+            base = name[: -len("gate_up_proj")]
+            for e in range(E):
+                apart[f"{base}{e}.gate_proj.weight"] = t[e, :, :I].t().contiguous()
+                apart[f"{base}{e}.up_proj.weight"] = t[e, :, I:].t().contiguous()
+        elif name.endswith("feed_forward.experts.down_proj"):
+            base = name[: -len("down_proj")]
+            for e in range(E):
+                apart[f"{base}{e}.down_proj.weight"] = t[e].t().contiguous()
+        else:
+            apart[name] = t
+    folder = tmp_path / "apart"
+    folder.mkdir()
+    shutil.copy(os.path.join(model_dirs["A"], "config.json"), folder / "config.json")
+    save_file(apart, str(folder / "model.safetensors"))
+    a = load_model(model_dirs["A"], dtype="bfloat16", device="cpu")
+    b = load_model(str(folder), dtype="bfloat16", device="cpu")
+    for blk_a, blk_b in zip(a.blocks, b.blocks):
+        assert torch.equal(blk_a.ffn.experts_gate_up.weight, blk_b.ffn.experts_gate_up.weight)
+        assert torch.equal(blk_a.ffn.experts_down.weight, blk_b.ffn.experts_down.weight)
+    del apart["model.layers.2.feed_forward.experts.3.up_proj.weight"]
+    save_file(apart, str(folder / "model.safetensors"))
+    with pytest.raises(WeightError, match=r"missing \(1\)[\s\S]*experts\.3\.up_proj"):
+        load_model(str(folder), dtype="bfloat16", device="cpu")
+
+
 def test_dtype_rules(model_dirs, tmp_path):
     t = load_file(os.path.join(model_dirs["A"], "model.safetensors"))
     t["model.layers.0.self_attn.o_proj.weight"] = t["model.layers.0.self_attn.o_proj.weight"].float()
