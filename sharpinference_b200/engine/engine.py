@@ -40,6 +40,11 @@ class EngineOptions:
     max_batch: int = 64                 # live requests (and state slots)
     max_tokens_per_step: int = 2048     # token budget of one step
     cuda_graphs: bool = True            # capture decode-only steps as CUDA graphs (when the model's parts allow)
+    # Dense bfloat16 products of steps of up to this many rows run on the engine's own tcgen05 weight-streaming
+    # kernel instead of the vendor library (which the reference also uses only for batched projections, its
+    # single-token products being kernels of its own).  0: the library everywhere, which measured faster on
+    # B200 (Scout sizes, batch 8: 947 against 897 tok/s).  The results differ by rounding only.
+    own_dense_rows: int = 0
 
 
 @dataclass
@@ -50,6 +55,26 @@ class RequestOutput:
     finished: bool
     finish_reason: Optional[str] = None
     preemptions: int = 0
+
+
+def _linears(root, depth: int = 4, seen=None):
+    """Every :class:`Linear` reachable from a model through attributes, lists and tuples."""
+    from ..parts.linear import Linear
+    seen = set() if seen is None else seen
+    if id(root) in seen or depth < 0:
+        return
+    seen.add(id(root))
+    if isinstance(root, Linear):
+        yield root
+        return
+    if isinstance(root, (list, tuple)):
+        for item in root:
+            yield from _linears(item, depth, seen)
+        return
+    if isinstance(root, torch.Tensor) or not hasattr(root, "__dict__"):
+        return
+    for value in vars(root).values():
+        yield from _linears(value, depth - 1, seen)
 
 
 class Engine:
@@ -64,6 +89,10 @@ class Engine:
         torch.cuda.set_device(self.device)
         self.model = load_model(model, self.dtype, self.device) if isinstance(model, str) else model
         o = self.options
+        if o.own_dense_rows > 0:
+            for lin in _linears(self.model):
+                if lin is not getattr(self.model, "head", None):      # the LM head streams 2 GB: the library's job
+                    lin.stream_rows = o.own_dense_rows
         num_pages = self._size_cache()
         self.cache = CacheManager(self.model.schedule, self.model.blocks, page_size=o.page_size,
                                   num_pages=num_pages, max_requests=o.max_batch, dtype=self.model.act_dtype,

@@ -118,6 +118,25 @@ def test_large_model_shapes_in_small(large_shapes, cut, dtype):
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
 
 
+def test_dense_products_on_the_engines_own_kernel(large_shapes):
+    """own_dense_rows: decode-size steps run their dense products (qkv, o, shared expert, dense layers) on the
+    tcgen05 weight-streaming kernel instead of the library; the logits stay within rounding."""
+    from sharpinference_b200 import Engine, EngineOptions
+    folder, reqs = large_shapes
+    reqs = {k: v[:200] for k, v in list(reqs.items())[:3]}
+    steps = traces.tail_decode(reqs)
+    engine = Engine(folder, dtype="bfloat16", device="cuda:0",
+                    options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8,
+                                          own_dense_rows=16))
+    assert all(b.mixer.qkv.stream_rows == 16 and b.ffn.shared.gate_up.stream_rows == 16 for b in engine.model.blocks)
+    assert engine.model.head.stream_rows == 0
+    routing = {}
+    got = traces.replay(engine, steps, routing)
+    ref, _ = plain_under_engine_routing(folder, reqs, routing)
+    err, where = traces.worst_error(got, ref)
+    assert err < TOL["bfloat16"], (err, where)
+
+
 @pytest.mark.parametrize("name", list(TINY))
 def test_float32_cuts_agree_with_each_other_tightly(model_dirs, name):
     """In 32-bit every kernel sums in an order that depends on the row alone, so a row's logits
