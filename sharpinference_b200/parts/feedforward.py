@@ -49,12 +49,20 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
     return _side_streams[key]
 
 
+def _urgent_stream(device: torch.device) -> "torch.cuda.Stream":
+    """A stream of higher priority for short kernels that a longer chain waits for."""
+    key = ("urgent", torch.device(device).index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device, priority=-1)
+    return _side_streams[key]
+
+
 @register_part("feed_forward", "moe_sigmoid_top1")
 class MoESigmoidTop1(FeedForward):
     wants_fp32_input = True
     graph_safe = True
-    # Steps of up to this many rows run the shared expert beside the routed gate|up product; larger steps run
-    # it beside the routing only (see forward).
+    # Steps of up to this many rows run the shared expert beside the routing and the routed gate|up product;
+    # larger steps run it beside the routing only (see forward).
     FORK_UP_TO = 256
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
@@ -80,38 +88,38 @@ class MoESigmoidTop1(FeedForward):
         if h32 is None:
             h32 = h.to(torch.float32)
         # The shared expert and the routed ones meet only where the routed outputs are added, so the shared
-        # expert runs on a second stream (inside a graph capture: a fork and a join).  Small steps: routing,
-        # sorting and gathering are short kernels that everything routed waits for, so they go first, and the
-        # shared expert then runs beside the routed gate|up product (two streams of weights keep the memory
-        # system busier than one).  Large steps: every product fills the GPU by itself, so what is worth
-        # hiding is the routing: the shared expert is forked off first and the streams join before the
-        # routed products.
+        # expert runs on a second stream (inside a graph capture: a fork and a join), forked off before the
+        # routing.  Small steps: the shared expert's products stream their weights beside the routing and the
+        # routed gate|up product (two streams of weights keep the memory system busier than one); routing,
+        # sorting and gathering are short kernels that everything routed waits for, and on the stream of the
+        # shared product they would queue behind its many blocks, so they run on a third stream of higher
+        # priority.  Large steps: every product fills the GPU by itself, so what is worth hiding is the
+        # routing alone, and the streams join before the routed products.
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
-        main = side = None
-        y = None
+        main = torch.cuda.current_stream(h.device)
+        side = None
         large = T > self.FORK_UP_TO
-
-        def fork_shared():
-            nonlocal main, side, y
+        if self.shared is not None:
             y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-            main, side = torch.cuda.current_stream(h.device), _side_stream(h.device)
+            side = _side_stream(h.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 self.shared.forward(ctx, h, out=y)
-
-        if self.shared is not None and large:
-            fork_shared()
-        expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
+        else:
+            y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        routing = main if large or side is None else _urgent_stream(h.device)
+        if routing is not main:
+            routing.wait_stream(main)
+        with torch.cuda.stream(routing):
+            expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
+            h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
+        if routing is not main:
+            main.wait_stream(routing)
         if "router_choices" in ctx.extras:          # tracing: which expert every row went to
             ctx.extras["router_choices"].append(expert)
-        h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
-        if self.shared is None:
-            y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-        elif large:
+        if large and side is not None:
             main.wait_stream(side)
             side = None
-        else:
-            fork_shared()
         if tensor_core:
             act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                       row_scale=weight, scale_rows=sorted_rows)
