@@ -321,40 +321,73 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
     }
 }
 
-// One block per (row, query head): the row's partials, weighted by exp2(max_s - max) and normalised.
-constexpr int MERGE_THREADS = 128;
+// One block per (row, query head): the row's partials, weighted by exp2(max_s - max) and normalised.  A warp
+// takes one split at a time (its D floats are one coalesced read, four per lane) and every MERGE_WARPS-th
+// split after it, several loads in flight; the warps' sums are then added in warp order, so the result
+// depends on the row's position alone.
+constexpr int MERGE_WARPS = 16;
+constexpr int MERGE_THREADS = MERGE_WARPS * 32;
+constexpr int MERGE_UNROLL = 4;
 
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(DecodeArgs a) {
-    __shared__ float w_s[MERGE_THREADS];
+    static_assert(D % 4 == 0 && D <= 128, "a warp reads a split's D floats four per lane");
+    __shared__ float4 acc_s[MERGE_WARPS][D / 4];
+    __shared__ float l_s[MERGE_WARPS];
     __shared__ float scratch[32];
     pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ri = blockIdx.x, head = blockIdx.y;
     const int r = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[r];
     const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
     const int n_s = pos / DEC_SPLIT - lo / DEC_SPLIT + 1;
     const size_t slot0 = ((size_t)ri * a.nq + head) * a.max_splits;
+    const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + slot0;
     float m = -INFINITY;
-    for (int s = threadIdx.x; s < n_s; s += MERGE_THREADS) m = fmaxf(m, a.part_ml[(slot0 + s) * 2]);
+    for (int s = threadIdx.x; s < n_s; s += MERGE_THREADS) m = fmaxf(m, ml[s].x);
     const float M = block_max(m, scratch);
-    float acc = 0.0f, l = 0.0f;
-    for (int s0 = 0; s0 < n_s; s0 += MERGE_THREADS) {
-        const int s = s0 + threadIdx.x;
-        float w = 0.0f;
-        if (s < n_s) {
-            w = exp2f(a.part_ml[(slot0 + s) * 2] - M);
-            l += w * a.part_ml[(slot0 + s) * 2 + 1];
+    const bool active = lane < D / 4;
+    const float4* po = reinterpret_cast<const float4*>(a.part_o + slot0 * D) + (active ? lane : 0);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.0f;
+    for (int s0 = warp; s0 < n_s; s0 += MERGE_WARPS * MERGE_UNROLL) {
+        float2 st[MERGE_UNROLL];
+        float4 v[MERGE_UNROLL];
+#pragma unroll
+        for (int u = 0; u < MERGE_UNROLL; ++u) {
+            const int s = s0 + u * MERGE_WARPS;
+            const bool ok = s < n_s;
+            st[u] = ok ? ml[s] : make_float2(-INFINITY, 0.0f);
+            v[u] = ok ? po[(size_t)s * (D / 4)] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        __syncthreads();
-        w_s[threadIdx.x] = w;
-        __syncthreads();
-        const int n_here = min(MERGE_THREADS, n_s - s0);
-        if (threadIdx.x < D)
-            for (int j = 0; j < n_here; ++j) acc += w_s[j] * a.part_o[(slot0 + s0 + j) * D + threadIdx.x];
+#pragma unroll
+        for (int u = 0; u < MERGE_UNROLL; ++u) {
+            const float w = exp2f(st[u].x - M);       // 0 for the splits past the end
+            l += w * st[u].y;
+            acc.x += w * v[u].x; acc.y += w * v[u].y; acc.z += w * v[u].z; acc.w += w * v[u].w;
+        }
     }
-    const float L = block_sum(l, scratch);
-    if (threadIdx.x < D) a.out[((size_t)r * a.nq + head) * D + threadIdx.x] = __float2bfloat16_rn(acc / L);
+    if (active) acc_s[warp][lane] = acc;
+    if (lane == 0) l_s[warp] = l;
+    __syncthreads();
+    if (threadIdx.x < D / 4) {
+        float4 o = acc_s[0][threadIdx.x];
+        float L = l_s[0];
+#pragma unroll
+        for (int w = 1; w < MERGE_WARPS; ++w) {
+            const float4 t = acc_s[w][threadIdx.x];
+            o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+            L += l_s[w];
+        }
+        const float inv = 1.0f / L;
+        bf16* dst = a.out + ((size_t)r * a.nq + head) * D + threadIdx.x * 4;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(o.x * inv, o.y * inv), p1 = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&p0);
+        pk.y = *reinterpret_cast<uint32_t*>(&p1);
+        *reinterpret_cast<uint2*>(dst) = pk;
+    }
 }
 
 template <int D, bool TMA>
