@@ -322,12 +322,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
 }
 
 // One block per (row, query head): the row's partials, weighted by exp2(max_s - max) and normalised.  A warp
-// takes one split at a time (its D floats are one coalesced read, four per lane) and every MERGE_WARPS-th
+// takes one split at a time (its D floats are one coalesced read, four per lane) and every n-th (n warps a block)
 // split after it, several loads in flight; the warps' sums are then added in warp order, so the result
 // depends on the row's position alone.
-constexpr int MERGE_WARPS = 16;
+constexpr int MERGE_WARPS = 32;          // at most; the launch takes half of them for rows of few splits
 constexpr int MERGE_THREADS = MERGE_WARPS * 32;
 constexpr int MERGE_UNROLL = 4;
+constexpr int MERGE_WIDE_FROM = 256;     // splits from which a block of MERGE_WARPS warps pays
 
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(DecodeArgs a) {
@@ -342,21 +343,23 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
     const int pos = a.positions[r];
     const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
     const int n_s = pos / DEC_SPLIT - lo / DEC_SPLIT + 1;
+    // how many warps share a row is a matter of the row alone (the block may have more), as the order of the sum
+    const int warps = n_s >= MERGE_WIDE_FROM ? MERGE_WARPS : MERGE_WARPS / 2;
     const size_t slot0 = ((size_t)ri * a.nq + head) * a.max_splits;
     const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + slot0;
     float m = -INFINITY;
-    for (int s = threadIdx.x; s < n_s; s += MERGE_THREADS) m = fmaxf(m, ml[s].x);
+    for (int s = threadIdx.x; s < n_s; s += blockDim.x) m = fmaxf(m, ml[s].x);
     const float M = block_max(m, scratch);
     const bool active = lane < D / 4;
     const float4* po = reinterpret_cast<const float4*>(a.part_o + slot0 * D) + (active ? lane : 0);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float l = 0.0f;
-    for (int s0 = warp; s0 < n_s; s0 += MERGE_WARPS * MERGE_UNROLL) {
+    for (int s0 = warp; s0 < n_s && warp < warps; s0 += warps * MERGE_UNROLL) {
         float2 st[MERGE_UNROLL];
         float4 v[MERGE_UNROLL];
 #pragma unroll
         for (int u = 0; u < MERGE_UNROLL; ++u) {
-            const int s = s0 + u * MERGE_WARPS;
+            const int s = s0 + u * warps;
             const bool ok = s < n_s;
             st[u] = ok ? ml[s] : make_float2(-INFINITY, 0.0f);
             v[u] = ok ? po[(size_t)s * (D / 4)] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -368,14 +371,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
             acc.x += w * v[u].x; acc.y += w * v[u].y; acc.z += w * v[u].z; acc.w += w * v[u].w;
         }
     }
-    if (active) acc_s[warp][lane] = acc;
-    if (lane == 0) l_s[warp] = l;
+    if (active && warp < warps) acc_s[warp][lane] = acc;
+    if (lane == 0 && warp < warps) l_s[warp] = l;
     __syncthreads();
     if (threadIdx.x < D / 4) {
         float4 o = acc_s[0][threadIdx.x];
         float L = l_s[0];
-#pragma unroll
-        for (int w = 1; w < MERGE_WARPS; ++w) {
+        for (int w = 1; w < warps; ++w) {
             const float4 t = acc_s[w][threadIdx.x];
             o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
             L += l_s[w];
@@ -422,7 +424,8 @@ static int launch_decode(const DecodeArgs& a, int R, int splits, long long pool_
         rc = launch_split<D, false>(map, a, R, splits, stream);
     }
     if (rc != SHARPI_OK) return rc;
-    SHARPI_LAUNCH_PDL(attn_decode_merge_kernel<D>, dim3(R, a.nq), MERGE_THREADS, 0, stream, a);
+    SHARPI_LAUNCH_PDL(attn_decode_merge_kernel<D>, dim3(R, a.nq), splits >= MERGE_WIDE_FROM ? MERGE_THREADS : MERGE_THREADS / 2, 0,
+                      stream, a);
     return SHARPI_OK;
 }
 
