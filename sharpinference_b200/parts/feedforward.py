@@ -61,9 +61,8 @@ def _urgent_stream(device: torch.device) -> "torch.cuda.Stream":
 class MoESigmoidTop1(FeedForward):
     wants_fp32_input = True
     graph_safe = True
-    # Steps of up to this many rows run the shared expert beside the routing and the routed gate|up product;
-    # larger steps run it beside the routing only (see forward).
-    FORK_UP_TO = 256
+    # Steps of more rows than this keep the routed gate|up product on the routing's stream (see forward).
+    SMALL_STEP_ROWS = 256
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
                  shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):
@@ -89,40 +88,40 @@ class MoESigmoidTop1(FeedForward):
             h32 = h.to(torch.float32)
         # The shared expert and the routed ones meet only where the routed outputs are added, so the shared
         # expert runs on a second stream (inside a graph capture: a fork and a join), forked off before the
-        # routing.  Small steps: the shared expert's products stream their weights beside the routing and the
-        # routed gate|up product (two streams of weights keep the memory system busier than one); routing,
-        # sorting and gathering are short kernels that everything routed waits for, and on the stream of the
-        # shared product they would queue behind its many blocks, so they run on a third stream of higher
-        # priority.  Large steps: every product fills the GPU by itself, so what is worth hiding is the
-        # routing alone, and the streams join before the routed products.
+        # routing, and the streams join before the routed down product.  Routing, sorting and gathering are
+        # short kernels that everything routed waits for, and behind the shared product's many blocks they
+        # would queue, so they run on a third stream of higher priority.  Small steps: the routed gate|up
+        # product returns to the main stream and streams its weights beside the shared expert's (two streams
+        # of weights keep the memory system busier than one; with priority over the shared expert it measured
+        # slower).  Large steps: every product fills the GPU by itself; the routed gate|up product stays on the
+        # third stream and takes over the SMs as the shared expert's products drain.
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
         main = torch.cuda.current_stream(h.device)
-        side = None
-        large = T > self.FORK_UP_TO
+        side = routed = None
         if self.shared is not None:
             y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-            side = _side_stream(h.device)
+            side, routed = _side_stream(h.device), _urgent_stream(h.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 self.shared.forward(ctx, h, out=y)
+            routed.wait_stream(main)
         else:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
-        routing = main if large or side is None else _urgent_stream(h.device)
-        if routing is not main:
-            routing.wait_stream(main)
-        with torch.cuda.stream(routing):
+        act = None
+        with torch.cuda.stream(routed if routed is not None else main):
             expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
             h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
-        if routing is not main:
-            main.wait_stream(routing)
+            if tensor_core and T > self.SMALL_STEP_ROWS:
+                act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
+                                          row_scale=weight, scale_rows=sorted_rows)
+        if routed is not None:
+            main.wait_stream(routed)
         if "router_choices" in ctx.extras:          # tracing: which expert every row went to
             ctx.extras["router_choices"].append(expert)
-        if large and side is not None:
-            main.wait_stream(side)
-            side = None
         if tensor_core:
-            act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
-                                      row_scale=weight, scale_rows=sorted_rows)
+            if act is None:
+                act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
+                                          row_scale=weight, scale_rows=sorted_rows)
             if side is not None:
                 main.wait_stream(side)
             ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
