@@ -610,6 +610,35 @@ def test_attention_decode_rows(ops, nq, nkv, d, ps, mask):
     assert bool((out2[rest] == 7.0).all())
 
 
+def test_attention_decode_many_splits_and_batch_invariance(ops):
+    """A row over 70000 keys (274 splits: the merge shares it among more warps) beside short rows; a short
+    row's output is the same bits whether the long row is in the launch or not."""
+    nq, nkv, d, ps = 4, 1, 64, 64
+    lens = [70000, 600, 65536]
+    kv, table, ks, vs = paged_setup(lens, nkv, d, ps, torch.bfloat16, seed=77)
+    rows = [(0, 69999), (1, 599), (2, 65535), (2, 65279), (1, 0)]        # 274, 3, 256, 255 and 1 splits
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([b for b, _ in rows], dtype=torch.int32, device=DEV)
+    q = (rnd(len(rows), nq, d, seed=78) * 3.0).to(torch.bfloat16)      # peaked: a few far keys carry the output
+    scale = 1.0 / math.sqrt(d)
+    ref = attention_ref(q.cpu(), ks, vs, positions.cpu(), row_req.cpu(), lambda p: 0, scale, nq, nkv)
+    assert float(ref.abs().max()) > 0.5
+    out = torch.zeros(len(rows), nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=len(rows), nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=0, mask_span=1, scale=scale, max_context=70000)
+    assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2)
+    short = torch.tensor([1, 4], dtype=torch.int32, device=DEV)
+    alone = torch.zeros_like(out)
+    ops.attention_decode(q, kv, table, row_req, positions, alone, rows=short, num_rows=2, nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=0, mask_span=1, scale=scale, max_context=600)
+    assert torch.equal(alone[short.long()], out[short.long()])
+    near = torch.tensor([3], dtype=torch.int32, device=DEV)              # 255 splits, launched with narrow blocks
+    alone3 = torch.zeros_like(out)
+    ops.attention_decode(q, kv, table, row_req, positions, alone3, rows=near, num_rows=1, nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=0, mask_span=1, scale=scale, max_context=65280)
+    assert torch.equal(alone3[3], out[3])
+
+
 @pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 4), (6, 3, 48, 16), (5, 1, 128, 64), (8, 2, 128, 16), (3, 3, 80, 32)])
 @pytest.mark.parametrize("mask", [("full", 0), ("chunk", 100), ("chunk", 64), ("window", 50), ("window", 200)])
 def test_attention_prefill_tiles(ops, nq, nkv, d, ps, mask):
