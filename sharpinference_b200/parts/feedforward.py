@@ -63,6 +63,11 @@ class MoESigmoidTop1(FeedForward):
     graph_safe = True
     # Steps of more rows than this keep the routed gate|up product on the routing's stream (see forward).
     SMALL_STEP_ROWS = 256
+    # Up to this many rows the shared expert's down product runs on our own weight-streaming kernel instead of
+    # the library's: alone the library is a little faster on that shape, but beside the routed gate|up product
+    # the step is not (Scout sizes, 20 layers: batch 1 284 -> 292 tok/s, batch 4 693 -> 702; no difference
+    # from batch 8 on; the shared gate|up product and the attention projections measured slower that way).
+    SHARED_DOWN_OWN_ROWS = 4
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
                  shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):
@@ -74,6 +79,9 @@ class MoESigmoidTop1(FeedForward):
         self.router = router
         self.experts_gate_up, self.experts_down = experts_gate_up, experts_down
         self.shared = shared
+        shared_down = getattr(shared, "down", None)
+        if isinstance(shared_down, Linear) and shared_down.stream_rows == 0:
+            shared_down.stream_rows = self.SHARED_DOWN_OWN_ROWS
         self.num_experts = E
         self.act_dtype = act_dtype
         # the tensor-core path takes bfloat16 weights whose inner sizes are multiples of 8 (TMA rows
