@@ -434,11 +434,13 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
 _dense_offsets = {}
 
 
-def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Optional[torch.Tensor] = None,
+             accumulate: bool = False) -> torch.Tensor:
     """A dense product ``a . w^T`` for a few rows (decode) on the grouped tensor-core kernel with one
     group: the weights stream once through 128-row tiles, K cut over CTAs when the tiles alone would
     not fill the GPU.  ``swiglu``: ``w`` holds gate rows then up rows and the result is
-    ``silu(g) * u`` in bfloat16; otherwise float32 ``[M, N]``."""
+    ``silu(g) * u`` in bfloat16; otherwise float32 ``[M, N]``, added into ``out`` with reductions when
+    ``accumulate`` (so that another launch may add into the same rows meanwhile)."""
     M = a.shape[0]
     key = (a.device, M)
     offsets = _dense_offsets.get(key)
@@ -450,7 +452,7 @@ def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Opt
     k_split = 1 if n_tiles >= 148 else max(1, min(4, (2 * 148 + n_tiles - 1) // n_tiles))
     row_tile = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     return tc_grouped_gemm(a, w.unsqueeze(0), offsets, mode=TC_MODE_SWIGLU if swiglu else TC_MODE_STORE, out=out,
-                           row_tile=row_tile, k_split=k_split)
+                           row_tile=row_tile, k_split=k_split, accumulate=accumulate)
 
 
 def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False, sort: bool = False):

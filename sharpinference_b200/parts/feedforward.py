@@ -30,12 +30,12 @@ class DenseSwiGLU(FeedForward):
         self.gate_up, self.down, self.act_dtype = gate_up, down, act_dtype
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
         if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h):
             act = ops.tc_dense(h, self.gate_up.weight, swiglu=True)       # SwiGLU in the product's epilogue
         else:
             act = ops.swiglu(self.gate_up(h), self.act_dtype)
-        return self.down(act, out=out)
+        return self.down(act, out=out, accumulate=accumulate)
 
 
 _side_streams: dict = {}
@@ -67,6 +67,7 @@ class MoESigmoidTop1(FeedForward):
     # the library's: alone the library is a little faster on that shape, but beside the routed gate|up product
     # the step is not (Scout sizes, 20 layers: batch 1 284 -> 292 tok/s, batch 4 693 -> 702; no difference
     # from batch 8 on; the shared gate|up product and the attention projections measured slower that way).
+    # Both experts then add into the output with reductions and no longer wait for each other (296 and 715).
     SHARED_DOWN_OWN_ROWS = 4
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
@@ -103,15 +104,25 @@ class MoESigmoidTop1(FeedForward):
         # of weights keep the memory system busier than one; with priority over the shared expert it measured
         # slower).  Large steps: every product fills the GPU by itself; the routed gate|up product stays on the
         # third stream and takes over the SMs as the shared expert's products drain.
+        # When the shared expert's down product adds with reductions too (few rows, see SHARED_DOWN_OWN_ROWS),
+        # both experts add into a zeroed output and the streams need not meet before the end: each element is
+        # 0 + a + b in one order or the other, which is the same number.
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
         main = torch.cuda.current_stream(h.device)
         side = routed = None
+        apart = False
         if self.shared is not None:
-            y = torch.empty((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+            shared_down = getattr(self.shared, "down", None)
+            apart = tensor_core and isinstance(shared_down, Linear) and shared_down.streams(h)
+            make = torch.zeros if apart else torch.empty
+            y = make((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
             side, routed = _side_stream(h.device), _urgent_stream(h.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                self.shared.forward(ctx, h, out=y)
+                if apart:
+                    self.shared.forward(ctx, h, out=y, accumulate=True)
+                else:
+                    self.shared.forward(ctx, h, out=y)
             routed.wait_stream(main)
         else:
             y = torch.zeros((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
@@ -130,10 +141,12 @@ class MoESigmoidTop1(FeedForward):
             if act is None:
                 act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                           row_scale=weight, scale_rows=sorted_rows)
-            if side is not None:
+            if side is not None and not apart:
                 main.wait_stream(side)
             ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
                                 out_rows=sorted_rows, accumulate=True)
+            if apart:
+                main.wait_stream(side)
             return y
         gu = self.experts_gate_up(h, offsets, rows=T, a_rows=sorted_rows)          # sorted order
         act = ops.swiglu(gu, self.act_dtype, row_scale=weight, scale_rows=sorted_rows)

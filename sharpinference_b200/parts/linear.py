@@ -40,7 +40,15 @@ class Linear:
         # 20 % faster on these shapes (qkv 14 vs 18 us, shared gate|up 28 vs 37 us at 8 rows).
         self.stream_rows = stream_rows
 
-    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+        """``a . W^T`` into ``out``, or added to it (``accumulate``).  Only the product that :meth:`streams`
+        adds with reductions, so that another kernel may add into the same ``out`` at the same time."""
+        if accumulate:
+            if out is None:
+                raise ValueError("accumulate needs an output to add to")
+            if self.streams(a):
+                return ops.tc_dense(a, self.weight, out=out, accumulate=True)
+            return out.add_(self(a))
         w = self.weight
         if w.dtype == torch.float32:
             if a.dtype != torch.float32:

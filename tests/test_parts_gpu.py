@@ -186,3 +186,28 @@ def test_linear_on_the_weight_streaming_kernel():
     assert float((out - ref).abs().max()) / float(ref.abs().max()) < 1e-2
     lib = DenseSwiGLU(gate_up=Linear(gate_up.weight), down=Linear(down.weight), act_dtype=torch.bfloat16)
     assert float((lib.forward(None, hb).double().cpu() - out).abs().max()) / float(ref.abs().max()) < 1e-2
+
+
+def test_linear_adds_into_its_output():
+    """accumulate: the product is added to what the output holds, on the weight-streaming kernel (with
+    reductions) and on the library's (product, then an addition); a dense SwiGLU passes it on to its down product."""
+    from sharpinference_b200.parts import DenseSwiGLU, Linear
+    H, I, T = 136, 200, 3
+    w = rnd(H, I, scale=0.1, seed=5).to(torch.bfloat16).to(DEV)
+    a = rnd(T, I, seed=6).to(torch.bfloat16).to(DEV)
+    base = rnd(T, H, seed=7).to(DEV)
+    want = base.double().cpu() + a.double().cpu() @ w.double().cpu().T
+    for stream_rows in (0, 8):
+        lin = Linear(w, stream_rows=stream_rows)
+        assert lin.streams(a) == (stream_rows > 0)
+        out = base.clone()
+        assert lin(a, out=out, accumulate=True) is out
+        assert torch.allclose(out.double().cpu(), want, rtol=1e-4, atol=1e-3)
+    with pytest.raises(ValueError, match="output"):
+        Linear(w)(a, accumulate=True)
+    g, u = rnd(I, H, scale=0.1, seed=8).to(torch.bfloat16).to(DEV), rnd(I, H, scale=0.1, seed=9).to(torch.bfloat16).to(DEV)
+    h = rnd(T, H, seed=10).to(torch.bfloat16).to(DEV)
+    part = DenseSwiGLU(gate_up=Linear(torch.cat([g, u])), down=Linear(w, stream_rows=8), act_dtype=torch.bfloat16)
+    alone = part.forward(None, h)
+    added = part.forward(None, h, out=base.clone(), accumulate=True)
+    assert torch.allclose(added, base + alone, rtol=1e-6, atol=1e-6)
