@@ -457,8 +457,10 @@ def main() -> int:
     achieved = need / (ms * 1e-3) / 1e9
     points = {}
     for b in batches[1:]:
-        pms, _, _, _, _ = decode_run(b, max(3, steps // 2), through_engine=False)
+        pms, pdistinct, _, _, _ = decode_run(b, max(3, steps // 2), through_engine=False)
         points[f"decode_b{b}"] = b / pms * 1e3
+        # the same roofline figure as for the headline batch: bytes the step has to read / its time / the peak
+        points[f"decode_b{b}_roofline_frac"] = decode_bytes(cfg, b, ns.context, pdistinct) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"]
 
     out = {
         "metric": f"decode tok/s @ batch {ns.batch}, context {ns.context} "
