@@ -97,6 +97,22 @@ LARGE_SHAPES = {
 }
 
 
+# The layer widths of the large models themselves, two layers deep: a dense SwiGLU layer of Maverick's width
+# with chunked RoPE attention, then a mixture layer with global attention; few experts and a small vocabulary
+# keep it at 2 GB.
+REAL_WIDTHS = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 2048, "hidden_size": 5120, "num_hidden_layers": 2, "num_attention_heads": 40,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "intermediate_size_mlp": 16384,
+    "num_local_experts": 4, "num_experts_per_tok": 1, "interleave_moe_layer_step": 2,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
+                     "original_max_position_embeddings": 8192},
+    "no_rope_layers": [1], "attention_chunk_size": 512, "use_qk_norm": True, "attn_temperature_tuning": True,
+    "floor_scale": 512, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+
+
 TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT)}
 
 

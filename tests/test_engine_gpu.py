@@ -7,7 +7,7 @@ import torch
 
 import plain_llama4 as plain
 import traces
-from conftest import LARGE_SHAPES, TINY
+from conftest import LARGE_SHAPES, REAL_WIDTHS, TINY
 
 pytestmark = pytest.mark.gpu
 
@@ -39,9 +39,9 @@ def expected(model_dirs):
     return out
 
 
-def plain_under_engine_routing(model_dir, reqs, routing):
+def plain_under_engine_routing(model_dir, reqs, routing, dtype=torch.float64):
     """Plain logits per request with the engine's expert choices imposed; asserts near-ties."""
-    cfg, w = plain.load_folder(model_dir)
+    cfg, w = plain.load_folder(model_dir, dtype)
     ref, flips = {}, 0
     for rid, toks in reqs.items():
         margins = []
@@ -114,6 +114,35 @@ def test_large_model_shapes_in_small(large_shapes, cut, dtype):
     err, where = traces.worst_error(got, ref)
     print(f"large shapes {cut} {dtype}: worst relative error {err:.3e} at {where}; near-tie expert choices: {flips}")
     assert err < TOL[dtype], f"worst error {err:.3e} at {where}"
+    engine.cache.check_invariants()
+    assert all(g.pages.held_count == 0 for g in engine.cache.groups)
+
+
+@pytest.fixture(scope="module")
+def real_widths(tmp_path_factory):
+    from sharpinference_b200.weights import write_random_model
+    folder = str(tmp_path_factory.mktemp("real_widths"))
+    write_random_model(dict(REAL_WIDTHS), folder, 5, std=0.02, norm_std=0.1)
+    reqs = {f"W{i}": traces.random_tokens(2048, n, seed=17 * i + n) for i, n in enumerate([1100, 40, 300])}
+    return folder, reqs
+
+
+@pytest.mark.parametrize("cut", ["tail_decode", "mixed"])
+def test_layer_widths_of_the_large_models(real_widths, cut):
+    """Hidden 5120, 40/8 heads of 128, experts of 8192, a dense layer of 16384: the kernels at the sizes the
+    benchmarks run them at (the persistent expert product for the 1100-token prompt, K cut over CTAs for the
+    decoded tokens), against the plain implementation in 32-bit on the same bfloat16 weights."""
+    from sharpinference_b200 import Engine, EngineOptions
+    folder, reqs = real_widths
+    steps = CUTS[cut](reqs)
+    engine = Engine(folder, dtype="bfloat16", device="cuda:0",
+                    options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8))
+    routing = {}
+    got = traces.replay(engine, steps, routing)
+    ref, flips = plain_under_engine_routing(folder, reqs, routing, dtype=torch.float32)
+    err, where = traces.worst_error(got, ref)
+    print(f"real widths {cut}: worst relative error {err:.3e} at {where}; near-tie expert choices: {flips}")
+    assert err < TOL["bfloat16"], f"worst error {err:.3e} at {where}"
     engine.cache.check_invariants()
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
 
