@@ -492,7 +492,8 @@ def test_tc_grouped_gemm_store(ops, T, E, N, K, row_tile):
 
 @pytest.mark.parametrize("T,E,I,K,row_tile", [(8, 4, 128, 128, 16), (7, 3, 40, 88, 16), (64, 16, 256, 320, 16),
                                               (300, 5, 72, 264, 64), (900, 3, 200, 128, 128), (600, 2, 136, 64, 256),
-                                              (900, 3, 200, 128, 0), (2300, 7, 136, 320, 0)])
+                                              (900, 3, 200, 128, 0), (2300, 7, 136, 320, 0), (2048, 128, 136, 128, 0), (64, 128, 72, 64, 16),
+                                              (3000, 200, 40, 64, 0)])
 def test_tc_grouped_gemm_swiglu(ops, T, E, I, K, row_tile):
     expert, order, offsets, a = grouped_case(T, E, K, seed=T + I, empty=(0,) if E > 2 else ())
     w = rnd(E, 2 * I, K, dtype=torch.bfloat16, scale=0.1, seed=5)
