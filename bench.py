@@ -136,6 +136,19 @@ def prefill_flops(cfg, tokens):
     return cfg.num_hidden_layers * (tokens * per_token + attn) + 2 * V * H
 
 
+def prefill_floor_ms(cfg, tokens, pk):
+    """The least time a prompt step can take at the peaks given: the routed experts' products at the slower
+    of their flops and the bytes of the experts touched (at most one per token), everything else at its
+    flops.  With 16 experts and 2048 tokens the routed products are bound by memory."""
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    routed_flops = tokens * 2 * 3 * H * I
+    routed_bytes = min(cfg.num_local_experts, tokens) * 3 * H * I * 2
+    flops_s, bytes_s = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    routed = max(routed_flops / flops_s, routed_bytes / bytes_s)
+    rest = (prefill_flops(cfg, tokens) - cfg.num_hidden_layers * routed_flops) / flops_s
+    return (cfg.num_hidden_layers * routed + rest) * 1e3
+
+
 def inject_prefilled(engine, prompt, params):
     """Benchmark glue: a running request whose first len(prompt) - 1 positions are already cached
     (the pool holds random keys and values), so the next step decodes at that context."""
@@ -400,7 +413,11 @@ def main() -> int:
     pre = statistics.median(pre_ms)
     prefill = {"value": ns.prefill_tokens / pre * 1e3, "tokens": ns.prefill_tokens, "ms": pre,
                "frac": prefill_flops(cfg, ns.prefill_tokens) / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12),
-               "peak_tflops": pk["bf16_tflops"], "peak": pk_kind}
+               "peak_tflops": pk["bf16_tflops"], "peak": pk_kind,
+               # beside the contract's flops fraction: against the step's own floor, whose routed experts are
+               # bound by the bytes of their weights
+               "floor_ms": prefill_floor_ms(cfg, ns.prefill_tokens, pk)}
+    prefill["frac_of_floor"] = prefill["floor_ms"] / pre
 
     # ---- decode -----------------------------------------------------------------------------
     def decode_run(B, timed_steps, through_engine):
