@@ -367,7 +367,7 @@ def tc_row_tile(rows: int, mode: Optional[int] = None, groups: int = 1) -> int:
 def tc_k_split(rows: int, n_out: int, sms: int = 148) -> int:
     """Into how many CTAs a tile's K range is cut.  With few rows few experts are active (at most one
     per row), so 128-row weight tiles alone cannot fill the GPU; cutting K makes up to four times as many
-    CTAs.  The parts are added in a fixed order by a second kernel."""
+    CTAs.  The CTA of a tile that finishes last adds the parts in a fixed order."""
     if rows > 16:
         return 1
     ctas = rows * ((n_out + 127) // 128)

@@ -550,7 +550,7 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
 
 @pytest.mark.parametrize("k_split", [2, 4, 7])
 def test_tc_grouped_gemm_k_split(ops, k_split):
-    """Few rows: K is cut over several CTAs per tile and a second kernel adds the parts and applies the epilogue."""
+    """Few rows: K is cut over several CTAs per tile; the last of them adds the parts and applies the epilogue."""
     T, E, I, K = 5, 4, 136, 328
     expert, order, offsets, a = grouped_case(T, E, K, seed=31)
     w_gu = rnd(E, 2 * I, K, dtype=torch.bfloat16, scale=0.1, seed=32)
