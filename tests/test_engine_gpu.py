@@ -377,3 +377,62 @@ def test_command_line_generates(model_dirs, tmp_path):
                           timeout=600)
     assert proc.returncode == 0, proc.stderr
     assert len(proc.stdout.strip().splitlines()[-1].split("|")[-1].split()) == 4
+
+
+def random_configuration(seed: int) -> dict:
+    """A configuration drawn from everything the architecture's config.json may say: head sizes in steps of
+    16 (and one that is merely even), any heads and groups, widths and vocabularies that are no power of two,
+    layers of both kinds of attention and both kinds of feed-forward in any arrangement."""
+    import random
+    r = random.Random(seed)
+    nkv = r.choice([1, 2, 3])
+    nq = nkv * r.choice([1, 2, 3, 5])
+    d = r.choice([16, 32, 48, 64, 80, 96, 112, 128, 24])
+    layers = r.randint(2, 5)
+    hidden = r.choice([8 * r.randint(5, 20), 2 * r.randint(21, 60) + 2])          # the second: no multiple of 8
+    chunk = 16 * r.randint(1, 4)
+    scaling = None
+    if r.random() < 0.5:
+        scaling = {"rope_type": "llama3", "factor": r.choice([2.0, 8.0, 16.0]), "low_freq_factor": 1.0,
+                   "high_freq_factor": r.choice([1.0, 4.0]), "original_max_position_embeddings": r.choice([16, 24, 64])}
+    cfg = {
+        "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+        "vocab_size": r.randint(100, 500) | 1, "hidden_size": hidden, "num_hidden_layers": layers,
+        "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d,
+        "intermediate_size": r.choice([8 * r.randint(3, 17), 2 * r.randint(13, 40) + 2]),
+        "intermediate_size_mlp": 8 * r.randint(4, 30),
+        "num_local_experts": r.randint(1, 9), "num_experts_per_tok": 1, "interleave_moe_layer_step": r.choice([1, 2]),
+        "rope_theta": r.choice([1000.0, 10000.0, 500000.0]), "rope_scaling": scaling,
+        "no_rope_layers": sorted(r.sample(range(layers), r.randint(0, layers))),
+        "attention_chunk_size": chunk, "use_qk_norm": r.random() < 0.5, "qk_norm_eps": r.choice([1e-6, 1e-5]),
+        "attn_temperature_tuning": r.random() < 0.5, "floor_scale": r.randint(3, 40), "attn_scale": r.choice([0.1, 0.3]),
+        "rms_norm_eps": r.choice([1e-6, 1e-5, 1e-4]), "tie_word_embeddings": r.random() < 0.3,
+    }
+    if r.random() < 0.3:
+        cfg["moe_layers"] = sorted(r.sample(range(layers), r.randint(0, layers)))
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(24))
+def test_random_configurations(tmp_path, seed, dtype):
+    """Drawn configurations, mixed batches on a cache so small that pages are used again."""
+    from sharpinference_b200.weights import write_random_model
+    cfg = random_configuration(seed)
+    folder = str(tmp_path / "model")
+    write_random_model(dict(cfg), folder, 50 + seed, std=0.06, norm_std=0.1)
+    reqs = {f"q{i}": traces.random_tokens(cfg["vocab_size"], n, seed=7 * seed + n) for i, n in enumerate([3, 37, 90, 20, 55])}
+    steps = traces.mixed(reqs)
+    engine = make_engine(folder, dtype, traces.max_tokens(steps))
+    routing = {} if dtype == "bfloat16" else None
+    got = traces.replay(engine, steps, routing)
+    if routing is None:
+        pc, w = plain.load_folder(folder)
+        ref, flips = {rid: plain.forward(pc, w, toks) for rid, toks in reqs.items()}, 0
+    else:
+        ref, flips = plain_under_engine_routing(folder, reqs, routing)
+    err, where = traces.worst_error(got, ref)
+    print(f"random configuration {seed} {dtype}: {cfg}\n  worst relative error {err:.3e} at {where}; near ties: {flips}")
+    assert err < TOL[dtype], f"worst error {err:.3e} at {where} with {cfg}"
+    engine.cache.check_invariants()
+    assert all(g.pages.held_count == 0 for g in engine.cache.groups)
