@@ -436,3 +436,33 @@ def test_random_configurations(tmp_path, seed, dtype):
     assert err < TOL[dtype], f"worst error {err:.3e} at {where} with {cfg}"
     engine.cache.check_invariants()
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("seed", range(100, 108))
+def test_random_configurations_on_the_tensor_memory_attention(tmp_path, seed):
+    """Drawn configurations with head sizes 64 and 128 and pages of 64 positions, which is what the tcgen05
+    attention kernel for prompts takes; prompts long enough for several of its tiles, chunks of one to four pages."""
+    import random
+    from sharpinference_b200 import Engine, EngineOptions
+    from sharpinference_b200.weights import write_random_model
+    r = random.Random(seed)
+    cfg = random_configuration(seed)
+    cfg["head_dim"] = r.choice([64, 128])
+    cfg["attention_chunk_size"] = 64 * r.randint(1, 4)
+    cfg["hidden_size"] = 8 * r.randint(5, 20)
+    cfg["intermediate_size"] = 8 * r.randint(3, 17)
+    folder = str(tmp_path / "model")
+    write_random_model(dict(cfg), folder, seed, std=0.06, norm_std=0.1)
+    reqs = {f"q{i}": traces.random_tokens(cfg["vocab_size"], n, seed=seed + n) for i, n in enumerate([300, 130, 70])}
+    for cut in ("whole", "tail_decode"):
+        steps = CUTS[cut](reqs)
+        engine = Engine(folder, dtype="bfloat16", device="cuda:0",
+                        options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8))
+        assert engine.runner.attention_tile == 128
+        routing = {}
+        got = traces.replay(engine, steps, routing)
+        ref, flips = plain_under_engine_routing(folder, reqs, routing)
+        err, where = traces.worst_error(got, ref)
+        print(f"random configuration {seed} {cut}: {cfg}\n  worst relative error {err:.3e} at {where}; near ties: {flips}")
+        assert err < TOL["bfloat16"], f"worst error {err:.3e} at {where} with {cfg}"
+        engine.cache.check_invariants()
