@@ -466,3 +466,23 @@ def test_random_configurations_on_the_tensor_memory_attention(tmp_path, seed):
         print(f"random configuration {seed} {cut}: {cfg}\n  worst relative error {err:.3e} at {where}; near ties: {flips}")
         assert err < TOL["bfloat16"], f"worst error {err:.3e} at {where} with {cfg}"
         engine.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(16))
+def test_drawn_schedules(model_dirs, expected, seed, dtype):
+    """Schedules drawn at random (who is live, who sits out, portion sizes, wanted places) on a cache that
+    holds no more than the schedule needs at its fullest."""
+    name = "ABCD"[seed % 4]
+    reqs = requests_for(name)
+    steps = traces.drawn(reqs, seed)
+    engine = make_engine(model_dirs[name], dtype, traces.max_tokens(steps))
+    routing = {} if dtype == "bfloat16" else None
+    got = traces.replay(engine, steps, routing)
+    ref, flips = (expected[name], 0) if routing is None else plain_under_engine_routing(model_dirs[name], reqs, routing)
+    err, where = traces.worst_error(got, ref)
+    print(f"{name} drawn schedule {seed} {dtype}: {len(steps)} steps, worst relative error {err:.3e} at {where}")
+    assert err < TOL[dtype], f"worst error {err:.3e} at {where}"
+    engine.cache.check_invariants()
+    assert not engine.cache.requests
+    assert all(g.pages.held_count == 0 for g in engine.cache.groups)

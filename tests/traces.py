@@ -86,6 +86,43 @@ def mixed(requests: Dict[str, List[int]], max_live: int = 4, tail: int = 6,
     return steps
 
 
+def drawn(requests: Dict[str, List[int]], seed: int, max_live: int = 4) -> List[dict]:
+    """A drawn schedule: up to ``max_live`` requests live; each step every live request either sits out,
+    brings one token, or brings a portion of a drawn size (1 to 40); the wanted places are a drawn subset of
+    the portion's places that always holds its last one."""
+    import random
+    r = random.Random(seed)
+    waiting = list(requests.items())
+    r.shuffle(waiting)
+    live: List[Tuple[str, List[int], int]] = []
+    steps, s = [], 0
+    while waiting or live:
+        while waiting and len(live) < max_live and (not live or r.random() < 0.5):
+            rid, toks = waiting.pop(0)
+            live.append((rid, toks, 0))
+        entries, ended, nxt = [], [], []
+        order = list(live)
+        r.shuffle(order)
+        for rid, toks, at in order:
+            left = len(toks) - at
+            kind = r.random()
+            if kind < 0.15 and len(order) > 1:
+                nxt.append((rid, toks, at))
+                continue
+            n = 1 if kind < 0.5 else min(left, r.choice([1, 2, 2, 3, 5, 8, 16, 17, 31, 40]))
+            want = sorted(set(i for i in range(n) if r.random() < 0.6) | {n - 1})
+            entries.append({"id": rid, "tokens": toks[at:at + n], "want": want})
+            if at + n == len(toks):
+                ended.append(rid)
+            else:
+                nxt.append((rid, toks, at + n))
+        live = nxt
+        if entries:
+            steps.append({"step": s, "entries": entries, "end": ended})
+            s += 1
+    return steps
+
+
 def max_tokens(steps: List[dict]) -> int:
     """The most positions live requests hold at any time, each rounded up to a multiple of 64."""
     held: Dict[str, int] = {}
