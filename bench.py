@@ -115,10 +115,15 @@ def layer_counts(cfg):
 
 
 def decode_bytes(cfg, batch, context, distinct_experts_per_layer, itemsize=2):
-    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests.
+    ``distinct_experts_per_layer`` has one entry per mixture layer, in layer order."""
     H, d, nq, nkv, I = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
-    per_layer = ((nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I) * itemsize + (cfg.num_local_experts * H + 2 * H) * 4
-    weights = cfg.num_hidden_layers * per_layer + sum(distinct_experts_per_layer) * 3 * H * I * itemsize
+    attention = ((nq + 2 * nkv) * d * H + H * nq * d) * itemsize + 2 * H * 4
+    mixture = 3 * H * I * itemsize + cfg.num_local_experts * H * 4                  # shared expert and router
+    dense = 3 * H * cfg.intermediate_size_mlp * itemsize
+    moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
+    weights = cfg.num_hidden_layers * attention + moe_layers * mixture + (cfg.num_hidden_layers - moe_layers) * dense
+    weights += sum(distinct_experts_per_layer) * 3 * H * I * itemsize
     weights += cfg.vocab_size * H * itemsize + batch * H * itemsize + H * 4
     rope_layers, nope_layers = layer_counts(cfg)
     pos = context - 1
