@@ -135,10 +135,14 @@ def decode_bytes(cfg, batch, context, distinct_experts_per_layer, itemsize=2):
 def prefill_flops(cfg, tokens):
     H, d, nq, nkv, I, V = (cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads,
                            cfg.intermediate_size, cfg.vocab_size)
-    per_token = 2 * H * (nq + 2 * nkv) * d + 2 * H * nq * d + 2 * H * cfg.num_local_experts + 2 * 2 * 3 * H * I
+    attention = 2 * H * (nq + 2 * nkv) * d + 2 * H * nq * d
+    mixture = 2 * H * cfg.num_local_experts + 2 * 2 * 3 * H * I          # router, shared and routed expert
+    dense = 2 * 3 * H * cfg.intermediate_size_mlp
+    moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
+    per_token = cfg.num_hidden_layers * attention + moe_layers * mixture + (cfg.num_hidden_layers - moe_layers) * dense
     pairs = tokens * (tokens + 1) // 2               # causal (query, key) pairs within one chunk
     attn = 4 * nq * d * pairs
-    return cfg.num_hidden_layers * (tokens * per_token + attn) + 2 * V * H
+    return tokens * per_token + cfg.num_hidden_layers * attn + 2 * V * H
 
 
 def prefill_floor_ms(cfg, tokens, pk):
@@ -150,8 +154,9 @@ def prefill_floor_ms(cfg, tokens, pk):
     routed_bytes = min(cfg.num_local_experts, tokens) * 3 * H * I * 2
     flops_s, bytes_s = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
     routed = max(routed_flops / flops_s, routed_bytes / bytes_s)
-    rest = (prefill_flops(cfg, tokens) - cfg.num_hidden_layers * routed_flops) / flops_s
-    return (cfg.num_hidden_layers * routed + rest) * 1e3
+    moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
+    rest = (prefill_flops(cfg, tokens) - moe_layers * routed_flops) / flops_s
+    return (moe_layers * routed + rest) * 1e3
 
 
 def inject_prefilled(engine, prompt, params):
