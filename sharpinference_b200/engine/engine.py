@@ -16,9 +16,8 @@ or request by request: ``add_request`` / ``step`` / ``has_unfinished``; or below
 from __future__ import annotations
 
 import itertools
-import time
-from dataclasses import dataclass, field
-from typing import Dict, Hashable, Iterable, List, Optional, Sequence, Union
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
@@ -26,7 +25,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, SamplerState
 from ..weights.loading import load_model, parse_dtype
-from .scheduler import FINISHED, Request, Scheduler, StepPlan
+from .scheduler import FINISHED, Request, Scheduler
 from .step import StepEntry, StepRunner
 
 
@@ -110,7 +109,6 @@ class Engine:
         if o.max_cache_tokens is not None:
             return max(1, (o.max_cache_tokens + o.page_size - 1) // o.page_size)
         per_token = 0
-        seen = {}
         itemsize = torch.empty((), dtype=self.model.act_dtype).element_size()
         for entry in self.model.schedule:
             spec = getattr(self.model.blocks[entry.layer].mixer, "cache_spec", None)

@@ -6,8 +6,6 @@ squares, the rsqrt and the scaling are float32.
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 
 from ..kernels import ops

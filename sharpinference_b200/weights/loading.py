@@ -17,7 +17,7 @@ import torch
 from ..config.base import read_config_json
 from ..registry import Architecture, get_architecture, resolve
 from . import safetensors_io
-from .source import DeclaringWeights, FileWeights, RandomWeights, TensorDecl, WeightError
+from .source import DeclaringWeights, FileWeights, RandomWeights, TensorDecl
 
 _DTYPE_ALIASES = {
     "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, torch.bfloat16: torch.bfloat16,
