@@ -63,6 +63,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-cache-tokens", type=int, default=None)
     ap.add_argument("--json", action="store_true", help="print the result as one JSON object")
+    ap.add_argument("--trace-layers", action="store_true",
+                    help="after every step print, per layer, the L2 norm of the last row's residual and the expert "
+                         "it was routed to (steps then run eagerly); for finding the first layer that differs")
     return ap
 
 
@@ -114,8 +117,19 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     t_first = None
+    if ns.trace_layers:
+        engine.runner.trace_layers = engine.runner.trace_router = True
+    steps = 0
     while engine.has_unfinished:
         engine.step()
+        if ns.trace_layers:
+            picks = iter(engine.runner.last_router_choices)
+            for layer, norms in enumerate(engine.runner.last_layer_norms):
+                routed = getattr(engine.model.blocks[engine.model.schedule[layer].layer].ffn, "num_experts", 0) > 0
+                expert = int(next(picks)[-1]) if routed else None
+                print(f"step {steps} layer {layer}: |x| = {float(norms[-1]):.6f}"
+                      + (f", expert {expert}" if expert is not None else ""), file=sys.stderr)
+        steps += 1
         if t_first is None and all(engine.output(i).tokens or engine.output(i).finished for i in ids):
             torch.cuda.synchronize()
             t_first = time.perf_counter()

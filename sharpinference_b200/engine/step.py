@@ -57,6 +57,12 @@ class StepRunner:
         # (one int32 [T] tensor per routed schedule entry, in schedule order).  The reference
         # prints the same with SHARPI_TRACE_ROUTERS (src/SharpInference.Engine/ForwardPass.cs:2042-2056).
         self.trace_router = False
+        # `trace_layers`: after every scheduled block the L2 norm of every row of the residual stream, in
+        # `last_layer_norms` (one float32 [T] tensor per schedule entry); the reference prints the same per
+        # layer with SHARPI_TRACE_NORMS (src/SharpInference.Engine/ForwardPass.cs:1795-1819).  Traced steps
+        # run eagerly, never as a replayed graph.
+        self.trace_layers = False
+        self.last_layer_norms: list = []
         # after every step, read the word in which a tensor-core kernel records a wait that gave up
         # (a 4-byte copy; the step's result is read by the host right after anyway)
         self.check_kernel_status = True
@@ -233,14 +239,17 @@ class StepRunner:
         self.validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
         logits, done, num_tokens = None, False, sum(len(e.tokens) for e in entries)
-        if self.use_graphs and not self.trace_router and num_tokens == len(entries):
+        if self.use_graphs and not (self.trace_router or self.trace_layers) and num_tokens == len(entries):
             done, logits = self._run_decode_graph(entries)
         if not done:
             ctx = self.build_context(entries)
             if self.trace_router:
                 ctx.extras["router_choices"] = []
+            if self.trace_layers:
+                ctx.extras["layer_norms"] = []
             logits = self.model.forward(ctx)
             self.last_router_choices = ctx.extras.get("router_choices", [])
+            self.last_layer_norms = ctx.extras.get("layer_norms", [])
         if self.check_kernel_status:
             self._note_status()
         for e in entries:

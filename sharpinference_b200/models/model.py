@@ -68,8 +68,12 @@ class DecoderModel:
         ``ctx.want_rows`` (None if no logits are wanted)."""
         x = ops.embed_gather(ctx.token_ids, self.embedding)
         pending = None
+        norms = ctx.extras.get("layer_norms")        # tracing: see StepRunner.trace_layers
         for index, entry in enumerate(self.schedule):
             x, pending = self.blocks[entry.layer].forward(ctx, ctx.slots[index], x, pending)
+            if norms is not None:
+                after = x.float() if pending is None else x.float() + pending.float()
+                norms.append(after.square().sum(dim=1).sqrt())
         if ctx.want_rows is None or ctx.want_rows.numel() == 0:
             return None
         h, _ = self.final_norm.apply(x, pending, rows=ctx.want_rows, out_dtype=self.act_dtype)

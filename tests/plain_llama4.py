@@ -250,13 +250,15 @@ def moe_ffn(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tensor, choi
 # ---------------------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], schedule=None,
             choices: Optional[list] = None, forced: Optional[list] = None,
-            margins: Optional[list] = None) -> torch.Tensor:
+            margins: Optional[list] = None, layer_norms: Optional[list] = None) -> torch.Tensor:
     """Logits [S, V] of a whole sequence: embedding (src/SharpInference.Engine/ForwardPass.cs:2230-2244),
     then per layer ``x += attn(norm(x))`` and ``x += ffn(norm(x))`` (:1557-1714), the final norm and
     the output product (:1740-1747; the embedding serves as output matrix when tied, :411-413).
     ``schedule`` is a list of ``(layer, borrow)``: run that layer's block, reading the keys and
     values that schedule entry ``borrow`` produced if it is not None; default: every layer once.
-    ``forced``: per routed schedule entry, in order, the expert of every token (see ``moe_ffn``)."""
+    ``forced``: per routed schedule entry, in order, the expert of every token (see ``moe_ffn``).
+    ``layer_norms``: a list that receives, per schedule entry, the L2 norm of every position's residual
+    after the layer (what SHARPI_TRACE_NORMS prints, :1795-1819)."""
     dtype = w["model.embed_tokens.weight"].dtype
     eps = cfg.get("rms_norm_eps", 1e-5)
     x = w["model.embed_tokens.weight"][torch.as_tensor(list(tokens), dtype=torch.long)]
@@ -282,6 +284,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], schedu
         else:
             x = x + dense_ffn(h, w[p + "feed_forward.gate_proj.weight"], w[p + "feed_forward.up_proj.weight"],
                               w[p + "feed_forward.down_proj.weight"])
+        if layer_norms is not None:
+            layer_norms.append(x.square().sum(dim=1).sqrt())
     x = rms_norm(x, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return (x @ head.T).to(dtype)

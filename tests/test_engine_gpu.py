@@ -377,6 +377,13 @@ def test_command_line_generates(model_dirs, tmp_path):
                           timeout=600)
     assert proc.returncode == 0, proc.stderr
     assert len(proc.stdout.strip().splitlines()[-1].split("|")[-1].split()) == 4
+    # --trace-layers: a line per step and layer, with the expert where the layer is a mixture (layers 1, 3, 5 of B)
+    proc = subprocess.run([cli, "-m", model_dirs["B"], "-p", "5 17 3", "-n", "2", "--temp", "0", "--page-size", "16",
+                           "--max-cache-tokens", "128", "--trace-layers"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    lines = [ln for ln in proc.stderr.splitlines() if ln.startswith("step ")]
+    assert len(lines) == 2 * TINY_B["num_hidden_layers"]
+    assert "step 0 layer 1: |x| = " in proc.stderr and ", expert " in lines[1] and ", expert " not in lines[0]
 
 
 def random_configuration(seed: int) -> dict:
@@ -486,3 +493,26 @@ def test_drawn_schedules(model_dirs, expected, seed, dtype):
     engine.cache.check_invariants()
     assert not engine.cache.requests
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_layer_trace_follows_the_plain_implementation(model_dirs, name):
+    """trace_layers: the residual's L2 norm per row after every layer, for finding the first layer that
+    differs; in 32-bit it equals the plain implementation's layer by layer."""
+    from sharpinference_b200 import StepEntry
+    toks = requests_for(name)["r2"]
+    engine = make_engine(model_dirs[name], "float32", 128)
+    engine.runner.trace_layers = True
+    engine.open_request("t")
+    engine.forward_step([StepEntry("t", toks[:-3], [])])
+    first = [n.cpu() for n in engine.runner.last_layer_norms]
+    engine.forward_step([StepEntry("t", toks[-3:], [2])])
+    second = [n.cpu() for n in engine.runner.last_layer_norms]
+    engine.close_request("t")
+    cfg, w = plain.load_folder(model_dirs[name])
+    want = []
+    plain.forward(cfg, w, toks, layer_norms=want)
+    assert len(first) == len(second) == len(want) == cfg["num_hidden_layers"]
+    for layer, ref in enumerate(want):
+        got = torch.cat([first[layer], second[layer]]).double()
+        assert torch.allclose(got, ref.double(), rtol=1e-5, atol=1e-6), f"layer {layer}"
