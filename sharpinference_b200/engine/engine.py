@@ -178,6 +178,17 @@ class Engine:
             outputs.append(self._output(req))
         return outputs
 
+    def metrics(self) -> dict:
+        """Counters of the serving machinery at this moment: what the reference's batching engine exposes as
+        QueueDepth, ActiveRequests and KvTokenBudget (src/SharpInference.Engine/ContinuousBatchingEngine.cs:180-187),
+        plus the pages of every cache group and the totals of ``stats``."""
+        groups = {g.index: {"kind": g.spec.kind, "pages": g.pages.capacity, "free": g.pages.free_count,
+                            "held": g.pages.held_count} for g in self.cache.groups}
+        return {"queued": len(self.scheduler.waiting), "running": len(self.scheduler.running),
+                "page_size": self.cache.page_size, "cache_groups": groups,
+                "state_slots_free": self.cache.state_slots.free_count,
+                "graph_replays": self.runner.graph_replays, **self.stats}
+
     def _output(self, req: Request) -> RequestOutput:
         return RequestOutput(req.request_id, list(req.prompt), list(req.generated), req.status == FINISHED,
                              req.finish_reason, req.preemptions)

@@ -267,6 +267,11 @@ def test_generation_with_preemption_gives_the_same_tokens(model_dirs):
     assert got == want
     assert engine.scheduler.num_preemptions >= 1
     assert not engine.cache.requests
+    m = engine.metrics()
+    assert m["queued"] == 0 and m["running"] == 0 and m["preemptions"] == engine.scheduler.num_preemptions
+    assert all(g["free"] == g["pages"] == 9 and g["held"] == 0 for g in m["cache_groups"].values())
+    # every prompt token and all but each request's last new token went through a step, some of them twice
+    assert m["decode_tokens"] + m["prefill_tokens"] >= 60 + 3 * 11 and m["prefill_tokens"] >= 60 and m["steps"] > 12
 
 
 def test_temperature_sampling_is_reproducible_and_follows_the_distribution(model_dirs):
