@@ -432,7 +432,8 @@ def main() -> int:
     # ---- decode -----------------------------------------------------------------------------
     def decode_run(B, timed_steps, through_engine):
         """B requests at `context`; returns (ms per step, distinct experts per layer, bytes moved per step)."""
-        total = warmup + timed_steps + 1
+        traced = 0 if through_engine else 4           # eager steps that record which experts the batch uses
+        total = warmup + timed_steps + traced
         ids = [inject_prefilled(engine, tokens(ns.context - total), greedy) for _ in range(B)]
         reqs = [engine._requests[i] for i in ids]
         h2d = d2h = 0
@@ -453,10 +454,13 @@ def main() -> int:
             d2h = 4 * B
         else:
             last = [r.tokens[-1] for r in reqs]
-            engine.runner.trace_router = True        # one traced step: which experts this batch uses
-            logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
-            last = engine.sampler.sample(logits, [r.sampler for r in reqs])
-            distinct = [len(set(c.tolist())) for c in engine.runner.last_router_choices]
+            engine.runner.trace_router = True        # distinct experts per mixture layer, the mean of a few steps
+            counts = []
+            for _ in range(traced):
+                logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
+                last = engine.sampler.sample(logits, [r.sampler for r in reqs])
+                counts.append([len(set(c.tolist())) for c in engine.runner.last_router_choices])
+            distinct = [round(sum(col) / traced, 2) for col in zip(*counts)]
             engine.runner.trace_router = False
             for _ in range(warmup):                   # includes the capture of this shape's CUDA graph
                 logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
