@@ -285,8 +285,9 @@ def timeline_run(ns, cfg) -> int:
                  "gather_rows_bf16", "tc_grouped_gemm"):
         setattr(ops, name, bracket(name, getattr(ops, name)))
     plain_call = linear_mod.Linear.__call__
-    linear_mod.Linear.__call__ = lambda self, a, out=None: bracket(
-        f"library product [{self.out_features} x {self.in_features}]", lambda: plain_call(self, a, out=out))()
+    linear_mod.Linear.__call__ = lambda self, a, out=None, accumulate=False: bracket(
+        f"dense product [{self.out_features} x {self.in_features}]" + (" (own kernel)" if self.streams(a) else ""),
+        lambda: plain_call(self, a, out=out, accumulate=accumulate))()
     last = [r.tokens[-1] for r in reqs]
     per_step = []
     for _ in range(6):                               # the first step runs eagerly, the second is captured, then replays
