@@ -89,11 +89,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the last tiles of a prompt have the most keys: start them first, so that the short ones fill the tail
-    const int* tile = a.tiles + (size_t)(gridDim.x - 1 - blockIdx.x) * 4;
+    // The last tiles of a prompt have the most keys: start them first, for every head (the head is the fast
+    // index of the grid, so CTAs are handed out tile by tile, all heads of a tile together: the short tiles
+    // of all heads fill the tail, and the query heads of a kv head read its keys at the same time).
+    const int* tile = a.tiles + (size_t)(gridDim.y - 1 - blockIdx.y) * 4;
     const int row0 = tile[0], n_rows = tile[1], p0 = tile[2];
     const int* table = a.block_table + (size_t)tile[3] * a.max_blocks;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (a.nq / a.nkv);
     const int p_last = p0 + n_rows - 1;
     const int key_lo = visible_lo(p0, a.mask_kind, a.mask_span);
@@ -319,7 +321,7 @@ static int launch_tc(const CUtensorMap& qm, const CUtensorMap& kvm, const Prefil
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
-    attn_prefill_tc_kernel<D><<<dim3(n_tiles, a.nq), TC_ATT_THREADS, Cfg::SMEM, stream>>>(qm, kvm, a);
+    attn_prefill_tc_kernel<D><<<dim3(a.nq, n_tiles), TC_ATT_THREADS, Cfg::SMEM, stream>>>(qm, kvm, a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -330,6 +332,7 @@ SHARPI_API int sharpi_attention_prefill_tc(const void* q, const void* kv, const 
                                            int d, int max_blocks, int page_size, int mask_kind, int mask_span,
                                            float scale, cudaStream_t stream) {
     if (n_tiles <= 0) return SHARPI_OK;
+    if (n_tiles > 65535) return SHARPI_BAD_ARGUMENT;        // tiles are the grid's second extent
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || max_blocks <= 0 || nq > 65535 || !status) return SHARPI_BAD_ARGUMENT;
     if (d != 64 && d != 128) return SHARPI_BAD_ARGUMENT;
     if (!(scale > 0.0f)) return SHARPI_BAD_ARGUMENT;
