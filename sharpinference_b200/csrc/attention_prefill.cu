@@ -58,10 +58,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(PrefillArgs
     bf16* kv_s = q_s + PF_BQ * LD;                         // [2 stages][K|V][64][LD]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* tile = a.tiles + (size_t)blockIdx.x * 4;
+    // the head is the grid's fast index and the last tiles (the ones with the most keys) come first, so that
+    // every head's longest tiles start first and the short ones fill the tail
+    const int* tile = a.tiles + (size_t)(gridDim.y - 1 - blockIdx.y) * 4;
     const int row0 = tile[0], n_rows = tile[1], p0 = tile[2];
     const int* table = a.block_table + (size_t)tile[3] * a.max_blocks;
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (a.nq / a.nkv);
 
     const int p_last = p0 + n_rows - 1;
@@ -218,7 +220,7 @@ static int launch_prefill(const PrefillArgs& a, int n_tiles, cudaStream_t stream
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
-    attn_prefill_kernel<D><<<dim3(n_tiles, a.nq), PF_THREADS, SMEM, stream>>>(a);
+    attn_prefill_kernel<D><<<dim3(a.nq, n_tiles), PF_THREADS, SMEM, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -227,6 +229,7 @@ SHARPI_API int sharpi_attention_prefill(const void* q, const void* kv, const int
                                         void* out, int n_tiles, int nq, int nkv, int d, int max_blocks, int page_size,
                                         int mask_kind, int mask_span, float scale, cudaStream_t stream) {
     if (n_tiles <= 0) return SHARPI_OK;
+    if (n_tiles > 65535) return SHARPI_BAD_ARGUMENT;        // tiles are the grid's second extent
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || nq > 65535)
         return SHARPI_BAD_ARGUMENT;
     if (mask_kind != SHARPI_MASK_FULL && mask_span <= 0) return SHARPI_BAD_ARGUMENT;
