@@ -3,7 +3,9 @@
 // The work is reading every visible key and value once, so the kernel is organised around
 // bytes in flight: one CTA takes one (row, kv head, split of 256 keys) and serves all the query
 // heads of that kv head at once, so keys and values are read once per group, not once per
-// query head.  Splits sit at absolute multiples of 256 positions, so the order in which a row's
+// query head.  For rows of unequal lengths the grid's first extent counts the splits of all rows together
+// (a CTA finds its row by a prefix sum over the rows' split counts), so a batch of one long row and many
+// short ones launches what it has, not rows times the longest row's splits.  Splits sit at absolute multiples of 256 positions, so the order in which a row's
 // keys are reduced depends on the row's position alone, never on the batch.  Each CTA writes an
 // unnormalised partial (max, sum, weighted values); a second kernel merges a row's partials.
 //
@@ -38,6 +40,7 @@ struct DecodeArgs {
     float* part_ml;           // [R, nq, max_splits, 2]   (max in log2 units, sum)
     bf16* out;                // [T, nq * D]
     int nq, nkv, max_blocks, page_size, page_shift, mask_kind, mask_span, max_splits;
+    int num_rows;             // R
     float scale_log2;         // softmax scale * log2(e)
     int* status;              // device word for a wait that gave up (TMA path)
 };
@@ -72,7 +75,7 @@ __device__ __forceinline__ void decode_load_chunk(const DecodeArgs& a, const int
 //                 of the head size, 128-byte swizzle) that complete on an mbarrier; ldmatrix undoes the
 //                 swizzle in its addresses.  Needs pages of a multiple of 16 positions and a head size of
 //                 64 or 128, and cuts the instructions spent on loading to a few per pass.
-template <int D, bool TMA>
+template <int D, bool TMA, bool COMPACT>
 __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                            DecodeArgs a) {
     constexpr int LD = TMA ? 64 : D + 8;   // row pitch in elements: swizzled 128-byte rows, or padded rows
@@ -93,11 +96,49 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
     const int kvh = blockIdx.y / groups, hg = blockIdx.y % groups;
     const int head0 = kvh * G + hg * 16;
     const int heads_here = min(16, G - hg * 16);
-    const int ri = blockIdx.z;
-    const int r = a.rows ? a.rows[ri] : ri;
-    const int pos = a.positions[r];
-    const int lo = visible_lo(pos, a.mask_kind, a.mask_span);
-    const int split = lo / DEC_SPLIT + blockIdx.x;
+    // COMPACT: blockIdx.x counts splits over all rows: find the row whose splits hold it (every warp does the
+    // same scan over the rows, 32 at a time) and the split's number within that row.  Otherwise the grid is
+    // (splits of the longest row, ., rows), which costs nothing to decode and suits rows of similar lengths.
+    int ri = -1, r = 0, pos = 0, lo = 0, split_in_row = 0;
+    if (!COMPACT) {
+        ri = blockIdx.z;
+        r = a.rows ? a.rows[ri] : ri;
+        pos = a.positions[r];
+        lo = visible_lo(pos, a.mask_kind, a.mask_span);
+        split_in_row = blockIdx.x;
+    } else {
+        const int item = blockIdx.x;
+        int base = 0;
+        for (int r0 = 0; r0 < a.num_rows; r0 += 32) {
+            const int i = r0 + lane;
+            int rr = 0, p = 0, l = 0, n = 0;
+            if (i < a.num_rows) {
+                rr = a.rows ? a.rows[i] : i;
+                p = a.positions[rr];
+                l = visible_lo(p, a.mask_kind, a.mask_span);
+                n = p / DEC_SPLIT - l / DEC_SPLIT + 1;
+            }
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int here = __shfl_sync(0xffffffffu, incl, 31);
+            if (item < base + here) {
+                const int owner = __ffs(__ballot_sync(0xffffffffu, item < base + incl)) - 1;
+                ri = r0 + owner;
+                r = __shfl_sync(0xffffffffu, rr, owner);
+                pos = __shfl_sync(0xffffffffu, p, owner);
+                lo = __shfl_sync(0xffffffffu, l, owner);
+                split_in_row = item - base - __shfl_sync(0xffffffffu, incl - n, owner);
+                break;
+            }
+            base += here;
+        }
+    }
+    if (ri < 0) return;          // past the last row's last split (pdl_wait has been called above)
+    const int split = lo / DEC_SPLIT + split_in_row;
     const int k_begin = max(lo, split * DEC_SPLIT);
     const int k_end = min(pos, split * DEC_SPLIT + DEC_SPLIT - 1);
     if (k_begin > k_end) return;
@@ -312,7 +353,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) attn_decode_split_kernel(const
             acc += f * base_o[w * warp_stride + g * D + dd];
             L += f * base_o[w * warp_stride + 16 * D + g * 2 + 1];
         }
-        const size_t slot = ((size_t)ri * a.nq + head0 + g) * a.max_splits + blockIdx.x;
+        const size_t slot = ((size_t)ri * a.nq + head0 + g) * a.max_splits + split_in_row;
         a.part_o[slot * D + dd] = acc;
         if (dd == 0) {
             a.part_ml[slot * 2] = M;
@@ -392,36 +433,44 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_decode_merge_kernel(Decode
     }
 }
 
-template <int D, bool TMA>
-static int launch_split(const CUtensorMap& map, const DecodeArgs& a, int R, int splits, cudaStream_t stream) {
+// A grid over all rows' splits together pays when rows times the longest row's splits would leave a fifth of
+// the CTAs without work; otherwise the grid is (splits, kv heads, rows).
+template <int D, bool TMA, bool COMPACT>
+static int launch_split(const CUtensorMap& map, const DecodeArgs& a, int R, int splits, int items, cudaStream_t stream) {
     constexpr int ROW = TMA ? D : D + 8;
     constexpr int SMEM = (DEC_WARPS * 2 * 2 * DEC_CHUNK * ROW + 16 * (D + 8)) * 2 + DEC_WARPS * 2 * 8;
     static_assert(2 * 2 * DEC_CHUNK * ROW * 2 >= (16 * D + 32) * 4, "a warp's staging area must hold its partial");
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_decode_split_kernel<D, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(attn_decode_split_kernel<D, TMA, COMPACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM) != cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
     const int G = a.nq / a.nkv;
-    dim3 grid(splits, a.nkv * ((G + 15) / 16), R);
-    auto kern = attn_decode_split_kernel<D, TMA>;
+    const dim3 grid = COMPACT ? dim3(items, a.nkv * ((G + 15) / 16)) : dim3(splits, a.nkv * ((G + 15) / 16), R);
+    auto kern = attn_decode_split_kernel<D, TMA, COMPACT>;
     SHARPI_LAUNCH_PDL(kern, grid, DEC_THREADS, SMEM, stream, map, a);
     return SHARPI_OK;
 }
 
+template <int D, bool TMA>
+static int launch_split(const CUtensorMap& map, const DecodeArgs& a, int R, int splits, int items, cudaStream_t stream) {
+    if ((long long)items * 5 < (long long)R * splits * 4) return launch_split<D, TMA, true>(map, a, R, splits, items, stream);
+    return launch_split<D, TMA, false>(map, a, R, splits, items, stream);
+}
+
 template <int D>
-static int launch_decode(const DecodeArgs& a, int R, int splits, long long pool_rows, cudaStream_t stream) {
+static int launch_decode(const DecodeArgs& a, int R, int splits, int items, long long pool_rows, cudaStream_t stream) {
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
     int rc;
     const bool tma = (D % 64 == 0) && a.page_shift >= 4 && a.status != nullptr && pool_rows > 0;
     if (tma) {
         if (!tmap::make_bf16_map(&map, a.kv, (uint64_t)D, (uint64_t)pool_rows, 0, 64, DEC_CHUNK)) return SHARPI_LAUNCH_FAILED;
-        rc = launch_split<D, (D % 64 == 0)>(map, a, R, splits, stream);
+        rc = launch_split<D, (D % 64 == 0)>(map, a, R, splits, items, stream);
     } else {
-        rc = launch_split<D, false>(map, a, R, splits, stream);
+        rc = launch_split<D, false>(map, a, R, splits, items, stream);
     }
     if (rc != SHARPI_OK) return rc;
     SHARPI_LAUNCH_PDL(attn_decode_merge_kernel<D>, dim3(R, a.nq), splits >= MERGE_WIDE_FROM ? MERGE_THREADS : MERGE_THREADS / 2, 0,
@@ -430,12 +479,13 @@ static int launch_decode(const DecodeArgs& a, int R, int splits, long long pool_
 }
 
 // `splits` is the largest number of 256-key splits any served row needs; part_o / part_ml are
-// scratch of [R, nq, splits, D] and [R, nq, splits, 2] floats.
+// scratch of [R, nq, splits, D] and [R, nq, splits, 2] floats.  `items` is an upper bound on the splits of all
+// served rows together (0: R * splits); CTAs past the true total leave at once.
 SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int* block_table, const int* row_req,
                                        const int* positions, const int* rows, float* part_o, float* part_ml,
                                        void* out, int* status, int num_pages, int R, int nq, int nkv, int d,
                                        int max_blocks, int page_size, int mask_kind, int mask_span, int splits,
-                                       float scale, cudaStream_t stream) {
+                                       int items, float scale, cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_blocks <= 0 || splits <= 0 || R > 65535 ||
         nq > 65535)
@@ -447,20 +497,23 @@ SHARPI_API int sharpi_attention_decode(const void* q, const void* kv, const int*
     a.positions = positions; a.rows = rows; a.part_o = part_o; a.part_ml = part_ml; a.out = (bf16*)out;
     a.nq = nq; a.nkv = nkv; a.max_blocks = max_blocks; a.page_size = page_size; a.mask_kind = mask_kind;
     a.mask_span = mask_span; a.max_splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
+    a.num_rows = R;
+    const long long all = (long long)R * splits;
+    if (items <= 0 || items > all) items = (int)(all < 2147483647LL ? all : 2147483647LL);
     a.page_shift = -1;
     for (int sft = 0; sft < 31; ++sft)
         if ((1 << sft) == page_size) a.page_shift = sft;
     a.status = status;
     const long long pool_rows = (long long)num_pages * 2 * nkv * page_size;
     switch (d) {
-        case 16: return launch_decode<16>(a, R, splits, pool_rows, stream);
-        case 32: return launch_decode<32>(a, R, splits, pool_rows, stream);
-        case 48: return launch_decode<48>(a, R, splits, pool_rows, stream);
-        case 64: return launch_decode<64>(a, R, splits, pool_rows, stream);
-        case 80: return launch_decode<80>(a, R, splits, pool_rows, stream);
-        case 96: return launch_decode<96>(a, R, splits, pool_rows, stream);
-        case 112: return launch_decode<112>(a, R, splits, pool_rows, stream);
-        case 128: return launch_decode<128>(a, R, splits, pool_rows, stream);
+        case 16: return launch_decode<16>(a, R, splits, items, pool_rows, stream);
+        case 32: return launch_decode<32>(a, R, splits, items, pool_rows, stream);
+        case 48: return launch_decode<48>(a, R, splits, items, pool_rows, stream);
+        case 64: return launch_decode<64>(a, R, splits, items, pool_rows, stream);
+        case 80: return launch_decode<80>(a, R, splits, items, pool_rows, stream);
+        case 96: return launch_decode<96>(a, R, splits, items, pool_rows, stream);
+        case 112: return launch_decode<112>(a, R, splits, items, pool_rows, stream);
+        case 128: return launch_decode<128>(a, R, splits, items, pool_rows, stream);
         default: return SHARPI_BAD_ARGUMENT;   // other head sizes use the generic kernel
     }
 }

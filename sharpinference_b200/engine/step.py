@@ -111,10 +111,11 @@ class StepRunner:
         return np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
 
     def build_context(self, entries: Sequence[StepEntry], width: Optional[int] = None,
-                      buffers: Optional[tuple] = None) -> StepContext:
+                      buffers: Optional[tuple] = None, decode_keys: Optional[int] = None) -> StepContext:
         """Lay out the step's metadata: one pinned host buffer, one copy to the device.  ``width``
         pads the block tables to a fixed number of columns; ``buffers`` = (pinned host tensor, device
-        tensor) of exactly the layout's size are reused instead of fresh ones (graph replay)."""
+        tensor) of exactly the layout's size are reused instead of fresh ones (graph replay), and
+        ``decode_keys`` then bounds the keys of the single rows for every step that reuses the layout."""
         cache = self.cache
         starts, lengths, slots = [], [], []
         for e in entries:
@@ -131,11 +132,13 @@ class StepRunner:
         want_rows: List[int] = []
         tiles: List[int] = []            # (first row, rows, first position, request) per attention tile
         decode_rows: List[int] = []
+        keys = 0                         # sum of position + 1 over the single rows
         r = 0
         for b, e in enumerate(entries):
             n = lengths[b]
             if n <= self.DECODE_ROWS_UP_TO:
                 decode_rows.extend(range(r, r + n))
+                keys += n * starts[b] + n * (n + 1) // 2
             else:
                 for t0 in range(0, n, self.attention_tile):
                     tiles.extend((r + t0, min(self.attention_tile, n - t0), starts[b] + t0, b))
@@ -205,6 +208,7 @@ class StepRunner:
             attn_tiles=view(7 + G, 4 * n_tiles).view(n_tiles, 4) if n_tiles else None, num_attn_tiles=n_tiles,
             attn_tile_rows=self.attention_tile,
             decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
+            decode_keys=keys if decode_keys is None else decode_keys,
         )
 
     # The word in which a tensor-core kernel records a wait that gave up is copied to pinned host memory
@@ -269,13 +273,18 @@ class StepRunner:
         step.  Returns (handled, logits); not handled means "run it eagerly this time"."""
         step = self.TABLE_WIDTH_STEP
         width = (self.table_width([e.request_id for e in entries]) + step - 1) // step * step
-        key = (len(entries), sum(len(e.want) for e in entries), width)
+        # the keys of all rows together, rounded up in steps of a sixteenth to an eighth of their number: the
+        # grid of the decode attention kernels is as large as this says, whatever the longest request is
+        keys = sum(self.cache.requests[e.request_id].length + 1 for e in entries)
+        kstep = 1 << max(8, keys.bit_length() - 4)
+        keys = (keys + kstep - 1) // kstep * kstep
+        key = (len(entries), sum(len(e.want) for e in entries), width, keys)
         rec = self._graphs.get(key)
         if rec is None:
             if key not in self._graph_seen:          # first sight: an eager run warms every kernel up
                 self._graph_seen.add(key)
                 return False, None
-            rec = self._capture(entries, width)
+            rec = self._capture(entries, width, keys)
             while len(self._graphs) >= self.max_graphs:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = rec
@@ -321,12 +330,12 @@ class StepRunner:
                     hv[o + len(t):o + width] = -1
         rec["dev"].copy_(rec["host"], non_blocking=True)
 
-    def _capture(self, entries: Sequence[StepEntry], width: int) -> dict:
+    def _capture(self, entries: Sequence[StepEntry], width: int, decode_keys: int) -> dict:
         B, R = len(entries), sum(len(e.want) for e in entries)
         size = int(self._layout(B, B, R, width, 0, B)[-1])
         host = torch.empty(size, dtype=torch.int32, pin_memory=True)
         dev = torch.empty(size, dtype=torch.int32, device=self.device)
-        ctx = self.build_context(entries, width=width, buffers=(host, dev))
+        ctx = self.build_context(entries, width=width, buffers=(host, dev), decode_keys=decode_keys)
         copied = torch.cuda.Event()
         copied.record()
         torch.cuda.synchronize(self.device)

@@ -35,7 +35,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_timestamp": ("elementwise", [P, I, P]),
     "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, P]),
     "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
-    "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
+    "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill_tc": ("attention_prefill_tc", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_gemm_nt": ("gemm_generic", [P, I, P, I, P, P, P, P, I, I, I, I, I, P]),

@@ -97,15 +97,18 @@ def attention_decode(ns) -> None:
     kv, table = _cache(B, S, nkv, d, ps)
     q = torch.randn(B, nq, d, device=DEV).to(torch.bfloat16)
     positions = torch.full((B,), S - 1, dtype=torch.int32, device=DEV)
+    if ns.others_context:                       # one row at the full context, the others shorter
+        positions[1:] = min(ns.others_context, S) - 1
     row_req = torch.arange(B, dtype=torch.int32, device=DEV)
     out = torch.empty(B, nq * d, dtype=torch.bfloat16, device=DEV)
     kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
+    keys = int((positions.long() + 1).sum())
     fn = lambda: ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=B, nq=nq, nkv=nkv, d=d,
                                       page_size=ps, mask_kind=kind, mask_span=ns.span, scale=1 / math.sqrt(d),
-                                      max_context=S)
+                                      max_context=S, max_keys=keys)
     ms = _time(fn, ns.iters)
-    nbytes = B * S * nkv * d * 2 * 2
-    print(f"attention_decode batch={B} context={S} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
+    nbytes = keys * nkv * d * 2 * 2
+    print(f"attention_decode batch={B} context={S}{'/' + str(ns.others_context) if ns.others_context else ''} heads={nq}/{nkv} d={d}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
 
 
 def attention_prefill(ns) -> None:
@@ -145,6 +148,8 @@ def main(argv=None) -> int:
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
         p.add_argument("--context", type=int, default=8192)
+        p.add_argument("--others-context", type=int, default=0,
+                       help="attention_decode: rows after the first have this many keys (a batch of unequal lengths)")
         p.add_argument("--tokens", type=int, default=2048)
         p.add_argument("--start", type=int, default=0)
         p.add_argument("--heads", type=int, default=40)

@@ -203,9 +203,11 @@ def decode_splits(max_context: int, mask_kind: int, mask_span: int) -> int:
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, row_req: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, *, rows: Optional[torch.Tensor], num_rows: int,
                      nq: int, nkv: int, d: int, page_size: int, mask_kind: int, mask_span: int, scale: float,
-                     max_context: int) -> None:
+                     max_context: int, max_keys: Optional[int] = None) -> None:
     """Split-KV paged attention for rows that bring one query each (bfloat16).  ``rows`` (int32) names
-    the rows to serve, or None for rows ``0 .. num_rows - 1``; results go to ``out[row]``."""
+    the rows to serve, or None for rows ``0 .. num_rows - 1``; results go to ``out[row]``.  ``max_context`` bounds
+    the longest row (position + 1), ``max_keys`` the sum of position + 1 over the served rows: with it the launch
+    holds about as many CTAs as the rows have splits together, not rows times the longest row's splits."""
     _need(q, "q", torch.bfloat16)
     _need(kv_layer, "kv_layer", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
@@ -214,13 +216,15 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
         raise KernelError(f"head size {d} is not served by the tensor-core attention kernels "
                           f"({FAST_ATTENTION_HEAD_SIZES}); use the generic kernel")
     splits = decode_splits(max_context, mask_kind, mask_span)
+    # a row at position p has at most p // 256 + 1 splits, so the rows together at most max_keys // 256 + rows
+    items = num_rows * splits if max_keys is None else min(num_rows * splits, max_keys // DECODE_SPLIT + num_rows)
     part_o = torch.empty((num_rows, nq, splits, d), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((num_rows, nq, splits, 2), dtype=torch.float32, device=q.device)
     check(kernel("sharpi_attention_decode")(q.data_ptr(), kv_layer.data_ptr(), block_table.data_ptr(),
                                             row_req.data_ptr(), positions.data_ptr(), _ptr(rows), part_o.data_ptr(),
                                             part_ml.data_ptr(), out.data_ptr(), status_word(q.device).data_ptr(),
                                             kv_layer.shape[0], num_rows, nq, nkv, d,
-                                            block_table.shape[-1], page_size, mask_kind, mask_span, splits,
+                                            block_table.shape[-1], page_size, mask_kind, mask_span, splits, items,
                                             float(scale), _stream()), "sharpi_attention_decode")
 
 

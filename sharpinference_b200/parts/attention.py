@@ -90,7 +90,7 @@ class PagedAttention(Mixer):
                 ops.attention_decode(q, slot.kv, table, ctx.row_request, ctx.positions, o, rows=ctx.decode_rows,
                                      num_rows=ctx.num_decode_rows, nq=nq, nkv=nkv, d=d, page_size=slot.page_size,
                                      mask_kind=mask_kind, mask_span=mask_span, scale=self.softmax_scale,
-                                     max_context=ctx.max_context)
+                                     max_context=ctx.max_context, max_keys=ctx.decode_keys)
         else:
             o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
                                             page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,

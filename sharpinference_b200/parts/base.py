@@ -115,6 +115,7 @@ class StepContext:
     attn_tile_rows: int = 64                # rows per tile: 128 when every attention layer takes the tcgen05 kernel
     decode_rows: Optional[torch.Tensor] = None
     num_decode_rows: int = 0
+    decode_keys: Optional[int] = None       # an upper bound on the sum of position + 1 over the single rows
     extras: Dict[str, Any] = field(default_factory=dict)
 
 

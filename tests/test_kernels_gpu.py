@@ -633,6 +633,12 @@ def test_attention_decode_many_splits_and_batch_invariance(ops):
     ops.attention_decode(q, kv, table, row_req, positions, alone, rows=short, num_rows=2, nq=nq, nkv=nkv, d=d,
                          page_size=ps, mask_kind=0, mask_span=1, scale=scale, max_context=600)
     assert torch.equal(alone[short.long()], out[short.long()])
+    # told how many keys the rows have together, the launch holds 793 CTAs a kv head instead of 5 x 274: the same bits
+    tight = torch.zeros_like(out)
+    ops.attention_decode(q, kv, table, row_req, positions, tight, rows=None, num_rows=len(rows), nq=nq, nkv=nkv, d=d,
+                         page_size=ps, mask_kind=0, mask_span=1, scale=scale, max_context=70000,
+                         max_keys=int((positions.long() + 1).sum()))
+    assert torch.equal(tight, out)
     near = torch.tensor([3], dtype=torch.int32, device=DEV)              # 255 splits, launched with narrow blocks
     alone3 = torch.zeros_like(out)
     ops.attention_decode(q, kv, table, row_req, positions, alone3, rows=near, num_rows=1, nq=nq, nkv=nkv, d=d,
