@@ -334,6 +334,33 @@ def test_decode_steps_replayed_as_cuda_graphs_give_the_same_logits(model_dirs, d
     assert err < (TOL["float32"] if dtype == "float32" else 0.1), (err, where)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_decode_steps_with_one_long_request_among_short_ones(model_dirs, dtype):
+    """Four requests decode together, one with 880 keys and three with a few: the decode attention launch then
+    counts all rows' splits together (in bfloat16), inside a replayed graph too; same numbers as eager steps."""
+    from sharpinference_b200 import Engine, EngineOptions
+    name = "D"                                   # head size 64: the split-KV kernels serve it in bfloat16
+    cfg, w = plain.load_folder(model_dirs[name])
+    reqs = {f"m{i}": traces.random_tokens(cfg["vocab_size"], n, seed=70 + i) for i, n in enumerate([900, 40, 30, 25])}
+    heads = {"m0": 880, "m1": 20, "m2": 10, "m3": 5}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:heads[r]], "want": []} for r, t in reqs.items()], "end": []}]
+    for s in range(1, 21):
+        steps.append({"step": s, "entries": [{"id": r, "tokens": [reqs[r][heads[r] + s - 1]], "want": [0]} for r in reqs],
+                      "end": list(reqs) if s == 20 else []})
+    outs = {}
+    for graphs in (False, True):
+        eng = Engine(model_dirs[name], dtype=dtype, device="cuda:0",
+                     options=EngineOptions(page_size=16, max_cache_tokens=traces.max_tokens(steps), max_batch=4,
+                                           cuda_graphs=graphs))
+        outs[graphs] = traces.replay(eng, steps)
+        assert (eng.runner.graph_replays >= 15) == graphs
+    for key, row in outs[False].items():
+        assert torch.equal(row, outs[True][key]), key
+    ref = {rid: plain.forward(cfg, w, toks[:heads[rid] + 20]) for rid, toks in reqs.items()}
+    err, where = traces.worst_error(outs[True], ref)
+    assert err < (TOL["float32"] if dtype == "float32" else 0.1), (err, where)
+
+
 def test_sampling_options_through_the_entry_point(model_dirs):
     """top-k / top-p / min-p / penalties / logit bias / stop tokens as request parameters."""
     from sharpinference_b200 import Engine, EngineOptions, SamplingParams
