@@ -1,0 +1,45 @@
+"""Host-side bounds that size kernel launches: they must never be below what the kernels will need (no GPU)."""
+import random
+
+from sharpinference_b200.kernels import ops
+
+
+def visible_lo(pos: int, kind: int, span: int) -> int:
+    """First visible key of a row at ``pos``: the mask rule of csrc/common.cuh, restated."""
+    if kind == ops.MASK_CHUNK:
+        return pos // span * span
+    if kind == ops.MASK_WINDOW:
+        return max(0, pos - span + 1)
+    return 0
+
+
+def splits_of(pos: int, kind: int, span: int) -> int:
+    """The 256-key splits (at absolute multiples of 256) that hold a visible key of the row."""
+    return pos // ops.DECODE_SPLIT - visible_lo(pos, kind, span) // ops.DECODE_SPLIT + 1
+
+
+def test_decode_split_bounds_hold_for_drawn_rows():
+    r = random.Random(0)
+    for _ in range(2000):
+        kind = r.choice([ops.MASK_FULL, ops.MASK_CHUNK, ops.MASK_WINDOW])
+        span = r.choice([1, 16, 100, 256, 257, 300, 512, 8192, 70000])
+        rows = r.randint(1, 70)
+        top = r.choice([1, 5, 255, 256, 257, 1000, 8192, 8193, 140000])
+        positions = [r.randrange(top) for _ in range(rows)]
+        max_context = max(positions) + 1
+        per_row = ops.decode_splits(max_context, kind, span)
+        need = [splits_of(p, kind, span) for p in positions]
+        assert max(need) <= per_row, (kind, span, positions)
+        # what attention_decode launches when it is told the rows' keys: never fewer CTAs than there are splits
+        keys = sum(p + 1 for p in positions)
+        items = min(rows * per_row, keys // ops.DECODE_SPLIT + rows)
+        assert sum(need) <= items, (kind, span, positions)
+
+
+def test_decode_split_bound_is_tight_for_whole_chunks():
+    assert ops.decode_splits(8192, ops.MASK_FULL, 1) == 32
+    assert ops.decode_splits(8193, ops.MASK_FULL, 1) == 33
+    assert ops.decode_splits(1, ops.MASK_FULL, 1) == 1
+    # a chunk of 8192 keys that starts on a split boundary never spans more than 33 splits, however long the row
+    assert ops.decode_splits(10 ** 6, ops.MASK_CHUNK, 8192) == 33
+    assert ops.decode_splits(100, ops.MASK_WINDOW, 700) == 1
