@@ -265,6 +265,12 @@ class StepRunner:
     # -- CUDA graphs for decode-only steps -------------------------------------------------------
     TABLE_WIDTH_STEP = 16      # block-table columns are rounded up to a multiple of this in a graph
 
+    @staticmethod
+    def keys_bucket(keys: int) -> int:
+        """``keys`` rounded up to a multiple of a power of two that is a sixteenth to an eighth of it (256 at least)."""
+        step = 1 << max(8, keys.bit_length() - 4)
+        return (keys + step - 1) // step * step
+
     def table_width(self, request_ids) -> int:
         return max([1] + [len(self.cache.requests[r].tables[g.index]) for r in request_ids for g in self.cache.groups])
 
@@ -275,9 +281,7 @@ class StepRunner:
         width = (self.table_width([e.request_id for e in entries]) + step - 1) // step * step
         # the keys of all rows together, rounded up in steps of a sixteenth to an eighth of their number: the
         # grid of the decode attention kernels is as large as this says, whatever the longest request is
-        keys = sum(self.cache.requests[e.request_id].length + 1 for e in entries)
-        kstep = 1 << max(8, keys.bit_length() - 4)
-        keys = (keys + kstep - 1) // kstep * kstep
+        keys = self.keys_bucket(sum(self.cache.requests[e.request_id].length + 1 for e in entries))
         key = (len(entries), sum(len(e.want) for e in entries), width, keys)
         rec = self._graphs.get(key)
         if rec is None:

@@ -43,3 +43,15 @@ def test_decode_split_bound_is_tight_for_whole_chunks():
     # a chunk of 8192 keys that starts on a split boundary never spans more than 33 splits, however long the row
     assert ops.decode_splits(10 ** 6, ops.MASK_CHUNK, 8192) == 33
     assert ops.decode_splits(100, ops.MASK_WINDOW, 700) == 1
+
+
+def test_keys_bucket_of_a_captured_decode_step():
+    """A replayed graph's attention launch is sized by the bucket: never below the keys, at most an eighth above."""
+    from sharpinference_b200.engine.step import StepRunner
+    for keys in list(range(1, 3000)) + [65080, 65536, 65537, 10 ** 6, 2 ** 31 - 5]:
+        b = StepRunner.keys_bucket(keys)
+        assert b >= keys
+        assert b - keys < max(256, keys // 8 + 1), keys
+        assert StepRunner.keys_bucket(b) == b                       # a bucket is its own bucket
+    # a batch that grows by a token per request stays in one bucket for many steps
+    assert len({StepRunner.keys_bucket(8 * (8192 - 57 + i)) for i in range(58)}) == 1
