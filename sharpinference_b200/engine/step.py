@@ -266,9 +266,11 @@ class StepRunner:
     TABLE_WIDTH_STEP = 16      # block-table columns are rounded up to a multiple of this in a graph
 
     @staticmethod
-    def keys_bucket(keys: int) -> int:
-        """``keys`` rounded up to a multiple of a power of two that is a sixteenth to an eighth of it (256 at least)."""
-        step = 1 << max(8, keys.bit_length() - 4)
+    def keys_bucket(keys: int, rows: int = 1) -> int:
+        """``keys`` rounded up to a multiple of a power of two: a sixteenth to an eighth of ``keys``, and at
+        least 256 keys a row, so that a batch that gains a key a row each step stays in its bucket for 256
+        steps or more (a new bucket means a step run eagerly and a graph captured)."""
+        step = 1 << max((256 * max(rows, 1) - 1).bit_length(), keys.bit_length() - 4)
         return (keys + step - 1) // step * step
 
     def table_width(self, request_ids) -> int:
@@ -279,9 +281,9 @@ class StepRunner:
         step.  Returns (handled, logits); not handled means "run it eagerly this time"."""
         step = self.TABLE_WIDTH_STEP
         width = (self.table_width([e.request_id for e in entries]) + step - 1) // step * step
-        # the keys of all rows together, rounded up in steps of a sixteenth to an eighth of their number: the
-        # grid of the decode attention kernels is as large as this says, whatever the longest request is
-        keys = self.keys_bucket(sum(self.cache.requests[e.request_id].length + 1 for e in entries))
+        # the keys of all rows together, rounded up (see keys_bucket): the grid of the decode attention kernels
+        # is as large as this says, whatever the longest request is
+        keys = self.keys_bucket(sum(self.cache.requests[e.request_id].length + 1 for e in entries), len(entries))
         key = (len(entries), sum(len(e.want) for e in entries), width, keys)
         rec = self._graphs.get(key)
         if rec is None:

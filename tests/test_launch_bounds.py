@@ -46,12 +46,17 @@ def test_decode_split_bound_is_tight_for_whole_chunks():
 
 
 def test_keys_bucket_of_a_captured_decode_step():
-    """A replayed graph's attention launch is sized by the bucket: never below the keys, at most an eighth above."""
+    """A replayed graph's attention launch is sized by the bucket: never below the keys, at most an eighth (or
+    256 keys a row) above; a batch that gains a key a row each step changes bucket every 256 steps at most."""
     from sharpinference_b200.engine.step import StepRunner
-    for keys in list(range(1, 3000)) + [65080, 65536, 65537, 10 ** 6, 2 ** 31 - 5]:
-        b = StepRunner.keys_bucket(keys)
-        assert b >= keys
-        assert b - keys < max(256, keys // 8 + 1), keys
-        assert StepRunner.keys_bucket(b) == b                       # a bucket is its own bucket
-    # a batch that grows by a token per request stays in one bucket for many steps
-    assert len({StepRunner.keys_bucket(8 * (8192 - 57 + i)) for i in range(58)}) == 1
+    for rows in (1, 3, 8, 64):
+        for keys in list(range(rows, 3000, 7)) + [65080, 65536, 65537, 10 ** 6, 2 ** 31 - 5]:
+            b = StepRunner.keys_bucket(keys, rows)
+            assert b >= keys
+            assert b - keys < max(512 * rows, keys // 8 + 1), (keys, rows)
+            assert StepRunner.keys_bucket(b, rows) == b                       # a bucket is its own bucket
+        start = 5 * rows
+        buckets = [StepRunner.keys_bucket(start + rows * step, rows) for step in range(4096)]
+        changes = sum(a != b for a, b in zip(buckets, buckets[1:]))
+        assert changes <= 4096 // 256 + 1, (rows, changes)
+    assert len({StepRunner.keys_bucket(8 * (8192 - 57 + i), 8) for i in range(58)}) == 1
