@@ -87,6 +87,18 @@ class ConfigReader:
     def bool(self, key: str, default: Any = _MISSING) -> bool:
         return self._get(key, "boolean", self._as_bool, default)
 
+    @staticmethod
+    def _as_switch(value: Any) -> bool:
+        if isinstance(value, bool):
+            return value
+        if isinstance(value, int) and value >= 0:
+            return value != 0
+        raise TypeError(f"{type(value).__name__}")
+
+    def switch(self, key: str, default: Any = _MISSING) -> bool:
+        """A boolean that some files write as a non-negative integer (non-zero = on)."""
+        return self._get(key, "boolean or non-negative integer", self._as_switch, default)
+
     def str(self, key: str, default: Any = _MISSING) -> str:
         return self._get(key, "string", self._as_str, default)
 

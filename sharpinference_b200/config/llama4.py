@@ -91,11 +91,14 @@ class Llama4TextConfig:
         no_rope = r.int_list("no_rope_layers", None)
         chunk = r.int("attention_chunk_size")
         qk_norm = r.bool("use_qk_norm", True)
-        qk_eps = r.float("qk_norm_eps", 1e-6)
-        temp_tuning = r.bool("attn_temperature_tuning", True)
+        eps = r.float("rms_norm_eps", 1e-5)
+        # The weightless q/k norm takes the model's RMSNorm eps (src/SharpInference.Engine/ForwardPass.cs:1642-1648
+        # passes _hp.RmsNormEps); checkpoints carry no key of its own.  An explicit `qk_norm_eps` overrides it.
+        qk_eps = r.float("qk_norm_eps", eps)
+        temp_tuning = r.switch("attn_temperature_tuning", True)
         floor_scale = r.float("floor_scale", 8192.0)
         attn_scale = r.float("attn_scale", 0.1)
-        eps = r.float("rms_norm_eps", 1e-5)
+        nope_interval = r.int("no_rope_layer_interval", 4)
         tied = r.bool("tie_word_embeddings", bool(top.get("tie_word_embeddings", False)))
         max_pos = r.int("max_position_embeddings", 1 << 20)
         act = r.str("hidden_act", "silu")
@@ -144,7 +147,9 @@ class Llama4TextConfig:
             moe = tuple(sorted(set(moe_layers)))
             r.require(all(0 <= i < layers for i in moe), f"moe_layers {moe_layers} holds an index outside [0, {layers})")
 
-        nope = _parse_no_rope_layers(no_rope, layers, r)
+        r.require(nope_interval is not None and nope_interval >= 1,
+                  f"no_rope_layer_interval must be >= 1, found {nope_interval}")
+        nope = _parse_no_rope_layers(no_rope, layers, r, nope_interval or 4)
 
         # ---- validation --------------------------------------------------------------
         for name, value in (("vocab_size", vocab), ("hidden_size", hidden), ("num_hidden_layers", layers),
@@ -163,7 +168,8 @@ class Llama4TextConfig:
         r.require(per_tok == 1, f"num_experts_per_tok must be 1 (top-1 sigmoid router), found {per_tok}")
         r.require(act == "silu", f"hidden_act must be 'silu', found '{act}'")
         r.require(not attn_bias, "attention_bias=true is not supported: Llama 4 projections carry no bias")
-        r.require(eps > 0 and qk_eps > 0, "rms_norm_eps and qk_norm_eps must be positive")
+        r.require(eps is not None and qk_eps is not None and eps > 0 and qk_eps > 0,
+                  "rms_norm_eps and qk_norm_eps must be positive")
         r.require(theta > 0, f"rope_theta must be positive, found {theta}")
         if temp_tuning:
             r.require(floor_scale > 0, f"floor_scale must be positive, found {floor_scale}")
@@ -211,7 +217,8 @@ class Llama4TextConfig:
             "use_qk_norm": self.use_qk_norm,
             "qk_norm_eps": self.qk_norm_eps,
             "attn_temperature_tuning": self.attn_temperature_tuning,
-            "floor_scale": self.floor_scale,
+            # whole numbers are written as integers, which is the form checkpoints carry
+            "floor_scale": int(self.floor_scale) if float(self.floor_scale).is_integer() else self.floor_scale,
             "attn_scale": self.attn_scale,
             "rms_norm_eps": self.rms_norm_eps,
             "tie_word_embeddings": self.tie_word_embeddings,
@@ -226,7 +233,7 @@ class Llama4TextConfig:
         return out
 
 
-def _parse_no_rope_layers(value: Optional[list], layers: int, r: ConfigReader) -> Tuple[int, ...]:
+def _parse_no_rope_layers(value: Optional[list], layers: int, r: ConfigReader, interval: int = 4) -> Tuple[int, ...]:
     """``no_rope_layers`` is written in two ways; both mean "which layers skip RoPE".
 
     * per-layer flags: a list of length ``num_hidden_layers`` of 0/1, where **1 means the
@@ -235,13 +242,14 @@ def _parse_no_rope_layers(value: Optional[list], layers: int, r: ConfigReader) -
 
     A list is read as flags exactly when its length equals ``num_hidden_layers`` and every
     entry is 0 or 1; otherwise as indices.  Absent or empty: the architecture's rule, every
-    4th layer (``(i + 1) % 4 == 0``) is without RoPE, which is what the reference fixes in
-    code (src/SharpInference.Core/ModelGraph.cs:292-295).
+    ``interval``-th layer (``(i + 1) % interval == 0``; ``no_rope_layer_interval``, 4 when the
+    file does not say) is without RoPE; the reference fixes 4 in code
+    (src/SharpInference.Core/ModelGraph.cs:292-295).
     """
     if not layers or layers <= 0:
         return ()
     if value is None or len(value) == 0:
-        return tuple(i for i in range(layers) if (i + 1) % 4 == 0)
+        return tuple(i for i in range(layers) if (i + 1) % max(interval, 1) == 0)
     if len(value) == layers and all(v in (0, 1) for v in value):
         return tuple(i for i, v in enumerate(value) if v == 0)
     idx = tuple(sorted(set(value)))

@@ -34,21 +34,16 @@ enum SharpiDtype : int {
 // before it in the stream is still running, so that its launch and set-up overlap that kernel's tail; it
 // must call pdl_wait() before it reads or writes anything that an earlier kernel touches (every such kernel
 // calls it on every path, before any return, so completion of a kernel implies completion of those before
-// it).  Launched the plain way, pdl_wait() does nothing.  SHARPI_PDL=0 in the environment turns the
-// attribute off.
+// it).  Launched the plain way, pdl_wait() does nothing.  sharpi_set_programmatic_launch(0) turns the
+// attribute off for the launches of this library (every kernel library exports its own switch).
 __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-static inline int sharpi_pdl_enabled() {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* v = getenv("SHARPI_PDL");
-        enabled = (v && v[0] == '0') ? 0 : 1;
-    }
-    return enabled;
-}
+static int sharpi_pdl_flag = 1;
+static inline int sharpi_pdl_enabled() { return sharpi_pdl_flag; }
+SHARPI_API void sharpi_set_programmatic_launch(int on) { sharpi_pdl_flag = on ? 1 : 0; }
 
 #define SHARPI_LAUNCH_PDL(kernel, grid, block, smem, stream, ...)                                  \
     do {                                                                                           \

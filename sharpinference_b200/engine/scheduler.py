@@ -16,7 +16,19 @@ recomputed from its prompt and the tokens it had generated (its sampler stream a
 continue where they were).  This repeats until the rest fits.  A request that does not fit even
 when it is the only one running can never finish: it ends with ``finish_reason="cache_full"``
 and the others go on.  Prompt portions only take pages that decodes left over; a portion shrinks
-to what fits, and a waiting request is admitted only when at least one of its tokens fits.
+to what fits, and a waiting request is admitted only when at least one of its tokens fits.  A
+plan that preempted admits nobody: the request it sent back would otherwise return at once and
+be sent back again.
+
+**More decodes than the token budget.**  The requests that ran least recently go first (ties:
+the one that has generated least, then the older one), so every running request gets its turn
+equally often; pages are taken only for the decodes that are planned.
+
+**Failures.**  ``fail`` ends one request with ``finish_reason="error"`` and the message;
+``fail_all`` ends every running and waiting request that way.  The reference's batching loop
+does the same: a request that cannot be prepared fails alone (ContinuousBatchingEngine.cs:529-535),
+a failed pass fails the requests in it (:662-672), a loop that dies completes everything in
+flight with the error and disposes the caches (:465-501).
 """
 from __future__ import annotations
 
@@ -46,6 +58,8 @@ class Request:
     admitted_order: int = -1
     preemptions: int = 0
     sampler: Optional[SamplerState] = None
+    last_step: int = -1                 # number of the last step that ran tokens of this request
+    error: Optional[str] = None         # why, when finish_reason is "error"
 
     @property
     def tokens(self) -> List[int]:
@@ -158,17 +172,50 @@ class Scheduler:
         if req.status == RUNNING:
             self.cache.free_request(req.request_id)
             self.running.remove(req)
+        elif req.status == WAITING and req in self.waiting:
+            self.waiting.remove(req)
         req.status, req.finish_reason = FINISHED, reason
         self.num_finished += 1
+
+    def fail(self, req: Request, error: str) -> None:
+        """End one request with ``finish_reason="error"``; its pages and state slot are given back."""
+        if req.status == FINISHED:
+            return
+        req.error = error
+        self._finish(req, "error")
+
+    def fail_all(self, error: str) -> List[Request]:
+        """End every running and every waiting request with the error.  Returns them."""
+        failed = list(self.running) + list(self.waiting)
+        for req in failed:
+            self.fail(req, error)
+        return failed
+
+    def preempt_newest(self, plan: Optional[StepPlan] = None) -> Optional[Request]:
+        """The out-of-pages rule, applied from outside a plan (the step function found fewer pages than the
+        plan counted on): the newest running request goes back to the queue; alone, it ends ``cache_full``."""
+        if not self.running:
+            return None
+        victim = self.running[-1]
+        plan = plan if plan is not None else StepPlan()
+        if len(self.running) == 1:
+            self._finish(victim, "cache_full")
+            plan.failed.append(victim)
+        else:
+            self._preempt(victim, plan)
+        return victim
 
     def plan(self) -> StepPlan:
         plan = StepPlan()
         budget = self.max_tokens_per_step
 
-        # 1. decodes: every running request whose prompt is done brings its one pending token.
+        # 1. decodes: every running request whose prompt is done brings its one pending token; if there are
+        # more of them than the budget, those that ran least recently.
         while True:
             left = dict(self.cache.free_pages())
             decodes = [r for r in self.running if r.pending == 1 and r.computed >= len(r.prompt)]
+            if len(decodes) > budget:
+                decodes = sorted(decodes, key=lambda r: (r.last_step, len(r.generated), r.admitted_order))[:budget]
             ok = True
             for req in decodes:
                 if self._fits(req, 1, left):
@@ -184,7 +231,7 @@ class Scheduler:
                 plan.failed.append(victim)
             else:
                 self._preempt(victim, plan)
-        for req in decodes[:budget]:
+        for req in decodes:
             plan.entries.append(PlannedEntry(req, req.computed, 1, True))
         budget -= len(plan.entries)
         planned = {e.request.request_id for e in plan.entries}
@@ -203,9 +250,10 @@ class Scheduler:
             planned.add(req.request_id)
             budget -= n
 
-        # 3. admission, first come first served; a request enters only if a token of it fits.
+        # 3. admission, first come first served; a request enters only if a token of it fits, and nobody
+        # enters a plan that had to send a request back.
         while self.waiting and budget > 0 and len(self.running) < self.max_batch \
-                and self.cache.state_slots.free_count > 0:
+                and self.cache.state_slots.free_count > 0 and not plan.preempted:
             req = self.waiting[0]
             self.cache.add_request(req.request_id)
             n = self._largest_fit(req, min(req.pending, budget), left)
@@ -248,6 +296,7 @@ class Scheduler:
         for e in plan.entries:
             req = e.request
             req.computed += e.count
+            req.last_step = self.num_steps
             if not e.want_last:
                 continue
             token = int(next(it))

@@ -27,7 +27,12 @@ from ..parts.base import StepContext
 
 
 class StepError(ValueError):
-    """A step that cannot run as given (unknown request, bad token id, bad wanted place)."""
+    """A step that cannot run as given (unknown request, bad token id, bad wanted place).  ``request_id``
+    names the entry at fault when there is one; nothing was reserved or launched."""
+
+    def __init__(self, message: str, request_id: Hashable = None):
+        super().__init__(message)
+        self.request_id = request_id
 
 
 @dataclass
@@ -89,19 +94,21 @@ class StepRunner:
         seen = set()
         for e in entries:
             if e.request_id in seen:
-                raise StepError(f"request {e.request_id!r} appears twice in one step")
+                raise StepError(f"request {e.request_id!r} appears twice in one step", e.request_id)
             seen.add(e.request_id)
             if e.request_id not in self.cache.requests:
-                raise StepError(f"request {e.request_id!r} is not live")
+                raise StepError(f"request {e.request_id!r} is not live", e.request_id)
             n = len(e.tokens)
             if n == 0:
-                raise StepError(f"request {e.request_id!r}: an entry must bring at least one token")
+                raise StepError(f"request {e.request_id!r}: an entry must bring at least one token", e.request_id)
             for w in e.want:
                 if not (0 <= w < n):
-                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} token(s)")
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} token(s)",
+                                    e.request_id)
             for t in e.tokens:
                 if not (0 <= t < V):
-                    raise StepError(f"token id {t} is outside the vocabulary [0, {V})")
+                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary [0, {V})",
+                                    e.request_id)
 
     def _layout(self, T: int, B: int, R: int, width: int, n_tiles: int, n_dec: int) -> np.ndarray:
         """Offsets (in int32 words, each segment starting on 16 bytes) of the staging buffer's segments:
@@ -275,6 +282,24 @@ class StepRunner:
 
     def table_width(self, request_ids) -> int:
         return max([1] + [len(self.cache.requests[r].tables[g.index]) for r in request_ids for g in self.cache.groups])
+
+    def drop_graphs(self) -> None:
+        """Forget every captured decode graph (after a failed step: a capture may have been cut short, and
+        the static buffers of the others describe requests that are gone)."""
+        self._graphs.clear()
+        self._graph_seen.clear()
+
+    def reset_after_failure(self) -> None:
+        """After a step that raised: no graph is trusted any more, and the kernels' status word and the
+        counters they may have left behind start from zero again."""
+        self.drop_graphs()
+        self._status_pending = False
+        if self.device.type == "cuda":
+            try:
+                torch.cuda.synchronize(self.device)
+                ops.check_status(self.device)
+            except Exception:                            # noqa: BLE001 - the failure is reported already
+                pass
 
     def _run_decode_graph(self, entries: Sequence[StepEntry]):
         """Replay (capturing first, if this shape was seen once before) the graph of a decode-only

@@ -70,7 +70,28 @@ def load_library(name: str) -> ctypes.CDLL:
             raise KernelError(f"cannot load the compiled kernel library {path}: {exc}") from None
         _libs[name] = lib
         loaded_libraries[name] = path
+        _apply_programmatic_launch(lib)
     return lib
+
+
+_programmatic_launch = True
+
+
+def _apply_programmatic_launch(lib: ctypes.CDLL) -> None:
+    fn = getattr(lib, "sharpi_set_programmatic_launch", None)
+    if fn is not None:
+        fn.argtypes, fn.restype = [c_int], None
+        fn(1 if _programmatic_launch else 0)
+
+
+def set_programmatic_launch(on: bool) -> None:
+    """Whether kernels are launched with programmatic stream serialization (a kernel's set-up may overlap the
+    tail of the kernel before it).  One switch for the process: it reaches every kernel library that is
+    loaded and every one loaded later."""
+    global _programmatic_launch
+    _programmatic_launch = bool(on)
+    for lib in _libs.values():
+        _apply_programmatic_launch(lib)
 
 
 def register(symbol: str, library: str, argtypes: list) -> None:

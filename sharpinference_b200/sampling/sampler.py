@@ -1,7 +1,8 @@
 """The sampler: one next token for every row of logits, on the device.
 
-Greedy rows take the arg-max with the lowest index among ties; other rows go through logit bias,
-window penalties, temperature, softmax, top-k, min-p, top-p and an inverse-CDF draw
+Greedy rows (temperature <= 0) take the arg-max of the raw logits, the lowest index among ties, before
+any bias or penalty, as the reference does (src/SharpInference.Engine/Sampler.cs:17-18); other rows go
+through logit bias, window penalties, temperature, softmax, top-k, min-p, top-p and an inverse-CDF draw
 (``csrc/sampling.cu``, following src/SharpInference.Engine/Sampler.cs:15-107).  Each request owns
 a counter-based random stream: draw ``n`` of a request with seed ``s`` is
 ``uniform(splitmix64(s, n))``, so its tokens do not depend on what else is in the batch.
@@ -73,6 +74,8 @@ class Sampler:
         pen_rows, pen_tok, pen_cnt = [], [], []
         for r, st in enumerate(states):
             p = st.params
+            if p.greedy:                    # the arg-max of the raw logits: no bias, no penalty
+                continue
             if p.logit_bias:
                 for tok, b in p.logit_bias.items():
                     bias_rows.append(r); bias_tok.append(int(tok)); bias_val.append(float(b))

@@ -180,7 +180,8 @@ def attention_layer(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tens
     if rope:
         q, k = apply_rope(q, positions, freqs), apply_rope(k, positions, freqs)
         if cfg.get("use_qk_norm", True):
-            eps = cfg.get("qk_norm_eps", 1e-6)
+            # the model's RMSNorm eps unless the file names one (src/SharpInference.Engine/ForwardPass.cs:1642-1648)
+            eps = cfg.get("qk_norm_eps", cfg.get("rms_norm_eps", 1e-5))
             q, k = l2_norm(q, eps), l2_norm(k, eps)
         ok = visible("chunk", cfg["attention_chunk_size"], S)
     else:

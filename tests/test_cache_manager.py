@@ -183,3 +183,30 @@ def test_random_orders_keep_the_invariants(seed):
     for rid in list(live):
         m.free_request(rid)
     assert m.free_pages() == {0: 10, 1: 10} and m.state_slots.free_count == 4
+
+
+def test_pages_per_group_follow_what_each_group_can_hold():
+    """Sizing from a memory budget: a group that forgets the past gets what max_batch requests can hold of it
+    (span + a step + a page each), the rest goes to the groups that keep everything."""
+    from fakes import fake_blocks
+    from sharpinference_b200.cache import group_layout, pages_per_group
+    from sharpinference_b200.models.model import ScheduleEntry
+    from sharpinference_b200.parts.base import CacheSpec
+    chunk, full = CacheSpec("chunk", 8192, 8, 128), CacheSpec("full", 0, 8, 128)
+    blocks = fake_blocks([chunk, chunk, chunk, full] * 2)
+    groups = group_layout([ScheduleEntry(i) for i in range(8)], blocks)
+    assert groups == [(chunk, 6), (full, 2)]
+    per_token = 2 * 8 * 128 * 2
+    pages = pages_per_group(groups, budget_bytes=12 << 30, itemsize=2, page_size=64, max_batch=8, max_tokens_per_step=2048)
+    # the chunked group: 8 requests x (8192 + 2048 + 64) positions
+    assert pages[0] == 8 * (8192 + 2048 + 64) // 64
+    spent = pages[0] * 64 * per_token * 6
+    assert pages[1] == (((12 << 30) - spent) // (per_token * 2)) // 64
+    assert pages[1] * 64 > 4 * pages[0] * 64                     # far more history than one size for all would give
+    # a budget too small for the bound: the forgetting group takes half, never nothing
+    small = pages_per_group(groups, budget_bytes=1 << 30, itemsize=2, page_size=64, max_batch=8, max_tokens_per_step=2048)
+    assert small[0] * 64 * per_token * 6 <= (1 << 29) and small[0] >= 1 and small[1] >= 1
+    # only forgetting groups: their bound, whatever the budget allows beyond it
+    alone = pages_per_group([(chunk, 4)], budget_bytes=100 << 30, itemsize=2, page_size=64, max_batch=2, max_tokens_per_step=128)
+    assert alone == [2 * (8192 + 128 + 64) // 64]
+    assert pages_per_group([], budget_bytes=1, itemsize=2, page_size=64, max_batch=1, max_tokens_per_step=1) == []

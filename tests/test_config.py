@@ -39,6 +39,32 @@ def test_no_rope_layers_both_forms():
     assert c.no_rope_layers == (1,) and c.moe_layers == (0, 2) and c.tie_word_embeddings
 
 
+def test_qk_norm_eps_defaults_to_the_rms_eps_and_an_explicit_key_wins():
+    base = dict(TINY_A, rms_norm_eps=3e-5)
+    assert Llama4TextConfig.from_dict(base).qk_norm_eps == 1e-6               # Tiny A names its own
+    base.pop("qk_norm_eps")
+    assert Llama4TextConfig.from_dict(base).qk_norm_eps == 3e-5               # what a checkpoint's file gives
+    from conftest import TINY_D
+    d = Llama4TextConfig.from_dict(TINY_D)
+    assert "qk_norm_eps" not in TINY_D and d.use_qk_norm and d.qk_norm_eps == d.rms_norm_eps == 1e-5
+
+
+def test_interval_switch_and_whole_floor_scale():
+    absent = dict(TINY_B, no_rope_layer_interval=3)
+    absent.pop("no_rope_layers")
+    assert Llama4TextConfig.from_dict(absent).no_rope_layers == (2, 5)
+    # the temperature switch is written as a boolean or as a non-negative integer
+    assert Llama4TextConfig.from_dict(dict(TINY_A, attn_temperature_tuning=4)).attn_temperature_tuning is True
+    assert Llama4TextConfig.from_dict(dict(TINY_A, attn_temperature_tuning=0)).attn_temperature_tuning is False
+    with pytest.raises(ConfigError):
+        Llama4TextConfig.from_dict(dict(TINY_A, attn_temperature_tuning="yes"))
+    with pytest.raises(ConfigError):
+        Llama4TextConfig.from_dict(dict(TINY_A, no_rope_layer_interval=0, no_rope_layers=None))
+    out = Llama4TextConfig.from_dict(TINY_A).to_dict()
+    assert out["floor_scale"] == 8 and isinstance(out["floor_scale"], int)
+    assert Llama4TextConfig.from_dict(dict(TINY_A, floor_scale=2.5)).to_dict()["floor_scale"] == 2.5
+
+
 def test_explicit_moe_layers_wins():
     c = Llama4TextConfig.from_dict(dict(TINY_B, moe_layers=[0, 4]))
     assert c.moe_layers == (0, 4)

@@ -371,13 +371,16 @@ def test_sampling_options_through_the_entry_point(model_dirs):
     greedy = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=6))[0]
     # top_k = 1 is greedy whatever the temperature and the seed
     assert eng.generate([prompt], SamplingParams(temperature=1.5, top_k=1, max_new_tokens=6, seed=5))[0] == greedy
-    # a logit bias large enough forces its token; a stop token ends the request and is not reported
-    forced = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=3, logit_bias={7: 1e4}))[0]
+    # a logit bias large enough forces its token (top_k = 1 makes the draw certain); greedy rows take the
+    # arg-max of the raw logits before any bias or penalty, as the reference does
+    forced = eng.generate([prompt], SamplingParams(temperature=1.0, top_k=1, max_new_tokens=3, logit_bias={7: 1e4}, seed=3))[0]
     assert forced == [7, 7, 7]
+    assert eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=6, logit_bias={7: 1e4},
+                                                 presence_penalty=1e4))[0] == greedy
     stopped = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=6, stop_token_ids=[greedy[2]]))[0]
     assert stopped == greedy[:2]
     # a presence penalty that large forbids every token seen so far (prompt tail included)
-    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_new_tokens=10, presence_penalty=1e4))[0]
+    out = eng.generate([prompt], SamplingParams(temperature=1.0, top_k=1, max_new_tokens=10, presence_penalty=1e4, seed=4))[0]
     assert len(set(out)) == len(out) and not (set(out) & set(prompt))
     # nucleus sampling only ever returns tokens of the nucleus
     sp = SamplingParams(temperature=1.0, top_p=0.3, max_new_tokens=1, seed=11)

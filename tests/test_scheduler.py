@@ -194,3 +194,76 @@ def test_random_arrivals_with_few_pages(seed):
         else:
             assert r.finish_reason == "cache_full"
     assert cache.free_pages() == {0: 12, 1: 12}
+
+
+def test_more_decodes_than_the_budget_take_turns():
+    """Four requests decode under a budget of three tokens a step: nobody starves, the one left out changes
+    from step to step, and pages are taken only for the decodes that run."""
+    cache, sched, runner = make(num_pages=64, max_batch=4, budget=8)
+    reqs = [req(i, 2, max_new=6) for i in range(4)]
+    for r in reqs:
+        sched.add(r)
+    plan = sched.plan()                                   # all four prompts in one step
+    sched.complete(plan, runner.run(plan))
+    sched.max_tokens_per_step = 3
+    left_out = []
+    for _ in range(200):
+        if not sched.has_work:
+            break
+        plan = sched.plan()
+        assert plan.num_tokens <= 3
+        deco = [r for r in sched.running if r.pending == 1 and r.computed >= len(r.prompt)]
+        if len(deco) == 4:
+            ran = {e.request.request_id for e in plan.entries}
+            assert len(ran) == 3
+            left_out.append(({0, 1, 2, 3} - ran).pop())
+        free_before = dict(cache.free_pages())
+        sched.complete(plan, runner.run(plan))
+        # no page was counted for a request that did not run
+        need = {0: 0, 1: 0}
+        assert all(free_before[g] - cache.free_pages()[g] <= len(plan.entries) for g in need)
+    assert not sched.has_work
+    assert len(set(left_out)) == 4, f"the same requests were left out every time: {left_out}"
+    assert all(a != b for a, b in zip(left_out, left_out[1:]))
+    for r in reqs:
+        assert r.finish_reason == "length" and r.generated == expected(r)
+
+
+def test_a_plan_that_preempted_admits_nobody():
+    # two requests fill the pool; when the newer one is sent back it must not return in the same plan
+    cache, sched, runner = make(num_pages=4, page_size=4, budget=32, chunk=64)
+    a, b = req(0, 7, max_new=8), req(1, 7, max_new=8)
+    sched.add(a)
+    sched.add(b)
+    saw = False
+    for _ in range(200):
+        if not sched.has_work:
+            break
+        plan = sched.plan()
+        if plan.preempted:
+            saw = True
+            assert all(e.request not in plan.preempted for e in plan.entries)
+            assert all(r.status == WAITING for r in plan.preempted)
+        if plan.entries:
+            sched.complete(plan, runner.run(plan))
+    assert saw and a.generated == expected(a) and b.generated == expected(b)
+    assert cache.free_pages() == {0: 4, 1: 4}
+
+
+def test_fail_and_fail_all_give_everything_back():
+    cache, sched, runner = make()
+    reqs = [req(i, 10, max_new=50) for i in range(6)]          # four run, two wait
+    for r in reqs:
+        sched.add(r)
+    plan = sched.plan()
+    sched.complete(plan, runner.run(plan))
+    sched.fail(reqs[1], "broken")
+    assert reqs[1].status == FINISHED and reqs[1].finish_reason == "error" and reqs[1].error == "broken"
+    assert 1 not in cache.requests
+    failed = sched.fail_all("the pass died")
+    assert {r.request_id for r in failed} == {0, 2, 3, 4, 5}
+    assert all(r.finish_reason == "error" and r.error == "the pass died" for r in failed)
+    assert not sched.has_work and cache.free_pages() == {0: 64, 1: 64} and cache.state_slots.free_count == 4
+    cache.check_invariants()
+    sched.fail(reqs[0], "again")                                 # ending twice changes nothing
+    assert reqs[0].error == "the pass died"
