@@ -197,7 +197,7 @@ def long_context_run(ns, cfg, pk, pk_kind) -> int:
     engine.generate([warm], SamplingParams(temperature=0.0, max_new_tokens=4))
     prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
     rid = engine.add_request(prompt, SamplingParams(temperature=0.0, max_new_tokens=new_tokens))
-    req = engine._requests[rid]
+    req = engine.request(rid)
     chunk_group = [g for g in engine.cache.groups if g.spec.kind == "chunk"][0].index
     full_group = [g for g in engine.cache.groups if g.spec.kind == "full"][0].index
     most_chunk_pages = 0
@@ -266,7 +266,7 @@ def timeline_run(ns, cfg) -> int:
     greedy = SamplingParams(temperature=0.0, max_new_tokens=1 << 30)
     ids = [inject_prefilled(engine, torch.randint(0, cfg.vocab_size, (ns.context - 20,), generator=gen).tolist(), greedy)
            for _ in range(B)]
-    reqs = [engine._requests[i] for i in ids]
+    reqs = [engine.request(i) for i in ids]
     slots = torch.zeros(8192, dtype=torch.int64, device=dev)
     events, state = [], {"n": 0}
 
@@ -436,7 +436,7 @@ def main() -> int:
         traced = 0 if through_engine else 4           # eager steps that record which experts the batch uses
         total = warmup + timed_steps + traced
         ids = [inject_prefilled(engine, tokens(ns.context - total), greedy) for _ in range(B)]
-        reqs = [engine._requests[i] for i in ids]
+        reqs = [engine.request(i) for i in ids]
         h2d = d2h = 0
         distinct = None
         launches0 = 0

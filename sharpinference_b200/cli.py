@@ -125,7 +125,8 @@ def main(argv=None) -> int:
         if ns.trace_layers:
             picks = iter(engine.runner.last_router_choices)
             for layer, norms in enumerate(engine.runner.last_layer_norms):
-                routed = getattr(engine.model.blocks[engine.model.schedule[layer].layer].ffn, "num_experts", 0) > 0
+                block = engine.model.blocks[engine.model.schedule[layer].layer]
+                routed = getattr(getattr(block, "ffn", None), "num_experts", 0) > 0
                 expert = int(next(picks)[-1]) if routed else None
                 print(f"step {steps} layer {layer}: |x| = {float(norms[-1]):.6f}"
                       + (f", expert {expert}" if expert is not None else ""), file=sys.stderr)

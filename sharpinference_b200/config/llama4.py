@@ -55,6 +55,7 @@ class Llama4TextConfig:
     eos_token_ids: Tuple[int, ...]
     bos_token_id: Optional[int]
     interleave_moe_layer_step: int
+    attention_bias: bool = False        # q, k, v and o projections carry a bias vector
 
     architecture = "Llama4ForCausalLM"
 
@@ -167,7 +168,6 @@ class Llama4TextConfig:
             r.require(experts >= 1, f"num_local_experts must be >= 1 when there are MoE layers, found {experts}")
         r.require(per_tok == 1, f"num_experts_per_tok must be 1 (top-1 sigmoid router), found {per_tok}")
         r.require(act == "silu", f"hidden_act must be 'silu', found '{act}'")
-        r.require(not attn_bias, "attention_bias=true is not supported: Llama 4 projections carry no bias")
         r.require(eps is not None and qk_eps is not None and eps > 0 and qk_eps > 0,
                   "rms_norm_eps and qk_norm_eps must be positive")
         r.require(theta > 0, f"rope_theta must be positive, found {theta}")
@@ -190,6 +190,7 @@ class Llama4TextConfig:
             attn_temperature_tuning=temp_tuning, floor_scale=floor_scale, attn_scale=attn_scale,
             rms_norm_eps=eps, tie_word_embeddings=tied, max_position_embeddings=max_pos,
             eos_token_ids=eos, bos_token_id=bos, interleave_moe_layer_step=step,
+            attention_bias=bool(attn_bias),
         )
 
     # -- writing -----------------------------------------------------------------------
@@ -224,7 +225,7 @@ class Llama4TextConfig:
             "tie_word_embeddings": self.tie_word_embeddings,
             "max_position_embeddings": self.max_position_embeddings,
             "hidden_act": "silu",
-            "attention_bias": False,
+            "attention_bias": self.attention_bias,
         }
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids)

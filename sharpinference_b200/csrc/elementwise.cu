@@ -39,6 +39,7 @@ SHARPI_API int sharpi_embed_gather(const int* ids, const void* table, int table_
 // ---------------------------------------------------------------------------------------
 // Residual add + RMSNorm.
 //   rows == nullptr:  x[t] += delta[t] (written back); out[t] = x[t] * rsqrt(mean(x[t]^2)+eps) * w
+//                     (w == nullptr: the weightless norm, src/SharpInference.Cpu/SimdKernels.cs:4252-4283)
 //   rows != nullptr:  r = rows[t]; v = x[r] + delta[r] (x untouched); out[t] = norm(v)
 // `out` has dtype out_dtype; `out32` (optional) receives the same values in fp32, for
 // consumers that must not see them rounded (the expert router).
@@ -95,7 +96,7 @@ add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __res
 #pragma unroll
         for (int k = 0; k < NORM_UNROLL; ++k) {
             const int i = i0 + k * NORM_THREADS;
-            ww[k] = (i < H) ? w[i] : 0.0f;
+            ww[k] = (i < H) ? (w ? w[i] : 1.0f) : 0.0f;
             if (CACHED) {
                 v[k] = (i < H) ? row_s[i] : 0.0f;      // this thread wrote it
             } else {
@@ -217,6 +218,21 @@ SHARPI_API int sharpi_add(const float* a, const float* b, float* y, long long n,
     if (blocks > 148 * 32) blocks = 148 * 32;
     add_kernel<<<(int)blocks, 256, 0, stream>>>(a, b, y, (size_t)n);
     SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
+// y[m, n] += bias[n]: the bias of a projection whose product came from the library.
+__global__ void add_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, int N) {
+    pdl_wait();
+    const int n = blockIdx.y * blockDim.x + threadIdx.x;
+    if (n < N) y[(size_t)blockIdx.x * N + n] += bias[n];
+}
+
+SHARPI_API int sharpi_add_bias(float* y, const float* bias, int M, int N, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return SHARPI_OK;
+    if ((N + 255) / 256 > 65535) return SHARPI_BAD_ARGUMENT;
+    dim3 grid(M, (N + 255) / 256);
+    SHARPI_LAUNCH_PDL(add_bias_kernel, grid, 256, 0, stream, y, bias, N);
     return SHARPI_OK;
 }
 

@@ -21,6 +21,9 @@ struct GemmArgs {
     const int* out_rows;
     int M, N, K, E;
     int accumulate;             // C += instead of C =
+    const float* bias;          // [N] added to every row (nullable)
+    const float* row_scale;     // row r of the product is multiplied by row_scale[scale_rows ? scale_rows[r] : r]
+    const int* scale_rows;      //   before the bias and before it is stored or added in (both nullable)
 };
 
 template <typename TA, typename TW>
@@ -95,23 +98,30 @@ __global__ void __launch_bounds__(256) gemm_nt_kernel(GemmArgs g) {
         const int m = m0 + ty * 4 + i;
         if (m >= m_end) continue;
         float* crow = g.C + (size_t)(g.out_rows ? g.out_rows[m] : m) * g.N;
+        const float s = g.row_scale ? g.row_scale[g.scale_rows ? g.scale_rows[m] : m] : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < g.N) crow[n] = g.accumulate ? crow[n] + acc[i][j] : acc[i][j];
+            if (n < g.N) {
+                float v = g.row_scale ? acc[i][j] * s : acc[i][j];
+                if (g.bias) v += g.bias[n];
+                crow[n] = g.accumulate ? crow[n] + v : v;
+            }
         }
     }
 }
 
 SHARPI_API int sharpi_gemm_nt(const void* A, int a_dtype, const void* W, int w_dtype, float* C,
                               const int* group_offsets, const int* a_rows, const int* out_rows, int M, int N,
-                              int K, int E, int accumulate, cudaStream_t stream) {
+                              int K, int E, int accumulate, const float* bias, const float* row_scale,
+                              const int* scale_rows, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return SHARPI_OK;
     if (K <= 0 || E <= 0) return SHARPI_BAD_ARGUMENT;
     if (!group_offsets && E != 1) return SHARPI_BAD_ARGUMENT;
     GemmArgs g;
     g.A = A; g.W = W; g.C = C; g.group_offsets = group_offsets; g.a_rows = a_rows; g.out_rows = out_rows;
     g.M = M; g.N = N; g.K = K; g.E = E; g.accumulate = accumulate;
+    g.bias = bias; g.row_scale = row_scale; g.scale_rows = scale_rows;
     long long m_tiles = (M + GB_M - 1) / GB_M + (group_offsets ? E : 0);
     long long n_tiles = (N + GB_N - 1) / GB_N;
     if (m_tiles > 65535 || n_tiles > 2147483647LL) return SHARPI_BAD_ARGUMENT;

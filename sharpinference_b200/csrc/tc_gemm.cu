@@ -13,7 +13,8 @@
 // rows) tile over all of K in steps of 64 elements.
 //
 // Two epilogues:
-//   MODE_STORE   C[out_row, n] = (or +=) D            fp32, out_row = out_rows[sorted row] or the sorted row
+//   MODE_STORE   C[out_row, n] = (or +=) s D          fp32, out_row = out_rows[sorted row] or the sorted row,
+//                s = row_scale[scale_rows[sorted row]] or 1 (a router that weights its experts' outputs)
 //   MODE_SWIGLU  W holds gate rows [0, I) and up rows [I, 2I); the CTA accumulates the gate tile
 //                and the matching up tile side by side and writes
 //                act[sorted row, i] = silu(s g) * (s u) as bf16, s = row_scale[scale_rows[sorted row]]
@@ -43,8 +44,8 @@ constexpr int TC_THREADS = 192;
 struct TcGemmParams {
     const int* group_offsets;   // [E + 1]
     const int* out_rows;        // MODE_STORE: nullable
-    const float* row_scale;     // MODE_SWIGLU: nullable
-    const int* scale_rows;      // MODE_SWIGLU: nullable
+    const float* row_scale;     // nullable
+    const int* scale_rows;      // nullable
     void* out;                  // MODE_STORE: float [*, N]; MODE_SWIGLU: bf16 [rows, I]
     int* status;                // device word: 0 ok, else the code of the wait that gave up
     int rows, N, K, E;          // N: weight rows per expert (MODE_SWIGLU: 2 I)
@@ -55,6 +56,11 @@ struct TcGemmParams {
     float* partial;
     int k_split;
     int* tickets;               // K split: one counter per tile, zero before the launch and again after it
+    // Every wait of the tiled kernel polls at most this often before it gives up.  `drop_loads_from` >= 0 makes
+    // the producer stop at that K block, so that the waits behind it run out: how a test sees a kernel give
+    // up, record its code and return (see sharpi_tc_set_wait_test); -1 in every other launch.
+    uint32_t wait_limit;
+    int drop_loads_from;
 };
 
 // WT: weight tiles of 128 rows that share one activation tile.  MODE_SWIGLU always has two (gate and up);
@@ -92,18 +98,18 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 template <int MODE>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const float* g, const float* u, bool two_tiles,
                                                   int n, int r_first, int count) {
+    // lane j of the warp fetches the scale of column j (all threads of a warp share the 16 columns)
+    const int lane = threadIdx.x & 31;
+    float mine = 1.0f;
+    if (p.row_scale && lane < count) {
+        const int r = r_first + lane;
+        mine = __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r));
+    }
+    float sc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sc[j] = __shfl_sync(0xffffffffu, mine, j);
     if (MODE == MODE_SWIGLU) {
         const int I = p.N / 2;
-        // lane j of the warp fetches the scale of column j (all threads of a warp share the 16 columns)
-        const int lane = threadIdx.x & 31;
-        float mine = 1.0f;
-        if (p.row_scale && lane < count) {
-            const int r = r_first + lane;
-            mine = __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r));
-        }
-        float sc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) sc[j] = __shfl_sync(0xffffffffu, mine, j);
         if (n < I) {
             bf16* act = reinterpret_cast<bf16*>(p.out);
 #pragma unroll
@@ -117,6 +123,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
     } else {
         float* C = reinterpret_cast<float*>(p.out);
         const bool n_ok = n < p.N, nb_ok = two_tiles && n + TC_BM < p.N;
+        const bool scaled = p.row_scale != nullptr;      // a router that weights the experts' outputs
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             if (j < count) {
@@ -125,12 +132,13 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
                 // without a round trip to memory per element.
                 const int r = r_first + j;
                 float* dst = C + (size_t)(p.out_rows ? __ldg(p.out_rows + r) : r) * p.N + n;
+                const float gv = scaled ? g[j] * sc[j] : g[j], uv = scaled ? u[j] * sc[j] : u[j];
                 if (p.accumulate) {
-                    if (n_ok) atomicAdd(dst, g[j]);
-                    if (nb_ok) atomicAdd(dst + TC_BM, u[j]);
+                    if (n_ok) atomicAdd(dst, gv);
+                    if (nb_ok) atomicAdd(dst + TC_BM, uv);
                 } else {
-                    if (n_ok) *dst = g[j];
-                    if (nb_ok) dst[TC_BM] = u[j];
+                    if (n_ok) *dst = gv;
+                    if (nb_ok) dst[TC_BM] = uv;
                 }
             }
         }
@@ -251,8 +259,9 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             int issued = 0;
             bool ok = true;
             for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                if (p.drop_loads_from >= 0 && kb >= p.drop_loads_from) break;     // test only: see TcGemmParams
                 const int s = kb % Cfg::STAGES;
-                if (kb >= Cfg::STAGES) ok = mbar_wait(&empty_bar[s], ((kb / Cfg::STAGES) - 1) & 1);
+                if (kb >= Cfg::STAGES) ok = mbar_wait(&empty_bar[s], ((kb / Cfg::STAGES) - 1) & 1, p.wait_limit);
                 if (!ok) { atomicExch(p.status, 1); break; }
                 uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
                 const int kx = (kb_begin + kb) * TC_BK;
@@ -277,7 +286,7 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             bool ok = true;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const int s = kb % Cfg::STAGES;
-                ok = mbar_wait(&full_bar[s], (kb / Cfg::STAGES) & 1);
+                ok = mbar_wait(&full_bar[s], (kb / Cfg::STAGES) & 1, p.wait_limit);
                 if (!ok) { atomicExch(p.status, 2); break; }
                 tcgen05_fence_after();
                 const uint8_t* stage = smem + s * Cfg::STAGE_BYTES;
@@ -296,7 +305,7 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         }
     } else {
         // ---- epilogue: warps 0..3, thread = TMEM lane = weight row ---------------------------
-        const bool ok = mbar_wait(accum_bar, 0);
+        const bool ok = mbar_wait(accum_bar, 0, p.wait_limit);
         const int n = n0 + warp * 32 + lane;
         const int nb = n1 - n0 + n;                    // the row of the second tile
         const int valid = min(NT, row_end - row0);
@@ -679,6 +688,18 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmPara
     return SHARPI_OK;
 }
 
+// Test hook: the NEXT launch of sharpi_tc_grouped_gemm (tiled kernel) polls every wait at most `limit` times
+// and its producer issues no loads from K block `drop_from` on.  The waits behind the missing loads run out,
+// the kernel records the code of a wait that gave up in *status and returns with its tensor memory freed:
+// the way a test observes that path without a fault.  The hook is consumed by that one launch.
+static uint32_t g_test_wait_limit = 0;
+static int g_test_drop_from = -1;
+
+SHARPI_API void sharpi_tc_set_wait_test(unsigned limit, int drop_from) {
+    g_test_wait_limit = limit;
+    g_test_drop_from = drop_from;
+}
+
 // A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
 // `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes; 0 asks for the
 // persistent kernel (up to 256 groups, no K split).
@@ -702,6 +723,10 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
     if (k_split < 1 || k_split > 16 || (k_split > 1 && (!partial || !tickets))) return SHARPI_BAD_ARGUMENT;
     p.partial = partial; p.k_split = k_split; p.tickets = tickets;
+    p.wait_limit = g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT;
+    p.drop_loads_from = g_test_drop_from;
+    g_test_wait_limit = 0;
+    g_test_drop_from = -1;
     const int n_out = (mode == MODE_SWIGLU) ? N / 2 : N;
     if (row_tile == 0) {
         // the persistent kernel: 128-row activation boxes, two weight tiles per item

@@ -16,6 +16,7 @@ committed after it.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from types import SimpleNamespace
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -42,19 +43,36 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=list)   # places among `tokens` whose logits are wanted
 
 
-class StepRunner:
-    ATTENTION_TILE = 64        # rows of one request that one attention CTA serves (128 with the tcgen05 kernel)
-    DECODE_ROWS_UP_TO = 4      # entries this short are served row by row by the split-KV kernel
+@dataclass
+class HostStep:
+    """One step's metadata laid out on the host: the int32 words of the staging buffer, where each named
+    segment lies in it (offset, shape), and what the planners returned beside their arrays."""
 
+    words: np.ndarray
+    segments: Dict[object, tuple]                    # name -> (offset in words, shape)
+    plan_values: Dict[Hashable, dict]
+    starts: List[int]
+    lengths: List[int]
+    slots: List[int]
+    num_wanted: int
+    width: int
+
+
+class StepRunner:
     def __init__(self, model, cache: CacheManager):
         self.model = model
         self.cache = cache
         self.device = cache.device
         self._slots = cache.layer_slots()
-        # rows per attention tile: the largest size every mixer that cares can take
-        sizes = [b.mixer.prefill_tile_rows(cache.page_size) for b in getattr(model, "blocks", [])
-                 if hasattr(b.mixer, "prefill_tile_rows")]
-        self.attention_tile = min(sizes) if sizes else self.ATTENTION_TILE
+        # Mixers that cut the step's rows for their kernels bring a planner (parts.base.StepPlanner); planners
+        # with equal keys are one.  The step function runs each once per step and ships its arrays in the
+        # step's one metadata copy; it knows nothing of what they mean.
+        self.planners: Dict[Hashable, object] = {}
+        for b in getattr(model, "blocks", []):
+            make = getattr(b.mixer, "step_planner", None)
+            planner = make(cache.page_size) if make is not None else None
+            if planner is not None:
+                self.planners.setdefault(planner.key, planner)
         self.steps_run = 0
         self.rows_run = 0
         # Tracing, for hunting the first difference: when `trace_router` is set, every routed
@@ -74,9 +92,9 @@ class StepRunner:
         self._status_host, self._status_event, self._status_pending = None, None, False
         self.last_router_choices: List[torch.Tensor] = []
         # Decode-only steps are launch-bound at small batches, so they are captured once per shape
-        # (requests, wanted rows, block-table width) as a CUDA graph and replayed; the step's metadata
-        # lives in one static device buffer that is refreshed before each replay.  The reference does
-        # the same for its per-token decode (src/SharpInference.Engine/CudaForwardPass.cs:1668-1675).
+        # (requests, wanted rows, block-table width, the planners' buckets) as a CUDA graph and replayed; the
+        # step's metadata lives in one static device buffer that is refreshed before each replay.  The
+        # reference does the same for its per-token decode (src/SharpInference.Engine/CudaForwardPass.cs:1668-1675).
         # Only models whose parts read the step through device tensors alone can be captured.
         self.use_graphs = all(getattr(b.mixer, "graph_safe", False) and getattr(getattr(b, "ffn", None), "graph_safe", False)
                               for b in model.blocks) if hasattr(model, "blocks") else False
@@ -110,19 +128,12 @@ class StepRunner:
                     raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary [0, {V})",
                                     e.request_id)
 
-    def _layout(self, T: int, B: int, R: int, width: int, n_tiles: int, n_dec: int) -> np.ndarray:
-        """Offsets (in int32 words, each segment starting on 16 bytes) of the staging buffer's segments:
-        token ids, positions, row -> request, request starts, row offsets, state slots, wanted rows, one
-        block table per cache group, attention tiles, single rows."""
-        sizes = [T, T, T, B, B + 1, B, R] + [B * width] * len(self.cache.groups) + [4 * n_tiles, n_dec]
-        return np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
-
-    def build_context(self, entries: Sequence[StepEntry], width: Optional[int] = None,
-                      buffers: Optional[tuple] = None, decode_keys: Optional[int] = None) -> StepContext:
-        """Lay out the step's metadata: one pinned host buffer, one copy to the device.  ``width``
-        pads the block tables to a fixed number of columns; ``buffers`` = (pinned host tensor, device
-        tensor) of exactly the layout's size are reused instead of fresh ones (graph replay), and
-        ``decode_keys`` then bounds the keys of the single rows for every step that reuses the layout."""
+    def lay_out(self, entries: Sequence[StepEntry], width: Optional[int] = None,
+                buckets: Optional[Dict[Hashable, Hashable]] = None) -> HostStep:
+        """The step's metadata as one int32 array (every segment starting on 16 bytes): token ids, positions,
+        row -> request, request starts, row offsets, state slots, wanted rows, one block table per cache
+        group, then every planner's arrays.  ``width`` pads the block tables to a fixed number of columns;
+        ``buckets`` (planner key -> bucket) is what a replayed graph fixed of each planner's plan."""
         cache = self.cache
         starts, lengths, slots = [], [], []
         for e in entries:
@@ -130,92 +141,98 @@ class StepRunner:
             starts.append(rc.length)
             lengths.append(len(e.tokens))
             slots.append(rc.state_slot)
-        B = len(entries)
-        T = sum(lengths)
+        B, T = len(entries), sum(lengths)
         tokens = np.empty(T, dtype=np.int64)
         positions = np.empty(T, dtype=np.int32)
         row_request = np.empty(T, dtype=np.int32)
         row_offsets = np.zeros(B + 1, dtype=np.int32)
         want_rows: List[int] = []
-        tiles: List[int] = []            # (first row, rows, first position, request) per attention tile
-        decode_rows: List[int] = []
-        keys = 0                         # sum of position + 1 over the single rows
         r = 0
         for b, e in enumerate(entries):
             n = lengths[b]
-            if n <= self.DECODE_ROWS_UP_TO:
-                decode_rows.extend(range(r, r + n))
-                keys += n * starts[b] + n * (n + 1) // 2
-            else:
-                for t0 in range(0, n, self.attention_tile):
-                    tiles.extend((r + t0, min(self.attention_tile, n - t0), starts[b] + t0, b))
             tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int64)
             positions[r:r + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             row_request[r:r + n] = b
             want_rows.extend(r + w for w in e.want)
             r += n
             row_offsets[b + 1] = r
-
-        # Block tables, one per group, padded to a common width with -1.
         ids = [e.request_id for e in entries]
         needed = self.table_width(ids)
         if width is None:
             width = needed
         elif width < needed:
             raise StepError(f"block tables need {needed} columns, the buffer has {width}")
-        G = len(cache.groups)
-        R = len(want_rows)
-        # layout of the one int32 staging buffer
-        n_tiles, n_dec = len(tiles) // 4, len(decode_rows)
-        offsets = self._layout(T, B, R, width, n_tiles, n_dec)
-        total = int(offsets[-1])
+        pieces: List[tuple] = [("token_ids", tokens), ("positions", positions), ("row_request", row_request),
+                               ("request_start", np.asarray(starts, dtype=np.int32)), ("row_offsets", row_offsets),
+                               ("state_slots", np.asarray(slots, dtype=np.int32)),
+                               ("want_rows", np.asarray(want_rows, dtype=np.int32))]
+        for g in cache.groups:
+            table = np.full((B, width), -1, dtype=np.int32)
+            for b, rid in enumerate(ids):
+                t = cache.requests[rid].tables[g.index]
+                table[b, :len(t)] = t
+            pieces.append((("table", g.index), table))
+        plan_values: Dict[Hashable, dict] = {}
+        for key, planner in self.planners.items():
+            data = planner.plan(starts, lengths, None if buckets is None else buckets.get(key))
+            plan_values[key] = dict(data.values)
+            for name in sorted(data.arrays):
+                pieces.append((("plan", key, name), np.ascontiguousarray(data.arrays[name], dtype=np.int32)))
+        segments, at = {}, 0
+        for name, arr in pieces:
+            segments[name] = (at, tuple(arr.shape))
+            at += (arr.size + 3) // 4 * 4
+        words = np.zeros(at, dtype=np.int32)
+        for name, arr in pieces:
+            o = segments[name][0]
+            words[o:o + arr.size] = arr.reshape(-1)
+        return HostStep(words, segments, plan_values, starts, lengths, slots, len(want_rows), width)
+
+    def build_context(self, entries: Sequence[StepEntry], width: Optional[int] = None,
+                      buffers: Optional[tuple] = None, buckets: Optional[Dict[Hashable, Hashable]] = None,
+                      host_step: Optional[HostStep] = None) -> StepContext:
+        """Lay out the step's metadata and bring it to the device in one copy.  ``buffers`` = (pinned host
+        tensor, device tensor) of exactly the layout's size are reused instead of fresh ones (graph replay)."""
+        hs = host_step if host_step is not None else self.lay_out(entries, width, buckets)
+        total = hs.words.size
         if buffers is None:
             host = torch.empty(total, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         else:
             host = buffers[0]
             if host.numel() != total:
                 raise StepError(f"static step buffer holds {host.numel()} words, this step needs {total}")
-        hv = host.numpy()
-        hv[offsets[0]:offsets[0] + T] = tokens
-        hv[offsets[1]:offsets[1] + T] = positions
-        hv[offsets[2]:offsets[2] + T] = row_request
-        hv[offsets[3]:offsets[3] + B] = starts
-        hv[offsets[4]:offsets[4] + B + 1] = row_offsets
-        hv[offsets[5]:offsets[5] + B] = slots
-        hv[offsets[6]:offsets[6] + R] = want_rows
-        for gi, g in enumerate(cache.groups):
-            table = np.full((B, width), -1, dtype=np.int32)
-            for b, rid in enumerate(ids):
-                t = cache.requests[rid].tables[g.index]
-                table[b, :len(t)] = t
-            o = offsets[7 + gi]
-            hv[o:o + B * width] = table.reshape(-1)
-        hv[offsets[7 + G]:offsets[7 + G] + 4 * n_tiles] = tiles
-        hv[offsets[8 + G]:offsets[8 + G] + n_dec] = decode_rows
+        host.numpy()[:] = hs.words
         if buffers is None:
             dev = host.to(self.device, non_blocking=True)
         else:
             dev = buffers[1]
             dev.copy_(host, non_blocking=True)
 
-        def view(i: int, n: int) -> torch.Tensor:
-            return dev[int(offsets[i]):int(offsets[i]) + n]
+        def view(name) -> Optional[torch.Tensor]:
+            o, shape = hs.segments[name]
+            n = int(np.prod(shape)) if shape else 1
+            return dev[o:o + n].view(shape) if n else None
 
+        plans = {}
+        for key in self.planners:
+            fields = dict(hs.plan_values[key])
+            for name in hs.segments:
+                if isinstance(name, tuple) and name[0] == "plan" and name[1] == key:
+                    fields[name[2]] = view(name)
+            plans[key] = SimpleNamespace(**fields)
+        B, T, lengths, starts = len(hs.lengths), sum(hs.lengths), hs.lengths, hs.starts
         return StepContext(
-            num_tokens=T, num_requests=B, token_ids=view(0, T), positions=view(1, T), row_request=view(2, T),
-            request_start=view(3, B), row_offsets=view(4, B + 1), state_slots=view(5, B),
-            block_tables={g.index: view(7 + gi, B * width).view(B, width) for gi, g in enumerate(cache.groups)},
-            want_rows=view(6, R) if R else None, slots=self._slots,
-            host_starts=starts, host_lengths=lengths, host_state_slots=slots,
+            num_tokens=T, num_requests=B, token_ids=view("token_ids"), positions=view("positions"),
+            row_request=view("row_request"), request_start=view("request_start"), row_offsets=view("row_offsets"),
+            state_slots=view("state_slots"),
+            block_tables={g.index: view(("table", g.index)) for g in self.cache.groups},
+            want_rows=view("want_rows"), slots=self._slots,
+            host_starts=starts, host_lengths=lengths, host_state_slots=hs.slots,
             max_rows_per_request=max(lengths),
             # with a fixed table width the bound must hold for every later step that reuses the layout
             max_context=(max(s + n for s, n in zip(starts, lengths)) if buffers is None
-                         else width * cache.page_size),
-            decode_only=all(n == 1 for n in lengths),
-            attn_tiles=view(7 + G, 4 * n_tiles).view(n_tiles, 4) if n_tiles else None, num_attn_tiles=n_tiles,
-            attn_tile_rows=self.attention_tile,
-            decode_rows=view(8 + G, n_dec) if (n_dec and n_dec != T) else None, num_decode_rows=n_dec,
-            decode_keys=keys if decode_keys is None else decode_keys,
+                         else hs.width * self.cache.page_size),
+            decode_only=all(n == 1 for n in lengths), plans=plans,
         )
 
     # The word in which a tensor-core kernel records a wait that gave up is copied to pinned host memory
@@ -272,14 +289,6 @@ class StepRunner:
     # -- CUDA graphs for decode-only steps -------------------------------------------------------
     TABLE_WIDTH_STEP = 16      # block-table columns are rounded up to a multiple of this in a graph
 
-    @staticmethod
-    def keys_bucket(keys: int, rows: int = 1) -> int:
-        """``keys`` rounded up to a multiple of a power of two: a sixteenth to an eighth of ``keys``, and at
-        least 256 keys a row, so that a batch that gains a key a row each step stays in its bucket for 256
-        steps or more (a new bucket means a step run eagerly and a graph captured)."""
-        step = 1 << max((256 * max(rows, 1) - 1).bit_length(), keys.bit_length() - 4)
-        return (keys + step - 1) // step * step
-
     def table_width(self, request_ids) -> int:
         return max([1] + [len(self.cache.requests[r].tables[g.index]) for r in request_ids for g in self.cache.groups])
 
@@ -306,22 +315,24 @@ class StepRunner:
         step.  Returns (handled, logits); not handled means "run it eagerly this time"."""
         step = self.TABLE_WIDTH_STEP
         width = (self.table_width([e.request_id for e in entries]) + step - 1) // step * step
-        # the keys of all rows together, rounded up (see keys_bucket): the grid of the decode attention kernels
-        # is as large as this says, whatever the longest request is
-        keys = self.keys_bucket(sum(self.cache.requests[e.request_id].length + 1 for e in entries), len(entries))
-        key = (len(entries), sum(len(e.want) for e in entries), width, keys)
+        # what every planner bakes into a graph (for attention: the keys of all rows together, rounded up, which
+        # sizes the grid of the decode kernels whatever the longest request is)
+        starts = [self.cache.requests[e.request_id].length for e in entries]
+        lengths = [1] * len(entries)
+        buckets = {key: p.bucket(starts, lengths) for key, p in self.planners.items()}
+        key = (len(entries), sum(len(e.want) for e in entries), width, tuple(buckets.values()))
         rec = self._graphs.get(key)
         if rec is None:
             if key not in self._graph_seen:          # first sight: an eager run warms every kernel up
                 self._graph_seen.add(key)
                 return False, None
-            rec = self._capture(entries, width, keys)
+            rec = self._capture(entries, width, buckets)
             while len(self._graphs) >= self.max_graphs:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = rec
         else:
             rec["copied"].synchronize()              # the previous copy out of the pinned buffer is over
-            self._refresh_decode(rec, entries, width)
+            self._refresh_decode(rec, entries, width, buckets)
             rec["copied"].record()
         rec["graph"].replay()
         library.launch_count += rec["launches"]     # the replay launches what the capture recorded
@@ -329,44 +340,52 @@ class StepRunner:
         self.last_router_choices = []
         return True, rec["logits"]
 
-    def _refresh_decode(self, rec: dict, entries: Sequence[StepEntry], width: int) -> None:
+    def _refresh_decode(self, rec: dict, entries: Sequence[StepEntry], width: int, buckets: dict) -> None:
         """The static buffer of a captured decode step, brought up to date.  While the same requests decode
-        with the same wanted places, only what moves is rewritten: token ids, positions, and the block-table
-        rows of requests whose tables changed (a new page, a page given back).  Anything else lays the whole
-        buffer out again."""
+        with the same wanted places, only what moves is rewritten: token ids, positions, the block-table
+        rows of requests whose tables changed (a new page, a page given back), and the planners' arrays.
+        Anything else lays the whole buffer out again."""
         cache = self.cache
         ids = tuple(e.request_id for e in entries)
         wants = tuple(tuple(e.want) for e in entries)
         if rec.get("ids") != ids or rec.get("wants") != wants:
-            self.build_context(entries, width=width, buffers=(rec["host"], rec["dev"]))
+            self.build_context(entries, width=width, buffers=(rec["host"], rec["dev"]), buckets=buckets)
             rec["ids"], rec["wants"] = ids, wants
             rec["versions"] = [cache.requests[i].version for i in ids]
             return
-        hv, offsets, B = rec["host"].numpy(), rec["offsets"], len(ids)
+        hv, seg, B = rec["host"].numpy(), rec["segments"], len(ids)
         starts = [cache.requests[i].length for i in ids]
-        hv[offsets[0]:offsets[0] + B] = [e.tokens[0] for e in entries]
-        hv[offsets[1]:offsets[1] + B] = starts                    # a decode row's position is its request's length
-        hv[offsets[3]:offsets[3] + B] = starts
+        hv[seg["token_ids"][0]:seg["token_ids"][0] + B] = [e.tokens[0] for e in entries]
+        hv[seg["positions"][0]:seg["positions"][0] + B] = starts       # a decode row's position is its request's length
+        hv[seg["request_start"][0]:seg["request_start"][0] + B] = starts
         versions = rec["versions"]
         for b, rid in enumerate(ids):
             rc = cache.requests[rid]
             if rc.version != versions[b]:
                 versions[b] = rc.version
-                for gi, g in enumerate(cache.groups):
+                for g in cache.groups:
                     t = rc.tables[g.index]
                     if len(t) > width:
                         raise StepError(f"block tables need {len(t)} columns, the buffer has {width}")
-                    o = int(offsets[7 + gi]) + b * width
+                    o = seg[("table", g.index)][0] + b * width
                     hv[o:o + len(t)] = t
                     hv[o + len(t):o + width] = -1
+        for key, planner in self.planners.items():
+            data = planner.plan(starts, [1] * B, buckets.get(key))
+            for name, arr in data.arrays.items():
+                o, shape = seg[("plan", key, name)]
+                arr = np.ascontiguousarray(arr, dtype=np.int32)
+                if tuple(arr.shape) != shape:
+                    raise StepError(f"planner {key!r}: array '{name}' changed shape inside a bucket "
+                                    f"({shape} captured, {tuple(arr.shape)} now)")
+                hv[o:o + arr.size] = arr.reshape(-1)
         rec["dev"].copy_(rec["host"], non_blocking=True)
 
-    def _capture(self, entries: Sequence[StepEntry], width: int, decode_keys: int) -> dict:
-        B, R = len(entries), sum(len(e.want) for e in entries)
-        size = int(self._layout(B, B, R, width, 0, B)[-1])
-        host = torch.empty(size, dtype=torch.int32, pin_memory=True)
-        dev = torch.empty(size, dtype=torch.int32, device=self.device)
-        ctx = self.build_context(entries, width=width, buffers=(host, dev), decode_keys=decode_keys)
+    def _capture(self, entries: Sequence[StepEntry], width: int, buckets: dict) -> dict:
+        hs = self.lay_out(entries, width, buckets)
+        host = torch.empty(hs.words.size, dtype=torch.int32, pin_memory=True)
+        dev = torch.empty(hs.words.size, dtype=torch.int32, device=self.device)
+        ctx = self.build_context(entries, buffers=(host, dev), host_step=hs)
         copied = torch.cuda.Event()
         copied.record()
         torch.cuda.synchronize(self.device)
@@ -380,6 +399,6 @@ class StepRunner:
             self._graph_pool = graph.pool()
         ids = tuple(e.request_id for e in entries)
         return {"graph": graph, "host": host, "dev": dev, "ctx": ctx, "logits": logits, "copied": copied,
-                "launches": launches, "offsets": [int(o) for o in self._layout(B, B, R, width, 0, B)],
+                "launches": launches, "segments": hs.segments,
                 "ids": ids, "wants": tuple(tuple(e.want) for e in entries),
                 "versions": [self.cache.requests[i].version for i in ids]}

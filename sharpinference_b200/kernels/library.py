@@ -38,7 +38,8 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill_tc": ("attention_prefill_tc", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P]),
-    "sharpi_gemm_nt": ("gemm_generic", [P, I, P, I, P, P, P, P, I, I, I, I, I, P]),
+    "sharpi_gemm_nt": ("gemm_generic", [P, I, P, I, P, P, P, P, I, I, I, I, I, P, P, P, P]),
+    "sharpi_add_bias": ("elementwise", [P, P, I, I, P]),
     "sharpi_router_top1": ("moe", [P, P, I, I, I, I, P, P, P, P, P, P, P]),
     "sharpi_moe_sort": ("moe", [P, I, I, P, P, P]),
     "sharpi_tc_grouped_gemm": ("tc_gemm", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),

@@ -68,7 +68,8 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     ``want_fp32`` (or ``out32``) is given, else ``None``.
     """
     _need(x, "x", torch.float32)
-    _need(weight, "weight", torch.float32)
+    if weight is not None:                  # None: the weightless norm
+        _need(weight, "weight", torch.float32)
     H = x.shape[-1]
     if delta is not None:
         _need(delta, "delta", torch.float32)
@@ -84,7 +85,7 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     if want_fp32 and out32 is None:
         out32 = out if out_dtype == torch.float32 else torch.empty((T, H), dtype=torch.float32, device=x.device)
     alias = out32 is not None and out32.data_ptr() == out.data_ptr()
-    check(kernel("sharpi_add_rmsnorm")(x.data_ptr(), _ptr(delta), weight.data_ptr(), float(eps), _ptr(rows), T, H,
+    check(kernel("sharpi_add_rmsnorm")(x.data_ptr(), _ptr(delta), _ptr(weight), float(eps), _ptr(rows), T, H,
                                        out.data_ptr(), dtype_code(out.dtype), None if alias else _ptr(out32),
                                        _stream()), "sharpi_add_rmsnorm")
     return out, out32
@@ -109,6 +110,17 @@ def timestamp(slots: torch.Tensor, index: int) -> None:
     if not 0 <= index < slots.numel():
         raise KernelError(f"timestamp slot {index} outside 0 .. {slots.numel() - 1}")
     check(kernel("sharpi_timestamp")(slots.data_ptr(), index, _stream()), "sharpi_timestamp")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``y[m, :] += bias`` in place (float32)."""
+    _need(y, "y", torch.float32)
+    _need(bias, "bias", torch.float32)
+    M, N = y.shape
+    if bias.numel() != N:
+        raise KernelError(f"bias has {bias.numel()} entries, the rows have {N}")
+    check(kernel("sharpi_add_bias")(y.data_ptr(), bias.data_ptr(), M, N, _stream()), "sharpi_add_bias")
+    return y
 
 
 def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -275,13 +287,16 @@ def attention_prefill_tc(q: torch.Tensor, kv_layer: torch.Tensor, block_table: t
 
 def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
             group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
-            out_rows: Optional[torch.Tensor] = None, rows: Optional[int] = None, accumulate: bool = False
-            ) -> torch.Tensor:
+            out_rows: Optional[torch.Tensor] = None, rows: Optional[int] = None, accumulate: bool = False,
+            bias: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+            scale_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``C = A . W^T`` with fp32 accumulation on the CUDA cores.
 
     Dense: ``w`` is [N, K].  Grouped: ``w`` is [E, N, K] and ``group_offsets`` (int32 [E+1])
     gives the first sorted row of every expert.  ``a_rows`` / ``out_rows`` (int32 [rows]) make
-    sorted row r read ``A[a_rows[r]]`` and write ``C[out_rows[r]]``.
+    sorted row r read ``A[a_rows[r]]`` and write ``C[out_rows[r]]``.  ``row_scale`` (float32)
+    multiplies row r of the product by ``row_scale[scale_rows[r] or r]``, ``bias`` (float32 [N]) is
+    added to it, before the row is stored or added in.
     """
     _need(a, "a")
     _need(w, "w")
@@ -307,9 +322,18 @@ def gemm_nt(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         _need(a_rows, "a_rows", torch.int32)
     if out_rows is not None:
         _need(out_rows, "out_rows", torch.int32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError(f"bias has {bias.numel()} entries, the product has {N} columns")
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32)
+    if scale_rows is not None:
+        _need(scale_rows, "scale_rows", torch.int32)
     check(kernel("sharpi_gemm_nt")(a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype),
                                    out.data_ptr(), _ptr(group_offsets), _ptr(a_rows), _ptr(out_rows), M, N, K, E,
-                                   int(accumulate), _stream()), "sharpi_gemm_nt")
+                                   int(accumulate), _ptr(bias), _ptr(row_scale), _ptr(scale_rows), _stream()),
+          "sharpi_gemm_nt")
     return out
 
 
@@ -368,6 +392,18 @@ def tc_row_tile(rows: int, mode: Optional[int] = None, groups: int = 1) -> int:
     return 128
 
 
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once)."""
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
 def tc_k_split(rows: int, n_out: int, sms: int = 148) -> int:
     """Into how many CTAs a tile's K range is cut.  With few rows few experts are active (at most one
     per row), so 128-row weight tiles alone cannot fill the GPU; cutting K makes up to four times as many
@@ -400,7 +436,8 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     """Per-expert products on the tensor cores.  ``a`` bfloat16 [rows, K] sorted by expert,
     ``w`` bfloat16 [E, N, K], ``group_offsets`` int32 [E + 1].
 
-    ``mode=TC_MODE_STORE``: float32 ``out[out_rows[r] or r] (+)= a[r] . w[e(r)]^T``, shape [*, N].
+    ``mode=TC_MODE_STORE``: float32 ``out[out_rows[r] or r] (+)= s * a[r] . w[e(r)]^T``, shape [*, N], with
+    ``s = row_scale[scale_rows[r] or r]`` when ``row_scale`` is given (a router that weights outputs), else 1.
     ``mode=TC_MODE_SWIGLU``: ``w`` holds gate rows then up rows (N = 2 I); bfloat16
     ``out[r] = silu(s g) * (s u)``, shape [rows, I], ``s = row_scale[scale_rows[r]]``.
     """
@@ -421,7 +458,7 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     _need(out, "out", torch.bfloat16 if mode == TC_MODE_SWIGLU else torch.float32)
     status = status_word(a.device)
     if k_split is None:
-        k_split = tc_k_split(rows, (N // 2 if mode == TC_MODE_SWIGLU else N))
+        k_split = tc_k_split(rows, (N // 2 if mode == TC_MODE_SWIGLU else N), sm_count(a.device))
     partial = torch.empty((k_split, rows, N), dtype=torch.float32, device=a.device) if k_split > 1 else None
     if row_tile is None:
         row_tile = tc_row_tile(rows, mode, E)
@@ -433,6 +470,17 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
                                            _ptr(partial), _ptr(tickets), rows, N, K, E, mode, row_tile,
                                            int(accumulate), k_split, _stream()), "sharpi_tc_grouped_gemm")
     return out
+
+
+def tc_set_wait_test(limit: int, drop_from: int) -> None:
+    """Test hook: the next ``tc_grouped_gemm`` launch (tiled kernel) polls each wait at most ``limit`` times and
+    loads nothing from K block ``drop_from`` on, so a wait runs out, the kernel records its code in the status
+    word and returns; ``check_status`` then raises.  Consumed by that one launch."""
+    import ctypes
+    from .library import load_library
+    fn = load_library("tc_gemm").sharpi_tc_set_wait_test
+    fn.argtypes, fn.restype = [ctypes.c_uint, ctypes.c_int], None
+    fn(int(limit), int(drop_from))
 
 
 _dense_offsets = {}
@@ -453,7 +501,8 @@ def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Opt
         _dense_offsets[key] = offsets
     N = w.shape[0]
     n_tiles = ((N // 2 if swiglu else N) + 127) // 128
-    k_split = 1 if n_tiles >= 148 else max(1, min(4, (2 * 148 + n_tiles - 1) // n_tiles))
+    sms = sm_count(a.device)
+    k_split = 1 if n_tiles >= sms else max(1, min(4, (2 * sms + n_tiles - 1) // n_tiles))
     row_tile = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     return tc_grouped_gemm(a, w.unsqueeze(0), offsets, mode=TC_MODE_SWIGLU if swiglu else TC_MODE_STORE, out=out,
                            row_tile=row_tile, k_split=k_split, accumulate=accumulate)

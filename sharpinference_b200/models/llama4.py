@@ -20,8 +20,10 @@ architecture's safetensors checkpoints: per-layer ``self_attn.{q,k,v,o}_proj.wei
 ``feed_forward.experts.<e>.{gate,up,down}_proj.weight`` as ``[out, in]`` matrices),
 ``feed_forward.shared_expert.{gate,up,down}_proj.weight``;
 dense layers ``feed_forward.{gate,up,down}_proj.weight``; ``model.embed_tokens.weight``,
-``model.norm.weight``, ``lm_head.weight``.  Q, K and V are concatenated for one product, gate and up
-likewise, and the expert tensors are transposed once to ``[E, out, in]``.
+``model.norm.weight``, ``lm_head.weight``; with ``attention_bias`` also ``self_attn.{q,k,v,o}_proj.bias``
+(the reference probes for a bias tensor, src/SharpInference.Core/ModelGraph.cs:269-270).  Q, K and V are
+concatenated for one product, gate and up likewise, and the expert tensors are transposed once to
+``[E, out, in]``.
 """
 from __future__ import annotations
 
@@ -60,14 +62,20 @@ def build_llama4(config: Llama4TextConfig, weights: WeightSource) -> DecoderMode
                     weights.matrix(p + "self_attn.k_proj.weight", (nkv * d, H)),
                     weights.matrix(p + "self_attn.v_proj.weight", (nkv * d, H))])
         o = weights.matrix(p + "self_attn.o_proj.weight", (H, nq * d))
+        qkv_bias = o_bias = None
+        if c.attention_bias:
+            qkv_bias = torch.cat([weights.vector(p + "self_attn.q_proj.bias", (nq * d,), init="normal"),
+                                  weights.vector(p + "self_attn.k_proj.bias", (nkv * d,), init="normal"),
+                                  weights.vector(p + "self_attn.v_proj.bias", (nkv * d,), init="normal")]).contiguous()
+            o_bias = weights.vector(p + "self_attn.o_proj.bias", (H,), init="normal")
         if c.layer_uses_rope(i):
-            mixer = PagedAttention(qkv=Linear(qkv, p + "qkv"), out=Linear(o, p + "o"), num_heads=nq,
+            mixer = PagedAttention(qkv=Linear(qkv, p + "qkv", bias=qkv_bias), out=Linear(o, p + "o", bias=o_bias), num_heads=nq,
                                    num_kv_heads=nkv, head_dim=d, mask="chunk", span=c.attention_chunk_size,
                                    position=rotary, qk_norm=L2Norm(c.qk_norm_eps) if c.use_qk_norm else None,
                                    temperature=None, act_dtype=act)
         else:
-            mixer = PagedAttention(qkv=Linear(qkv, p + "qkv"), out=Linear(o, p + "o"), num_heads=nq,
-                                   num_kv_heads=nkv, head_dim=d, mask="full", position=None, qk_norm=None,
+            mixer = PagedAttention(qkv=Linear(qkv, p + "qkv", bias=qkv_bias), out=Linear(o, p + "o", bias=o_bias),
+                                   num_heads=nq, num_kv_heads=nkv, head_dim=d, mask="full", position=None, qk_norm=None,
                                    temperature=(c.attn_scale, c.floor_scale) if c.attn_temperature_tuning else None,
                                    act_dtype=act)
         if c.layer_is_moe(i):

@@ -27,7 +27,8 @@ Adding a part: subclass the interface below, give it a ``kind`` name with
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from types import SimpleNamespace
+from typing import Any, Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -105,18 +106,48 @@ class StepContext:
     host_lengths: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
     max_rows_per_request: int = 0
-    max_context: int = 0                    # highest position + 1 over the step
+    max_context: int = 0                    # highest position + 1 over the step (an upper bound in a replayed graph)
     decode_only: bool = False               # every request brings exactly one row
-    # how attention kernels split the step's rows: tiles of up to 64 consecutive rows of one request
-    # (int32 [n, 4]: first row, rows, first position, request index) for portions of prompts, and a
-    # list of single rows (int32 [m]; None with num_decode_rows == num_tokens means "all rows")
-    attn_tiles: Optional[torch.Tensor] = None
-    num_attn_tiles: int = 0
-    attn_tile_rows: int = 64                # rows per tile: 128 when every attention layer takes the tcgen05 kernel
-    decode_rows: Optional[torch.Tensor] = None
-    num_decode_rows: int = 0
-    decode_keys: Optional[int] = None       # an upper bound on the sum of position + 1 over the single rows
+    # what the mixers' step planners made of this step, by planner key: the arrays as int32 device tensors
+    # (None where an array is empty) and the host-side values, as attributes (see StepPlanner)
+    plans: Dict[Hashable, SimpleNamespace] = field(default_factory=dict)
     extras: Dict[str, Any] = field(default_factory=dict)
+
+
+# ---------------------------------------------------------------------------------------
+# Per-step metadata that a kind of mixer brings along
+# ---------------------------------------------------------------------------------------
+@dataclass
+class StepPlanData:
+    """What a planner made of one step: int32 host arrays (any shape) that travel to the device in the
+    step's one metadata copy, and host-side values (counts, bounds) that the mixer's launches use."""
+
+    arrays: Dict[str, Any] = field(default_factory=dict)
+    values: Dict[str, Any] = field(default_factory=dict)
+
+
+class StepPlanner:
+    """How a kind of mixer cuts a step's rows for its kernels.
+
+    The step function knows requests, rows and block tables; how a mixer's kernels want the rows grouped
+    (tiles of a prompt portion, single rows, segments of a scan) is the mixer's business.  A mixer that needs
+    such metadata returns a planner from ``Mixer.step_planner(page_size)``.  Planners with equal ``key`` are
+    one planner: they run once per step and every mixer with that key reads ``ctx.plans[key]``.
+
+    ``plan(starts, lengths, bucket)`` gets, per request of the step, the position of its first row and its
+    number of rows (rows of all requests lie end to end).  For decode-only steps that are replayed as a CUDA
+    graph, ``bucket(starts, lengths)`` names what of the plan is baked into the graph (grid sizes, bounds):
+    steps with the same number of requests and the same bucket share a graph, and ``plan`` is then called
+    with that bucket and must return arrays of the same shapes, and values that hold for every such step.
+    """
+
+    key: Hashable = None
+
+    def plan(self, starts: Sequence[int], lengths: Sequence[int], bucket: Hashable = None) -> StepPlanData:
+        raise NotImplementedError
+
+    def bucket(self, starts: Sequence[int], lengths: Sequence[int]) -> Hashable:
+        return None
 
 
 # ---------------------------------------------------------------------------------------
@@ -147,6 +178,10 @@ class PositionEncoding(Part):
 class Mixer(Part):
     cache_spec: Optional[CacheSpec] = None
     state_spec: Optional[StateSpec] = None
+
+    def step_planner(self, page_size: int) -> Optional[StepPlanner]:
+        """The planner of this mixer's per-step metadata, or None if the step context is all it needs."""
+        return None
 
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

@@ -25,12 +25,18 @@ from ..kernels import ops
 
 
 class Linear:
-    """A weight ``[out, in]`` and the product with it.  Output is float32 ``[M, out]``."""
+    """A weight ``[out, in]``, an optional bias ``[out]`` (float32) and the product with them.  Output is
+    float32 ``[M, out]``.  The reference adds a projection's bias where a model stores one
+    (src/SharpInference.Core/ModelGraph.cs:269-270 probes for it)."""
 
-    def __init__(self, weight: torch.Tensor, name: str = "", stream_rows: int = 0):
+    def __init__(self, weight: torch.Tensor, name: str = "", stream_rows: int = 0,
+                 bias: Optional[torch.Tensor] = None):
         if weight.dim() != 2:
             raise ValueError(f"linear weight '{name}' must be 2-D, found shape {tuple(weight.shape)}")
+        if bias is not None and tuple(bias.shape) != (weight.shape[0],):
+            raise ValueError(f"bias of '{name}' has shape {tuple(bias.shape)}, expected ({weight.shape[0]},)")
         self.weight = weight
+        self.bias = bias
         self.name = name
         self.out_features, self.in_features = weight.shape
         self._use_library = (weight.dtype == torch.bfloat16 and self.in_features % 8 == 0)
@@ -53,18 +59,21 @@ class Linear:
         if w.dtype == torch.float32:
             if a.dtype != torch.float32:
                 a = a.to(torch.float32)
-            return ops.gemm_nt(a, w, out=out)
+            return ops.gemm_nt(a, w, out=out, bias=self.bias)
         if self._use_library and a.dtype == torch.bfloat16:
-            if a.shape[0] <= self.stream_rows:
-                return ops.tc_dense(a, w, out=out)
-            if out is not None:
-                return torch.mm(a, self._wt, out_dtype=torch.float32, out=out)
-            return torch.mm(a, self._wt, out_dtype=torch.float32)
-        return ops.gemm_nt(a, w, out=out)
+            if self.streams(a):
+                y = ops.tc_dense(a, w, out=out)
+            elif out is not None:
+                y = torch.mm(a, self._wt, out_dtype=torch.float32, out=out)
+            else:
+                y = torch.mm(a, self._wt, out_dtype=torch.float32)
+            return ops.add_bias(y, self.bias) if self.bias is not None else y
+        return ops.gemm_nt(a, w, out=out, bias=self.bias)
 
     def streams(self, a: torch.Tensor) -> bool:
         """Whether this product of ``a`` would run on the weight-streaming tensor-core kernel."""
-        return self._use_library and a.dtype == torch.bfloat16 and a.shape[0] <= self.stream_rows
+        return (self._use_library and self.bias is None and a.dtype == torch.bfloat16
+                and a.shape[0] <= self.stream_rows)
 
 
 class GroupedLinear:

@@ -24,11 +24,14 @@ class RMSNorm(Norm):
 
 @register_part("norm", "l2")
 class L2Norm(Norm):
-    """``x * rsqrt(mean(x^2) + eps)`` over the last axis, no weight.  The attention mixer runs it
-    fused with the rotation and the cache write; it has no launch of its own."""
+    """``x * rsqrt(mean(x^2) + eps)`` over the last axis, no weight.  As the q/k norm after a rotary encoding
+    the attention mixer runs it fused with the rotation and the cache write (``fuses_into_rotation``); anywhere
+    else it is a launch of its own like every norm."""
+
+    fuses_into_rotation = True
 
     def __init__(self, eps: float):
         self.eps = float(eps)
 
     def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
-        raise NotImplementedError("L2Norm is applied inside the attention mixer's fused kernel")
+        return ops.add_rmsnorm(x, delta, None, self.eps, out_dtype, rows=rows, want_fp32=want_fp32)

@@ -51,8 +51,8 @@ TINY_B = {
 }
 TINY_B_INIT = {"seed": 1, "std": 0.05, "norm_std": 0.0}
 
-# A third one with sizes that are no power of two anywhere, tied embeddings and the flag form of
-# no_rope_layers: hidden 88, 6 heads in 3 groups, head size 48, vocabulary 301.
+# A third one with sizes that are no power of two anywhere, tied embeddings, biased attention projections and
+# the flag form of no_rope_layers: hidden 88, 6 heads in 3 groups, head size 48, vocabulary 301.
 TINY_C = {
     "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
     "vocab_size": 301, "hidden_size": 88, "num_hidden_layers": 3, "num_attention_heads": 6,
@@ -63,7 +63,7 @@ TINY_C = {
                      "original_max_position_embeddings": 24},
     "no_rope_layers": [1, 0, 1], "attention_chunk_size": 24, "use_qk_norm": True, "qk_norm_eps": 1e-5,
     "attn_temperature_tuning": True, "floor_scale": 5, "attn_scale": 0.25, "rms_norm_eps": 1e-4,
-    "tie_word_embeddings": True,
+    "tie_word_embeddings": True, "attention_bias": True,
 }
 TINY_C_INIT = {"seed": 2, "std": 0.08, "norm_std": 0.2}
 
@@ -110,6 +110,29 @@ REAL_WIDTHS = {
                      "original_max_position_embeddings": 8192},
     "no_rope_layers": [1], "attention_chunk_size": 512, "use_qk_norm": True, "attn_temperature_tuning": True,
     "floor_scale": 512, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+
+
+# The mixtures of the large models at reduced width: 16 experts on every layer (Scout's count), and dense layers
+# alternating with layers of 128 experts (Maverick's arrangement); head size 128 in groups of five, pages of 64.
+EXPERTS_16 = dict(LARGE_SHAPES, num_hidden_layers=2, num_local_experts=16, intermediate_size=256, no_rope_layers=[1],
+                  interleave_moe_layer_step=1)
+EXPERTS_128 = dict(LARGE_SHAPES, num_hidden_layers=2, num_local_experts=128, intermediate_size=128,
+                   intermediate_size_mlp=768, no_rope_layers=[1], interleave_moe_layer_step=2)
+
+# The benchmark's own attention constants at a small width: chunks of 8192 positions, the temperature factor
+# stepping at 8192, the Scout rope scaling; a chunked rotary layer with a dense feed-forward, then a global layer
+# with 16 experts.  A request of 8300 tokens crosses the chunk's edge.
+CHUNK_EDGE = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "vocab_size": 500, "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 2,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 64, "intermediate_size_mlp": 128,
+    "num_local_experts": 16, "num_experts_per_tok": 1, "interleave_moe_layer_step": 2,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
+                     "original_max_position_embeddings": 8192},
+    "no_rope_layers": [1], "attention_chunk_size": 8192, "use_qk_norm": True, "attn_temperature_tuning": True,
+    "floor_scale": 8192, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
 }
 
 

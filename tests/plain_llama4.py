@@ -173,9 +173,13 @@ def attention_layer(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tens
     nq, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     d = cfg.get("head_dim") or cfg["hidden_size"] // nq
     S = h.shape[0]
-    q = (h @ w[p + "q_proj.weight"].T).reshape(S, nq, d)
-    k = (h @ w[p + "k_proj.weight"].T).reshape(S, nkv, d)
-    v = (h @ w[p + "v_proj.weight"].T).reshape(S, nkv, d)
+    bias = cfg.get("attention_bias", False)          # a bias where the model stores one (ModelGraph.cs:269-270)
+    q = h @ w[p + "q_proj.weight"].T
+    k = h @ w[p + "k_proj.weight"].T
+    v = h @ w[p + "v_proj.weight"].T
+    if bias:
+        q, k, v = q + w[p + "q_proj.bias"], k + w[p + "k_proj.bias"], v + w[p + "v_proj.bias"]
+    q, k, v = q.reshape(S, nq, d), k.reshape(S, nkv, d), v.reshape(S, nkv, d)
     rope = i not in nope_layers(cfg)
     if rope:
         q, k = apply_rope(q, positions, freqs), apply_rope(k, positions, freqs)
@@ -191,8 +195,10 @@ def attention_layer(cfg: dict, w: Dict[str, torch.Tensor], i: int, h: torch.Tens
         ok = visible("full", 0, S)
     if borrowed_kv is not None:
         k, v = borrowed_kv
-    o = attention_scores(q, k, v, ok)
-    return o @ w[p + "o_proj.weight"].T, (k, v)
+    o = attention_scores(q, k, v, ok) @ w[p + "o_proj.weight"].T
+    if bias:
+        o = o + w[p + "o_proj.bias"]
+    return o, (k, v)
 
 
 def silu(x: torch.Tensor) -> torch.Tensor:

@@ -94,10 +94,21 @@ def test_all_problems_in_one_error():
 
 @pytest.mark.parametrize("key,value", [("hidden_size", "64"), ("use_qk_norm", 1), ("rope_theta", "x"),
                                        ("no_rope_layers", [9]), ("moe_layers", [7]), ("attention_chunk_size", 0),
-                                       ("hidden_act", "gelu"), ("attention_bias", True)])
+                                       ("hidden_act", "gelu"), ("attention_bias", "yes")])
 def test_bad_values(key, value):
     with pytest.raises(ConfigError):
         Llama4TextConfig.from_dict(dict(TINY_A, **{key: value}))
+
+
+def test_attention_bias_declares_the_bias_tensors():
+    from sharpinference_b200.weights.loading import declared_tensors
+    c = Llama4TextConfig.from_dict(dict(TINY_A, attention_bias=True))
+    assert c.attention_bias and Llama4TextConfig.from_dict(c.to_dict()) == c
+    names = {d.name: d.shape for d in declared_tensors(get_architecture("Llama4ForCausalLM"), c)}
+    assert names["model.layers.0.self_attn.q_proj.bias"] == (64,) and names["model.layers.3.self_attn.k_proj.bias"] == (32,)
+    assert names["model.layers.1.self_attn.o_proj.bias"] == (64,)
+    plain = {d.name for d in declared_tensors(get_architecture("Llama4ForCausalLM"), Llama4TextConfig.from_dict(TINY_A))}
+    assert not any(n.endswith(".bias") for n in plain)
 
 
 def test_unsupported_rope_type():

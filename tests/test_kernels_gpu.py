@@ -797,3 +797,66 @@ def test_attention_prefill_tcgen05_far_key_and_edges(ops):
                 assert float(out[0, :64].float().abs().max()) < 10.0, (kind, pos, key)
             else:
                 assert float(out[0, :64].float().min()) > 40.0, (kind, pos, key)
+
+
+# ---------------------------------------------------------------------------------------
+# what another architecture's parts would need of the kernels: a bias, a weightless norm, a router that
+# weights its experts' outputs; and the path a kernel takes when one of its waits runs out
+# ---------------------------------------------------------------------------------------
+def test_weightless_norm_and_bias(ops):
+    x = rnd(21, 72, seed=1)
+    out, _ = ops.add_rmsnorm(x.clone(), None, None, 1e-5, torch.float32)
+    ref = x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-5)
+    assert torch.allclose(out.double(), ref, rtol=2e-6, atol=1e-6)
+    y, b = rnd(13, 301, seed=2), rnd(301, seed=3)
+    assert torch.equal(ops.add_bias(y.clone(), b), y + b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_nt_bias_and_row_scale(ops, dtype):
+    M, N, K = 45, 70, 52
+    a, w, bias, s = rnd(M, K, dtype=dtype, seed=1), rnd(N, K, dtype=dtype, seed=2), rnd(N, seed=3), rnd(M, seed=4)
+    out = ops.gemm_nt(a, w, bias=bias, row_scale=s)
+    ref = (a.double() @ w.double().T) * s.double()[:, None] + bias.double()
+    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4)
+    perm = torch.randperm(M, generator=torch.Generator().manual_seed(5)).to(torch.int32).to(DEV)
+    out2 = ops.gemm_nt(a, w, row_scale=s, scale_rows=perm)
+    assert torch.allclose(out2.double(), (a.double() @ w.double().T) * s.double()[perm.long()][:, None], rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("T,E,N,K,row_tile", [(8, 4, 256, 128, 16), (300, 5, 136, 264, 64), (2100, 3, 520, 128, 128),
+                                              (700, 3, 520, 128, 0), (3, 2, 384, 1024, 16)])
+def test_tc_grouped_gemm_store_weights_its_output_rows(ops, T, E, N, K, row_tile):
+    """MODE_STORE with a per-row factor: what a router that weights its experts' outputs needs."""
+    expert, order, offsets, a = grouped_case(T, E, K, seed=T + N)
+    w = rnd(E, N, K, dtype=torch.bfloat16, scale=0.1, seed=3)
+    scale = torch.rand(T, generator=torch.Generator().manual_seed(6)) + 0.5
+    sorted_rows = order.to(torch.int32).to(DEV)
+    ref = torch.stack([a[t].double() @ w[int(expert[t])].double().cpu().T * float(scale[t]) for t in range(T)])
+    base = rnd(T, N, seed=4)
+    acc = base.clone()
+    ops.tc_grouped_gemm(a[order].contiguous().to(DEV), w, offsets, mode=ops.TC_MODE_STORE, out=acc, out_rows=sorted_rows,
+                        accumulate=True, row_tile=row_tile, row_scale=scale.to(DEV), scale_rows=sorted_rows)
+    ops.check_status(DEV)
+    assert torch.allclose(acc.double().cpu(), base.double().cpu() + ref, rtol=1e-4, atol=1e-3)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(ops):
+    """The producer of one launch is told to stop after the first K block and every wait to give up after a few
+    thousand polls: the tensor-core warp's wait for the second block runs out, the kernel records the code and
+    returns (no fault, no hang), check_status raises it, and the next launch is right again."""
+    from sharpinference_b200.kernels.library import KernelError
+    expert, order, offsets, a = grouped_case(8, 2, 256, seed=11)
+    w = rnd(2, 128, 256, dtype=torch.bfloat16, scale=0.1, seed=3)
+    a_sorted = a[order].contiguous().to(DEV)
+    ops.check_status(DEV)
+    ops.tc_set_wait_test(1 << 12, 1)
+    ops.tc_grouped_gemm(a_sorted, w, offsets, mode=ops.TC_MODE_STORE, row_tile=16, k_split=1)
+    torch.cuda.synchronize()
+    with pytest.raises(KernelError, match="gave up"):
+        ops.check_status(DEV)
+    ops.check_status(DEV)                                            # the word is back at zero
+    out = ops.tc_grouped_gemm(a_sorted, w, offsets, mode=ops.TC_MODE_STORE, row_tile=16, k_split=1)
+    ops.check_status(DEV)
+    ref = torch.stack([a[t].double() @ w[int(expert[t])].double().cpu().T for t in order.tolist()])
+    assert torch.allclose(out.double().cpu(), ref, rtol=1e-4, atol=1e-3)

@@ -45,10 +45,25 @@ def test_decode_split_bound_is_tight_for_whole_chunks():
     assert ops.decode_splits(100, ops.MASK_WINDOW, 700) == 1
 
 
+def test_attention_planner_cuts_tiles_and_single_rows():
+    """Portions become tiles of the planner's size, short entries single rows; the plan of a decode-only step
+    has no arrays at all, so a replayed graph has nothing of it to refresh."""
+    from sharpinference_b200.parts.attention import PagedAttentionPlanner
+    p = PagedAttentionPlanner(64)
+    d = p.plan([100, 7, 0, 33], [150, 1, 4, 5])
+    assert d.arrays["tiles"].tolist() == [[0, 64, 100, 0], [64, 64, 164, 0], [128, 22, 228, 0], [155, 5, 33, 3]]
+    assert d.arrays["decode_rows"].tolist() == [150, 151, 152, 153, 154]
+    assert d.values == {"num_tiles": 4, "num_decode_rows": 5, "tile_rows": 64, "decode_keys": 8 + (1 + 2 + 3 + 4)}
+    d = p.plan([10, 20, 30], [1, 1, 1], bucket=p.bucket([10, 20, 30], [1, 1, 1]))
+    assert d.arrays["tiles"].shape == (0, 4) and d.arrays["decode_rows"].size == 0
+    assert d.values["num_decode_rows"] == 3 and d.values["decode_keys"] == p.keys_bucket(63, 3) >= 63
+    assert PagedAttentionPlanner(128).key != p.key
+
+
 def test_keys_bucket_of_a_captured_decode_step():
     """A replayed graph's attention launch is sized by the bucket: never below the keys, at most an eighth (or
     256 keys a row) above; a batch that gains a key a row each step changes bucket every 256 steps at most."""
-    from sharpinference_b200.engine.step import StepRunner
+    from sharpinference_b200.parts.attention import PagedAttentionPlanner as StepRunner
     for rows in (1, 3, 8, 64):
         for keys in list(range(rows, 3000, 7)) + [65080, 65536, 65537, 10 ** 6, 2 ** 31 - 5]:
             b = StepRunner.keys_bucket(keys, rows)

@@ -211,3 +211,86 @@ def test_linear_adds_into_its_output():
     alone = part.forward(None, h)
     added = part.forward(None, h, out=base.clone(), accumulate=True)
     assert torch.allclose(added, base + alone, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_with_a_bias(dtype):
+    from sharpinference_b200.parts import Linear
+    w, b, a = rnd(70, 96, scale=0.1, seed=1), rnd(70, seed=2), rnd(9, 96, seed=3)
+    if dtype == torch.bfloat16:
+        w, a = w.to(torch.bfloat16).float(), a.to(torch.bfloat16).float()
+    want = a.double() @ w.double().T + b.double()
+    for stream_rows in (0, 16):
+        lin = Linear(w.to(dtype).to(DEV), bias=b.to(DEV), stream_rows=stream_rows)
+        assert not lin.streams(a.to(dtype).to(DEV))                   # a biased product stays off the streaming kernel
+        assert torch.allclose(lin(a.to(dtype).to(DEV)).double().cpu(), want, rtol=1e-4, atol=1e-3)
+    with pytest.raises(ValueError, match="bias"):
+        Linear(w.to(DEV), bias=b[:5].to(DEV))
+
+
+def test_l2_norm_is_a_part_of_its_own():
+    from sharpinference_b200.parts import L2Norm
+    from sharpinference_b200.parts.base import make_part
+    x = rnd(17, 48, seed=4)
+    part = make_part("norm", "l2", eps=1e-5)
+    assert isinstance(part, L2Norm)
+    h, h32 = part.apply(x.to(DEV), None, rows=None, out_dtype=torch.bfloat16, want_fp32=True)
+    ref = plain.l2_norm(x.double(), 1e-5)
+    assert torch.allclose(h32.double().cpu(), ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(h.double().cpu(), ref, rtol=1e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("norm_kind", ["rmsnorm_first", "l2_first", "l2_no_position"])
+def test_attention_mixer_with_another_qk_norm(norm_kind, dtype):
+    """A weighted norm of q and k before the rotation (and the weightless one in places where it does not fuse
+    into the rotation kernel) is a norm part handed to the mixer: nothing in the mixer's kernels changes."""
+    from sharpinference_b200.parts import L2Norm, Linear, PagedAttention, RMSNorm, RotaryEncoding, rotary_inv_freq
+    H, nq, nkv, d, S = 64, 4, 2, 32, 40
+    wq, wk, wv, wo = (rnd(nq * d, H, scale=0.1, seed=4), rnd(nkv * d, H, scale=0.1, seed=5),
+                      rnd(nkv * d, H, scale=0.1, seed=6), rnd(H, nq * d, scale=0.1, seed=7))
+    if dtype == torch.bfloat16:
+        wq, wk, wv, wo = (t.to(torch.bfloat16).float() for t in (wq, wk, wv, wo))
+    inv_freq = rotary_inv_freq(d, 5000.0, None)
+    nw = 1 + 0.2 * rnd(d, seed=9)
+    if norm_kind == "rmsnorm_first":
+        norm, first, position = RMSNorm(nw.to(DEV), 1e-5), True, RotaryEncoding(inv_freq.to(DEV), "interleaved")
+    elif norm_kind == "l2_first":
+        norm, first, position = L2Norm(1e-5), True, RotaryEncoding(inv_freq.to(DEV), "interleaved")
+    else:
+        norm, first, position = L2Norm(1e-5), False, None
+    mixer = PagedAttention(qkv=Linear(torch.cat([wq, wk, wv]).to(dtype).to(DEV)), out=Linear(wo.to(dtype).to(DEV)),
+                           num_heads=nq, num_kv_heads=nkv, head_dim=d, mask="full", position=position,
+                           qk_norm=norm, qk_norm_first=first, act_dtype=dtype)
+    h = rnd(S, H, seed=8)
+    if dtype == torch.bfloat16:
+        h = h.to(torch.bfloat16).float()
+    cache, runner, StepEntry = context_for(mixer, None)
+    cache.add_request("a")
+    slot = cache.layer_slots()[0]
+    outs, at = [], 0
+    for n in (11, 1, 1, 20, 7):
+        cache.reserve([("a", n)])
+        ctx = runner.build_context([StepEntry("a", [0] * n, [])])
+        outs.append(mixer.forward(ctx, slot, h[at:at + n].to(dtype).to(DEV)).cpu())
+        cache.commit("a", n)
+        at += n
+    got = torch.cat(outs).double()
+    hd, pos = h.double(), torch.arange(S)
+    q = (hd @ wq.double().T).reshape(S, nq, d)
+    k = (hd @ wk.double().T).reshape(S, nkv, d)
+    v = (hd @ wv.double().T).reshape(S, nkv, d)
+    if norm_kind == "rmsnorm_first":
+        q, k = plain.l2_norm(q, 1e-5) * nw.double(), plain.l2_norm(k, 1e-5) * nw.double()
+    else:
+        q, k = plain.l2_norm(q, 1e-5), plain.l2_norm(k, 1e-5)
+    if position is not None:
+        q, k = plain.apply_rope(q, pos, inv_freq), plain.apply_rope(k, pos, inv_freq)
+    ref = plain.attention_scores(q, k, v, plain.visible("full", 0, S)) @ wo.double().T
+    err = float((got - ref).abs().max()) / float(ref.abs().max())
+    assert err < (2e-5 if dtype == torch.float32 else 2e-2), err
+    # the one combination that is not built says so
+    with pytest.raises(ValueError, match="qk_norm_first"):
+        PagedAttention(qkv=mixer.qkv, out=mixer.out, num_heads=nq, num_kv_heads=nkv, head_dim=d,
+                       position=RotaryEncoding(inv_freq.to(DEV), "interleaved"), qk_norm=RMSNorm(nw.to(DEV), 1e-5),
+                       act_dtype=dtype)

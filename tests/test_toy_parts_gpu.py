@@ -373,3 +373,144 @@ def test_schedule_is_validated():
         model.set_schedule([ScheduleEntry(0), ScheduleEntry(3, cache_from=0)])      # chunked against full
     with pytest.raises(ValueError, match="itself borrows"):
         model.set_schedule([ScheduleEntry(0), ScheduleEntry(1, cache_from=0), ScheduleEntry(2, cache_from=1)])
+
+
+# ---------------------------------------------------------------------------------------
+# a mixer that ships per-step metadata of its own and is replayed inside a captured decode graph
+# ---------------------------------------------------------------------------------------
+def define_prefix_toy():
+    """out_t = W . mean(h_0 .. h_t): a running sum per request in a state slot.  Within a step the sums are a
+    segmented prefix sum over the step's rows, for which the mixer needs to know, per row, where its request's
+    rows begin, and per request, which row is its last: metadata that its own planner adds to the step.  It
+    reads the step through device tensors only, so decode steps with it are captured and replayed."""
+    import numpy as np
+    from sharpinference_b200.models.model import DecoderModel
+    from sharpinference_b200.parts import DenseSwiGLU, Linear, PreNormBlock, RMSNorm
+    from sharpinference_b200.parts.base import Mixer, StateSpec, StepPlanData, StepPlanner, make_part, register_part
+    from sharpinference_b200.registry import register_architecture
+
+    class SegmentPlanner(StepPlanner):
+        key = "toy_segments"
+
+        def plan(self, starts, lengths, bucket=None):
+            first = np.cumsum([0] + list(lengths[:-1]))
+            return StepPlanData(arrays={"row_first": np.repeat(first, lengths), "last_row": first + np.asarray(lengths) - 1},
+                                values={"requests": len(lengths)})
+
+    @register_part("mixer", "toy_prefix_mean")
+    class PrefixMean(Mixer):
+        graph_safe = True
+
+        def __init__(self, *, weight, act_dtype):
+            self.weight, self.act_dtype = weight, act_dtype
+            self.state_spec = StateSpec((weight.shape[1],), torch.float32)
+            self.cache_spec = None
+
+        def step_planner(self, page_size):
+            return SegmentPlanner()
+
+        def forward(self, ctx, slot, h):
+            plan = ctx.plans["toy_segments"]
+            h32 = h.float()
+            run = torch.cumsum(h32, dim=0)
+            first = plan.row_first.long()
+            within = run - (run[first] - h32[first])                       # inclusive sums inside each request's rows
+            slots = ctx.state_slots.long()
+            total = slot.state[slots[ctx.row_request.long()]] + within
+            slot.state.index_copy_(0, slots, total[plan.last_row.long()])  # the state after the request's last row
+            mean = total / (ctx.positions.float() + 1.0)[:, None]
+            return mean @ self.weight.float().t()
+
+    @dataclass(frozen=True)
+    class PrefixToyConfig:
+        vocab_size: int = 41
+        hidden_size: int = 32
+        intermediate_size: int = 48
+        num_layers: int = 2
+        eps: float = 1e-5
+        architecture = "ToyPrefixForCausalLM"
+
+        @classmethod
+        def from_dict(cls, obj, where="config.json"):
+            return cls(**{k: obj[k] for k in cls.__dataclass_fields__ if k in obj})
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], **asdict(self)}
+
+    def build(c, weights):
+        act, H, I = weights.compute_dtype, c.hidden_size, c.intermediate_size
+        norm = lambda name: RMSNorm(weights.vector(name, (H,)), c.eps)
+        blocks = [PreNormBlock(mixer_norm=norm(f"l{i}.n1"), ffn_norm=norm(f"l{i}.n2"), act_dtype=act,
+                               mixer=make_part("mixer", "toy_prefix_mean", weight=weights.matrix(f"l{i}.mix.weight", (H, H)),
+                                               act_dtype=act),
+                               ffn=DenseSwiGLU(gate_up=Linear(weights.matrix(f"l{i}.gate_up.weight", (2 * I, H))),
+                                               down=Linear(weights.matrix(f"l{i}.down.weight", (H, I))), act_dtype=act))
+                  for i in range(c.num_layers)]
+        return DecoderModel(embedding=weights.matrix("embed.weight", (c.vocab_size, H)), blocks=blocks,
+                            final_norm=norm("final.weight"), head=Linear(weights.matrix("head.weight", (c.vocab_size, H))),
+                            act_dtype=act, config=c)
+
+    register_architecture("ToyPrefixForCausalLM", PrefixToyConfig, build)
+    return PrefixToyConfig
+
+
+def prefix_toy_plain(folder, toks):
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as fh:
+        c = json.load(fh)
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    I, S = c["intermediate_size"], len(toks)
+    x = w["embed.weight"][torch.tensor(toks)]
+    for i in range(c["num_layers"]):
+        h = plain.rms_norm(x, w[f"l{i}.n1"], c["eps"])
+        mean = torch.cumsum(h, 0) / torch.arange(1, S + 1, dtype=torch.float64)[:, None]
+        x = x + mean @ w[f"l{i}.mix.weight"].T
+        h = plain.rms_norm(x, w[f"l{i}.n2"], c["eps"])
+        gu = h @ w[f"l{i}.gate_up.weight"].T
+        x = x + (plain.silu(gu[:, :I]) * gu[:, I:]) @ w[f"l{i}.down.weight"].T
+    return plain.rms_norm(x, w["final.weight"], c["eps"]) @ w["head.weight"].T
+
+
+def test_toy_mixer_with_its_own_step_metadata_inside_a_decode_graph(tmp_path):
+    """The planner and the mixer are defined above, in this file: the step function ships the planner's arrays
+    without knowing what they mean, in eager steps and in the static buffer of a replayed graph alike."""
+    from sharpinference_b200 import Engine, EngineOptions, write_random_model
+    from sharpinference_b200.registry import unregister_architecture
+    Cfg = define_prefix_toy()
+    try:
+        folder = str(tmp_path / "prefix")
+        write_random_model(Cfg(), folder, seed=8, std=0.2, norm_std=0.1)
+        reqs = {f"p{i}": traces.random_tokens(41, n, seed=5 * n) for i, n in enumerate([50, 23, 61, 9])}
+        ref = {rid: prefix_toy_plain(folder, toks) for rid, toks in reqs.items()}
+        # every way of cutting, in 32-bit
+        for cut in (traces.whole, traces.portions, lambda r: traces.mixed(r, max_live=3), lambda r: traces.tail_decode(r, 32)):
+            eng = Engine(folder, dtype="float32", device=DEV, options=EngineOptions(page_size=16, max_cache_tokens=64, max_batch=3))
+            assert list(eng.runner.planners) == ["toy_segments"] and eng.runner.use_graphs and not eng.cache.groups
+            got = traces.replay(eng, cut(reqs))
+            err, where = traces.worst_error(got, ref)
+            assert err < 2e-5, (err, where)
+        assert eng.runner.graph_replays >= 3 * 28          # tail_decode: 32 single-token steps per request, replayed
+        # three requests decode together, then two, then one: graphs of three shapes, same numbers as eager steps
+        heads = {"p0": 20, "p1": 10, "p2": 5}
+        steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:n], "want": []} for r, n in heads.items()], "end": []}]
+        at, s = dict(heads), 0
+        while at:
+            s += 1
+            entries = [{"id": r, "tokens": [reqs[r][p]], "want": [0]} for r, p in at.items()]
+            at = {r: p + 1 for r, p in at.items()}
+            ended = [r for r, p in at.items() if p == len(reqs[r])]
+            steps.append({"step": s, "entries": entries, "end": ended})
+            for r in ended:
+                del at[r]
+        outs = {}
+        for graphs in (False, True):
+            eng = Engine(folder, dtype="float32", device=DEV,
+                         options=EngineOptions(page_size=16, max_cache_tokens=64, max_batch=3, cuda_graphs=graphs))
+            outs[graphs] = traces.replay(eng, steps)
+            assert (eng.runner.graph_replays > 40) == graphs
+        for key, row in outs[False].items():
+            assert torch.equal(row, outs[True][key]), key
+        err, where = traces.worst_error(outs[True], ref)
+        assert err < 2e-5, (err, where)
+    finally:
+        unregister_architecture("ToyPrefixForCausalLM")

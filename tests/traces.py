@@ -123,14 +123,15 @@ def drawn(requests: Dict[str, List[int]], seed: int, max_live: int = 4) -> List[
     return steps
 
 
-def max_tokens(steps: List[dict]) -> int:
-    """The most positions live requests hold at any time, each rounded up to a multiple of 64."""
+def max_tokens(steps: List[dict], page: int = PAGE_ROUND) -> int:
+    """The most positions live requests hold at any time, each rounded up to a multiple of ``page`` (64 is
+    what ``bin/trace_run`` is told; an engine with smaller pages can be given the smaller, exact figure)."""
     held: Dict[str, int] = {}
     most = 0
     for st in steps:
         for e in st["entries"]:
             held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
-        most = max(most, sum((n + PAGE_ROUND - 1) // PAGE_ROUND * PAGE_ROUND for n in held.values()))
+        most = max(most, sum((n + page - 1) // page * page for n in held.values()))
         for rid in st["end"]:
             held.pop(rid, None)
     return most
