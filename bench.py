@@ -8,7 +8,9 @@ One JSON line on standard output.  The default run has the layer sizes of Llama-
 random bfloat16 weights (20 layers), batch 8, context 8192.  ``value`` is decoded tokens per
 second of the step function plus sampling, timed with CUDA events; ``e2e`` is the same through
 ``Engine.step()`` with token ids going in from (pinned) host memory and sampled ids coming back to
-the host every step.  ``--impl reference`` reports that the reference cannot run here.
+the host every step.  ``--impl reference`` reports that the reference cannot run here.  Beside this file:
+``bench_timeline.py`` (where a step's time goes, from clock markers inside the replayed graph) and
+``bench_kernels.py`` (one kernel at model sizes).
 """
 from __future__ import annotations
 
@@ -132,7 +134,8 @@ def decode_bytes(cfg, batch, context, distinct_experts_per_layer, itemsize=2):
     return weights + cache
 
 
-def prefill_flops(cfg, tokens):
+def prefill_flops(cfg, tokens, start=0):
+    """Flops of a prompt portion of ``tokens`` rows whose first row is at position ``start`` (logits at one row)."""
     H, d, nq, nkv, I, V = (cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads,
                            cfg.intermediate_size, cfg.vocab_size)
     attention = 2 * H * (nq + 2 * nkv) * d + 2 * H * nq * d
@@ -140,12 +143,16 @@ def prefill_flops(cfg, tokens):
     dense = 2 * 3 * H * cfg.intermediate_size_mlp
     moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
     per_token = cfg.num_hidden_layers * attention + moe_layers * mixture + (cfg.num_hidden_layers - moe_layers) * dense
-    pairs = tokens * (tokens + 1) // 2               # causal (query, key) pairs within one chunk
-    attn = 4 * nq * d * pairs
-    return tokens * per_token + cfg.num_hidden_layers * attn + 2 * V * H
+    # (query, key) pairs: a global layer's query at position p sees p + 1 keys, a chunked layer's p % chunk + 1
+    C = cfg.attention_chunk_size
+    full_pairs = sum(p + 1 for p in range(start, start + tokens))
+    chunk_pairs = sum(p % C + 1 for p in range(start, start + tokens))
+    rope_layers, nope_layers = layer_counts(cfg)
+    attn = 4 * nq * d * (rope_layers * chunk_pairs + nope_layers * full_pairs)
+    return tokens * per_token + attn + 2 * V * H
 
 
-def prefill_floor_ms(cfg, tokens, pk):
+def prefill_floor_ms(cfg, tokens, pk, start=0):
     """The least time a prompt step can take at the peaks given: the routed experts' products at the slower
     of their flops and the bytes of the experts touched (at most one per token), everything else at its
     flops.  With 16 experts and 2048 tokens the routed products are bound by memory."""
@@ -155,7 +162,7 @@ def prefill_floor_ms(cfg, tokens, pk):
     flops_s, bytes_s = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
     routed = max(routed_flops / flops_s, routed_bytes / bytes_s)
     moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
-    rest = (prefill_flops(cfg, tokens) - moe_layers * routed_flops) / flops_s
+    rest = (prefill_flops(cfg, tokens, start) - moe_layers * routed_flops) / flops_s
     return (moe_layers * routed + rest) * 1e3
 
 
@@ -221,13 +228,27 @@ def long_context_run(ns, cfg, pk, pk_kind) -> int:
     torch.cuda.synchronize()
     t2 = time.perf_counter()
     timed_tokens = new_tokens - 1 - settle
+    dec_ms = (t2 - t1d) * 1e3 / timed_tokens
+    # the decode step's roofline: every weight it uses once (one expert a layer) and the request's cache at the
+    # middle of the timed stretch
+    mid_context = prompt_len + settle + timed_tokens // 2
+    moe_layers = sum(cfg.layer_is_moe(i) for i in range(cfg.num_hidden_layers))
+    need = decode_bytes(cfg, 1, mid_context, [1.0] * moe_layers)
+    achieved = need / (dec_ms * 1e-3) / 1e9
+    floor_ms = sum(prefill_floor_ms(cfg, portion, pk, start) for start in range(0, prompt_len, portion))
+    flops = sum(prefill_flops(cfg, portion, start) for start in range(0, prompt_len, portion))
     out = {
         "metric": "long context: prefill tok/s over a 65536-token prompt in 2048-token portions, then decode tok/s",
         "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
         "prefill": {"value": prompt_len / (t1 - t0), "unit": "tokens/s", "tokens": prompt_len, "portions": portions,
-                    "seconds": t1 - t0},
+                    "ms": (t1 - t0) * 1e3, "frac": flops / (t1 - t0) / (pk["bf16_tflops_sustained"] * 1e12),
+                    "peak_tflops": pk["bf16_tflops_sustained"], "peak": pk_kind + ", sustained (a seconds-long run)",
+                    "floor_ms": floor_ms, "frac_of_floor": floor_ms / ((t1 - t0) * 1e3)},
         "decode": {"value": timed_tokens / (t2 - t1d), "unit": "tokens/s", "tokens": timed_tokens,
-                   "ms_per_step": (t2 - t1d) * 1e3 / timed_tokens},
+                   "ms_per_step": dec_ms},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": need, "peak_kind": pk_kind,
+                     "context": mid_context},
         "cache": {"page_size": page, "chunk_group_pages_at_most": most_chunk_pages,
                   "chunk_group_positions_at_most": most_chunk_pages * page,
                   "global_group_pages_after_prefill": full_pages},
@@ -237,96 +258,6 @@ def long_context_run(ns, cfg, pk, pk_kind) -> int:
                    "prompt": prompt_len, "portion": portion, "new_tokens": new_tokens},
     }
     print(json.dumps(out))
-    return 0
-
-
-def timeline_run(ns, cfg) -> int:
-    """Where a decode step's time goes, measured inside the captured graph: every kernel wrapper and library
-    product of the step is bracketed by two marker kernels that write the GPU's clock; the table gives the
-    mean time between the markers per kind of call (a marker pair itself costs about 2 us, and calls on the
-    second stream overlap those on the first)."""
-    import collections
-
-    import torch
-
-    from sharpinference_b200 import Engine, EngineOptions, SamplingParams, StepEntry, build_random_model
-    from sharpinference_b200.kernels import ops
-    from sharpinference_b200.parts import linear as linear_mod
-
-    dev = torch.device("cuda:0")
-    B = ns.batch
-    model = build_random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
-    engine = Engine(model, dtype="bfloat16", device=dev,
-                    options=EngineOptions(page_size=64, max_cache_tokens=B * (ns.context + 128) + 256 + ns.prefill_tokens, max_batch=B + 1,
-                                          max_tokens_per_step=max(B, 64, ns.prefill_tokens)))
-    torch.manual_seed(0)
-    for g in engine.cache.groups:
-        g.kv.normal_(0.0, 1.0)
-    gen = torch.Generator().manual_seed(0)
-    greedy = SamplingParams(temperature=0.0, max_new_tokens=1 << 30)
-    ids = [inject_prefilled(engine, torch.randint(0, cfg.vocab_size, (ns.context - 20,), generator=gen).tolist(), greedy)
-           for _ in range(B)]
-    reqs = [engine.request(i) for i in ids]
-    slots = torch.zeros(8192, dtype=torch.int64, device=dev)
-    events, state = [], {"n": 0}
-
-    def bracket(name, fn):
-        def inner(*a, **k):
-            i = state["n"]
-            state["n"] += 2
-            ops.timestamp(slots, i)
-            r = fn(*a, **k)
-            ops.timestamp(slots, i + 1)
-            events.append((name, i, i + 1))
-            return r
-        return inner
-
-    for name in ("embed_gather", "add_rmsnorm", "swiglu", "qkv_post", "attention_decode", "router_top1",
-                 "gather_rows_bf16", "tc_grouped_gemm"):
-        setattr(ops, name, bracket(name, getattr(ops, name)))
-    plain_call = linear_mod.Linear.__call__
-    linear_mod.Linear.__call__ = lambda self, a, out=None, accumulate=False: bracket(
-        f"dense product [{self.out_features} x {self.in_features}]" + (" (own kernel)" if self.streams(a) else ""),
-        lambda: plain_call(self, a, out=out, accumulate=accumulate))()
-    last = [r.tokens[-1] for r in reqs]
-    per_step = []
-    for _ in range(6):                               # the first step runs eagerly, the second is captured, then replays
-        n0 = len(events)
-        logits = engine.forward_step([StepEntry(i, [t], [0]) for i, t in zip(ids, last)])
-        last = engine.sampler.sample(logits, [r.sampler for r in reqs])
-        per_step.append(events[n0:])
-    torch.cuda.synchronize()
-    t = slots.cpu().tolist()
-    captured = max(per_step[1:], key=len)            # the markers of the captured step hold the last replay's clocks
-    table = collections.OrderedDict()
-    for name, a, b in sorted(captured, key=lambda e: t[e[1]]):
-        table.setdefault(name, []).append((t[b] - t[a]) / 1e3)
-    first, final = min(t[a] for _, a, _ in captured), max(t[b] for _, _, b in captured)
-    print(f"decode step, batch {B}, context {ns.context}, {ns.layers} layers: {(final - first) / 1e3:.1f} us from the "
-          f"first marker to the last")
-    for name, v in table.items():
-        print(f"  {name:40s} calls {len(v):3d}   mean {sum(v) / len(v):7.1f} us   sum {sum(v):8.1f} us")
-
-    # a prompt portion (not captured: the host launches every kernel, and is ahead of the device after the first few)
-    for name in ("attention_prefill", "attention_prefill_tc"):
-        setattr(ops, name, bracket(name, getattr(ops, name)))
-    prompt = torch.randint(0, cfg.vocab_size, (ns.prefill_tokens,), generator=gen).tolist()
-    for _ in range(3):
-        n0 = len(events)
-        engine.open_request("p")
-        engine.forward_step([StepEntry("p", prompt, [len(prompt) - 1])])
-        engine.close_request("p")
-        torch.cuda.synchronize()
-        last_events = events[n0:]
-    t = slots.cpu().tolist()
-    table = collections.OrderedDict()
-    for name, a, b in sorted(last_events, key=lambda e: t[e[1]]):
-        table.setdefault(name, []).append((t[b] - t[a]) / 1e3)
-    first, final = min(t[a] for _, a, _ in last_events), max(t[b] for _, _, b in last_events)
-    print(f"prompt portion of {ns.prefill_tokens} tokens, {ns.layers} layers: {(final - first) / 1e3:.1f} us from the first "
-          f"marker to the last")
-    for name, v in table.items():
-        print(f"  {name:40s} calls {len(v):3d}   mean {sum(v) / len(v):7.1f} us   sum {sum(v):8.1f} us")
     return 0
 
 
@@ -346,9 +277,6 @@ def main() -> int:
                          "Maverick-sized layers (dense / 128 experts alternating), batch 64 at context 4096; long: 8 "
                          "Scout-sized layers, one 65536-token prompt prefilled in 2048-token portions, then 256 "
                          "decoded tokens")
-    ap.add_argument("--timeline", action="store_true",
-                    help="instead of the benchmark: a table of where one decode step's time goes, from clock "
-                         "markers inside the captured graph (use a few layers)")
     ns = ap.parse_args()
     if ns.preset == "maverick":
         defaults = ap.parse_args([])
@@ -379,8 +307,6 @@ def main() -> int:
     cfg = Llama4TextConfig.from_dict(dict(base, num_hidden_layers=ns.layers,
                                           no_rope_layers=[i for i in range(ns.layers) if (i + 1) % 4 == 0]))
     pk, pk_kind = peaks()
-    if ns.timeline:
-        return timeline_run(ns, cfg)
     if ns.preset == "long":
         return long_context_run(ns, cfg, pk, pk_kind)
     dev = torch.device("cuda:0")
@@ -485,6 +411,7 @@ def main() -> int:
         ms, distinct, _, _, launches = decode_run(ns.batch, steps, through_engine=False)
     clock_summary = clocks.summary()
     e2e_ms, _, h2d, d2h, _ = decode_run(ns.batch, steps, through_engine=True)
+    e2e_b1_ms = decode_run(1, max(3, steps // 2), through_engine=True)[0] if 1 in batches[1:] else None
     need = decode_bytes(cfg, ns.batch, ns.context, distinct)
     achieved = need / (ms * 1e-3) / 1e9
     points = {}
@@ -493,6 +420,8 @@ def main() -> int:
         points[f"decode_b{b}"] = b / pms * 1e3
         # the same roofline figure as for the headline batch: bytes the step has to read / its time / the peak
         points[f"decode_b{b}_roofline_frac"] = decode_bytes(cfg, b, ns.context, pdistinct) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"]
+    if e2e_b1_ms is not None:           # what the host adds at batch 1: the same steps through Engine.step()
+        points["decode_b1_e2e"] = 1 / e2e_b1_ms * 1e3
 
     out = {
         "metric": f"decode tok/s @ batch {ns.batch}, context {ns.context} "

@@ -1,23 +1,27 @@
 """Single-kernel timing at model sizes, for profiling one kernel without the model around it.
 
-    python -m sharpinference_b200.kernels.microbench tc_gemm --mode gate_up --rows 2048 --row-tile 128
-    python -m sharpinference_b200.kernels.microbench tc_gemm --mode down --rows 8
-    python -m sharpinference_b200.kernels.microbench attention_decode --batch 64 --context 8192
-    python -m sharpinference_b200.kernels.microbench attention_prefill --tokens 2048
+    python bench_kernels.py tc_gemm --mode gate_up --rows 2048 --row-tile 128
+    python bench_kernels.py tc_gemm --mode down --rows 8
+    python bench_kernels.py attention_decode --batch 64 --context 8192
+    python bench_kernels.py attention_prefill --tokens 2048
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
 the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
-cache at the default sizes.  Profiler captures name this module so that they run committed code only.
+cache at the default sizes.  Profiler captures name this file so that they run committed code only.  It is a measuring tool beside
+``bench.py``, not part of the package.
 """
 from __future__ import annotations
 
 import argparse
 import math
+import os
 import sys
 
 import torch
 
-from . import ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from sharpinference_b200.kernels import ops  # noqa: E402
 
 DEV = "cuda:0"
 

@@ -618,12 +618,20 @@ def test_abort_in_the_middle_of_a_prompt_and_the_pages_go_to_the_next_request(mo
     cfg, w = plain.load_folder(model_dirs[name])
     eng = Engine(model_dirs[name], dtype=dtype, device="cuda:0",
                  options=EngineOptions(page_size=8, max_cache_tokens=64, max_batch=2, max_tokens_per_step=24))
+    handed_out = {g.index: [] for g in eng.cache.groups}       # every page a group hands out, in order
+    for g in eng.cache.groups:
+        def noting(g=g, inner=g.pages.take):
+            handed_out[g.index].append(inner())
+            return handed_out[g.index][-1]
+        g.pages.take = noting
     long_prompt = traces.random_tokens(cfg["vocab_size"], 60, seed=5)
     a = eng.add_request(long_prompt, SamplingParams(temperature=0.0, max_new_tokens=4))
     eng.step()                                            # 24 of the 60 tokens
     assert eng.request(a).computed == 24 and not eng.request(a).generated
-    held = {g.index: {p for p in eng.cache.requests[a].tables[g.index] if p >= 0} for g in eng.cache.groups}
-    assert all(held.values())
+    held = {gi: set(pages) for gi, pages in handed_out.items()}     # written by the request that is aborted now
+    assert all(len(pages) == 3 for pages in held.values())
+    for pages in handed_out.values():
+        pages.clear()
     out = eng.abort(a)
     assert out.finish_reason == "abort" and not eng.cache.requests
     assert all(g.pages.held_count == 0 for g in eng.cache.groups)
@@ -631,7 +639,7 @@ def test_abort_in_the_middle_of_a_prompt_and_the_pages_go_to_the_next_request(mo
     sp = SamplingParams(temperature=0.0, max_new_tokens=8)
     b = eng.add_request(prompt, sp)
     eng.step()
-    reused = {g.index: {p for p in eng.cache.requests[b].tables[g.index] if p >= 0} & held[g.index] for g in eng.cache.groups}
+    reused = {gi: set(pages) & held[gi] for gi, pages in handed_out.items()}
     assert all(reused.values()), "the new request did not receive pages the aborted one had written"
     while eng.has_unfinished:
         eng.step()

@@ -24,7 +24,7 @@ def context_for(mixer, lengths_by_step, page_size=8, num_pages=32):
     blocks = [SimpleNamespace(mixer=mixer)]
     cache = CacheManager([ScheduleEntry(0)], blocks, page_size=page_size, num_pages=num_pages, max_requests=4,
                          dtype=mixer.act_dtype, device=DEV)
-    runner = StepRunner(SimpleNamespace(vocab_size=1 << 30), cache)
+    runner = StepRunner(SimpleNamespace(vocab_size=1 << 30, blocks=blocks), cache)
     return cache, runner, StepEntry
 
 
