@@ -73,7 +73,7 @@ def tc_gemm(ns) -> None:
         a = torch.empty(T, H, dtype=torch.bfloat16, device=DEV).normal_(0, 1, generator=g)
         scale = torch.rand(T, device=DEV, generator=g)
         fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_SWIGLU, row_scale=scale, row_tile=ns.row_tile,
-                                         k_split=ns.k_split)
+                                         k_split=ns.k_split, max_ctas=ns.max_ctas)
         weight_bytes, flops = used * 2 * I * H * 2, 2 * T * 2 * I * H
     else:
         w = torch.empty(E, H, I, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02, generator=g)
@@ -81,8 +81,31 @@ def tc_gemm(ns) -> None:
         out = torch.zeros(T, H, device=DEV)
         rows = torch.randperm(T, device=DEV).to(torch.int32)
         fn = lambda: ops.tc_grouped_gemm(a, w, offsets, mode=ops.TC_MODE_STORE, out=out, out_rows=rows, accumulate=True,
-                                         row_tile=ns.row_tile, k_split=ns.k_split)
+                                         row_tile=ns.row_tile, k_split=ns.k_split, max_ctas=ns.max_ctas)
         weight_bytes, flops = used * H * I * 2, 2 * T * H * I
+    if ns.beside:
+        # the library's dense product (rows x N x K, operands in L2 for the most part) on a second stream beside
+        # every launch: what a mixture layer's shared expert does while the routed experts stream their weights
+        M2, N2, K2 = (int(v) for v in ns.beside.split(","))
+        a2 = torch.randn(M2, K2, device=DEV).to(torch.bfloat16)
+        w2 = torch.randn(N2, K2, device=DEV).to(torch.bfloat16)
+        o2 = torch.empty(M2, N2, device=DEV)
+        side = torch.cuda.Stream()
+        dense = lambda: torch.mm(a2, w2.t(), out_dtype=torch.float32, out=o2)
+        alone_dense = _time(dense, ns.iters)
+        alone = _time(fn, ns.iters)
+        inner = fn
+
+        def fn():
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                for _ in range(ns.beside_count):
+                    dense()
+            inner()
+            main.wait_stream(side)
+        print(f"alone: grouped {alone * 1e3:.1f} us, dense {M2}x{N2}x{K2} {alone_dense * 1e3:.1f} us x {ns.beside_count} "
+              f"({2 * M2 * N2 * K2 / alone_dense / 1e9:.0f} TFLOP/s)")
     ms = _time(fn, ns.iters)
     print(f"tc_gemm {ns.mode} rows={T} experts={used}/{E} row_tile={ops.tc_row_tile(T, ops.TC_MODE_SWIGLU if ns.mode == "gate_up" else ops.TC_MODE_STORE, E) if ns.row_tile is None else ns.row_tile}: {ms * 1e3:.1f} us, "
           f"weights {weight_bytes / ms / 1e6:.0f} GB/s, {flops / ms / 1e9:.0f} TFLOP/s")
@@ -145,6 +168,9 @@ def main(argv=None) -> int:
     p.add_argument("--inter", type=int, default=8192)
     p.add_argument("--row-tile", type=int, default=None)
     p.add_argument("--k-split", type=int, default=None)
+    p.add_argument("--max-ctas", type=int, default=0, help="persistent kernel: at most this many SMs (0 = all)")
+    p.add_argument("--beside", default="", help="M,N,K of a library product launched on a second stream beside each call")
+    p.add_argument("--beside-count", type=int, default=1)
     p.add_argument("--skew", type=float, default=0.0,
                    help="0: equal groups; else expert e gets rows in proportion to (1 - skew)^e")
     p.set_defaults(fn=tc_gemm)

@@ -400,14 +400,15 @@ tc_grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 // Items go to CTAs round-robin; items next to each other share a group, so its activations stay in L2.
 // Each output element is still one accumulation over K in ascending order inside the tensor core.
 // ---------------------------------------------------------------------------------------
-constexpr int PS_W_STAGES = 4;
-constexpr int PS_A_SLOTS = 6;
+// Two shapes of the rings, both 224 KB: four weight stages and six activation slots when the kernel has every SM
+// (a CTA then needs 128 KB of weights in flight), five and four when it is given a part of the SMs and the rest
+// run another kernel beside it (fewer CTAs must keep the same memory stream going: 160 KB in flight each).
 constexpr int PS_W_BYTES = 2 * TC_BM * TC_BK * 2;   // two weight tiles: 32 KB
 constexpr int PS_A_BYTES = 128 * TC_BK * 2;         // 128 activation rows: 16 KB
 constexpr int PS_CHUNK = 256;                       // rows per item
 constexpr int PS_MAX_E = 256;                       // groups whose bounds fit the shared-memory table
 constexpr int PS_TABLE_BYTES = 2 * (PS_MAX_E + 1) * 4;
-constexpr int PS_SMEM = PS_W_STAGES * PS_W_BYTES + PS_A_SLOTS * PS_A_BYTES + 256 + PS_TABLE_BYTES;
+constexpr int PS_SMEM = 224 * 1024 + 256 + PS_TABLE_BYTES;
 static_assert(PS_SMEM <= 227 * 1024, "the persistent kernel's rings must fit one CTA");
 
 struct PsItem {
@@ -430,10 +431,12 @@ __device__ __forceinline__ PsItem ps_decode(int w, int& e, const int* first_s, c
 constexpr int PS_EPI_WARPS = 8;                     // two per quarter of the tensor-memory lanes
 constexpr int PS_THREADS = (PS_EPI_WARPS + 2) * 32;  // then the producer warp and the MMA warp
 
-template <int MODE>
+template <int MODE, int PS_W_STAGES, int PS_A_SLOTS>
 __global__ void __launch_bounds__(PS_THREADS, 1)
 tc_grouped_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                                   const TcGemmParams p) {
+    static_assert(PS_W_STAGES * PS_W_BYTES + PS_A_SLOTS * PS_A_BYTES == 224 * 1024, "the rings take 224 KB");
+    static_assert(PS_W_STAGES + PS_A_SLOTS + PS_W_STAGES + PS_A_SLOTS + 4 <= 31, "barriers and the slot fit 256 bytes");
     extern __shared__ __align__(1024) uint8_t ps_smem[];
     if (smem_u32(ps_smem) & 1023u) {             // the swizzled tiles need it; nothing has been set up yet
         if (threadIdx.x == 0) atomicExch(p.status, 6);
@@ -577,7 +580,7 @@ tc_grouped_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, con
                     mma_commit(&empty_w[ws]);         // free when these MMAs have read them
                     mma_commit(&empty_a[as]);
                     if (SUBS == 2) mma_commit(&empty_a[as1]);
-                    ws = (ws + 1) & (PS_W_STAGES - 1);
+                    ws = (ws + 1 == PS_W_STAGES) ? 0 : ws + 1;
                     pw ^= (ws == 0);
                     as += SUBS;
                     if (as >= PS_A_SLOTS) { as -= PS_A_SLOTS; pa ^= 1; }
@@ -647,9 +650,10 @@ tc_grouped_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, con
     }
 }
 
-template <int MODE>
+// `max_ctas` > 0 gives the kernel that many SMs at most (and the deeper weight ring); 0: every SM.
+template <int MODE, int WS, int AS>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const TcGemmParams& p, long long max_items,
-                             cudaStream_t stream) {
+                             int max_ctas, cudaStream_t stream) {
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -657,13 +661,14 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const
         if (cudaGetDevice(&dev) != cudaSuccess ||
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             return SHARPI_LAUNCH_FAILED;
-        if (cudaFuncSetAttribute(tc_grouped_gemm_persistent_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 PS_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(tc_grouped_gemm_persistent_kernel<MODE, WS, AS>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM) != cudaSuccess)
             return SHARPI_LAUNCH_FAILED;
         configured = true;
     }
-    const int grid = (int)(max_items < sms ? max_items : sms);
-    tc_grouped_gemm_persistent_kernel<MODE><<<grid, PS_THREADS, PS_SMEM, stream>>>(mw, ma, p);
+    long long grid = max_items < sms ? max_items : sms;
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    tc_grouped_gemm_persistent_kernel<MODE, WS, AS><<<(int)grid, PS_THREADS, PS_SMEM, stream>>>(mw, ma, p);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -702,13 +707,13 @@ SHARPI_API void sharpi_tc_set_wait_test(unsigned limit, int drop_from) {
 
 // A [rows, K] bf16 sorted by expert; W [E, N, K] bf16; see the file header for the two modes.
 // `row_tile` (16, 32, 64, 128 or 256) is the number of activation rows one CTA takes; 0 asks for the
-// persistent kernel (up to 256 groups, no K split).
+// persistent kernel (up to 256 groups, no K split), which `max_ctas` > 0 keeps to that many SMs.
 // `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch, and `tickets`, one zero int per tile of the
 // launch grid) cuts K over that many CTAs per tile.
 SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
                                       const int* out_rows, const float* row_scale, const int* scale_rows,
                                       int* status, float* partial, int* tickets, int rows, int N, int K, int E, int mode,
-                                      int row_tile, int accumulate, int k_split, cudaStream_t stream) {
+                                      int row_tile, int accumulate, int k_split, int max_ctas, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return SHARPI_OK;
     if (K <= 0 || E <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;          // TMA: rows 16-byte aligned
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return SHARPI_UNALIGNED;
@@ -733,8 +738,11 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
         if (k_split != 1 || E > PS_MAX_E || rows < 128) return SHARPI_BAD_ARGUMENT;
         const long long tiles = (mode == MODE_SWIGLU) ? (n_out + TC_BM - 1) / TC_BM : (N + 2 * TC_BM - 1) / (2 * TC_BM);
         const long long max_items = ((long long)rows / PS_CHUNK + (rows < E ? rows : E)) * tiles;
-        return mode == MODE_SWIGLU ? launch_persistent<MODE_SWIGLU>(mw, ma, p, max_items, stream)
-                                   : launch_persistent<MODE_STORE>(mw, ma, p, max_items, stream);
+        if (max_ctas > 0)
+            return mode == MODE_SWIGLU ? launch_persistent<MODE_SWIGLU, 5, 4>(mw, ma, p, max_items, max_ctas, stream)
+                                       : launch_persistent<MODE_STORE, 5, 4>(mw, ma, p, max_items, max_ctas, stream);
+        return mode == MODE_SWIGLU ? launch_persistent<MODE_SWIGLU, 4, 6>(mw, ma, p, max_items, 0, stream)
+                                   : launch_persistent<MODE_STORE, 4, 6>(mw, ma, p, max_items, 0, stream);
     }
     // two weight tiles per activation tile pay from about 2048 rows on (measured at 16 experts: 281 vs 315 us
     // at 2048 rows, 658 vs 719 us at 8192; below that the larger number of CTAs of single tiles wins)

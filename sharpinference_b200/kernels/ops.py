@@ -432,7 +432,7 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
                     out: Optional[torch.Tensor] = None, out_rows: Optional[torch.Tensor] = None,
                     row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
                     accumulate: bool = False, row_tile: Optional[int] = None,
-                    k_split: Optional[int] = None) -> torch.Tensor:
+                    k_split: Optional[int] = None, max_ctas: int = 0) -> torch.Tensor:
     """Per-expert products on the tensor cores.  ``a`` bfloat16 [rows, K] sorted by expert,
     ``w`` bfloat16 [E, N, K], ``group_offsets`` int32 [E + 1].
 
@@ -440,6 +440,7 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     ``s = row_scale[scale_rows[r] or r]`` when ``row_scale`` is given (a router that weights outputs), else 1.
     ``mode=TC_MODE_SWIGLU``: ``w`` holds gate rows then up rows (N = 2 I); bfloat16
     ``out[r] = silu(s g) * (s u)``, shape [rows, I], ``s = row_scale[scale_rows[r]]``.
+    ``max_ctas`` > 0 (persistent kernel only) keeps the launch to that many SMs, for running beside another kernel.
     """
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
@@ -468,7 +469,8 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     check(kernel("sharpi_tc_grouped_gemm")(a.data_ptr(), w.data_ptr(), group_offsets.data_ptr(), out.data_ptr(),
                                            _ptr(out_rows), _ptr(row_scale), _ptr(scale_rows), status.data_ptr(),
                                            _ptr(partial), _ptr(tickets), rows, N, K, E, mode, row_tile,
-                                           int(accumulate), k_split, _stream()), "sharpi_tc_grouped_gemm")
+                                           int(accumulate), k_split, int(max_ctas) if row_tile == TC_PERSISTENT else 0,
+                                           _stream()), "sharpi_tc_grouped_gemm")
     return out
 
 
