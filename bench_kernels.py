@@ -4,6 +4,7 @@
     python bench_kernels.py tc_gemm --mode down --rows 8
     python bench_kernels.py attention_decode --batch 64 --context 8192
     python bench_kernels.py attention_prefill --tokens 2048
+    python bench_kernels.py dense --rows 8 --n 7168 --k 5120 --impl grouped
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
 the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
@@ -111,6 +112,29 @@ def tc_gemm(ns) -> None:
           f"weights {weight_bytes / ms / 1e6:.0f} GB/s, {flops / ms / 1e9:.0f} TFLOP/s")
 
 
+def dense(ns) -> None:
+    """A dense product of a few rows: the grouped tensor-core kernel with one group, or the library.  The weights rotate through enough copies to exceed the L2 cache, as in a model of many layers."""
+    M, N, K = ns.rows, ns.n, ns.k
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    ws = [torch.empty(N, K, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02) for _ in range(copies)]
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV)
+    state = {"i": 0}
+
+    def fn():
+        w = ws[state["i"] % copies]
+        state["i"] += 1
+        if ns.impl == "grouped":
+            ops.tc_dense(a, w, swiglu=ns.swiglu, out=None if ns.swiglu else out)
+        else:
+            y = torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
+            if ns.swiglu:
+                ops.swiglu(y, torch.bfloat16)
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"dense {ns.impl} rows={M} N={N} K={K}{' swiglu' if ns.swiglu else ''}: {ms * 1e3:.1f} us, "
+          f"weights {N * K * 2 / ms / 1e6:.0f} GB/s")
+
+
 def _cache(batch: int, context: int, nkv: int, d: int, ps: int):
     blocks = (context + ps - 1) // ps
     pages = batch * blocks
@@ -174,6 +198,13 @@ def main(argv=None) -> int:
     p.add_argument("--skew", type=float, default=0.0,
                    help="0: equal groups; else expert e gets rows in proportion to (1 - skew)^e")
     p.set_defaults(fn=tc_gemm)
+    p = sub.add_parser("dense")
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--n", type=int, default=7168)
+    p.add_argument("--k", type=int, default=5120)
+    p.add_argument("--swiglu", action="store_true")
+    p.add_argument("--impl", choices=["grouped", "library"], default="grouped")
+    p.set_defaults(fn=dense)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)

@@ -860,3 +860,4 @@ def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(ops):
     ops.check_status(DEV)
     ref = torch.stack([a[t].double() @ w[int(expert[t])].double().cpu().T for t in order.tolist()])
     assert torch.allclose(out.double().cpu(), ref, rtol=1e-4, atol=1e-3)
+
