@@ -46,6 +46,30 @@ struct PrefillTcArgs {
     float scale_log2;
 };
 
+// Two fp32 operations in one instruction (sm_100 has packed f32x2 forms): the softmax warps are bound by the
+// instructions they issue, so the scale-and-subtract and the row sum take pairs of columns at a time.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 enum { ERR_Q = 11, ERR_K = 12, ERR_V = 13, ERR_S = 14, ERR_P = 15, ERR_O = 16, ERR_EMPTY = 17, ERR_ALIGN = 18 };
 
 template <int D>
@@ -254,17 +278,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // exp2(s * scale - m_ref): one fused multiply-add and one ex2 per score; a hidden score is -inf and
             // gives 0, also for a row that has seen no key yet (its reference stands in as 0)
             const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-            float l0 = 0.0f, l1 = 0.0f;
             uint32_t packed[TK / 2];
+            const uint64_t scale2 = pack2(scale, scale), neg_m2 = pack2(neg_m, neg_m);
+            uint64_t l2 = pack2(0.0f, 0.0f);
 #pragma unroll
             for (int c = 0; c < TK; c += 2) {
-                const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c]), scale, neg_m));
-                const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c + 1]), scale, neg_m));
-                l0 += e0;
-                l1 += e1;
+                float x0, x1;
+                unpack2(fma2(pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+                const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                l2 = add2(l2, pack2(e0, e1));
                 __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
                 packed[c / 2] = *reinterpret_cast<uint32_t*>(&pr);
             }
+            float l0, l1;
+            unpack2(l2, l0, l1);
             l_run += l0 + l1;
             // P may be overwritten once the MMAs that read the previous block's are done
             if (j >= 1 && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(a.status, ERR_P); ok = false; break; }
