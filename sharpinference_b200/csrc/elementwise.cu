@@ -55,7 +55,11 @@ constexpr int NORM_THREADS = 256;
 constexpr int NORM_UNROLL = 8;
 constexpr int NORM_CACHE_FLOATS = 12288;     // 48 KB
 
-template <typename TO, bool CACHED>
+// WIDE_ORDER: the sum of squares is formed in the order of add_rmsnorm_wide_kernel below (as if 1024 threads each
+// added their own elements and the block's tree were that of 32 warps), so that a row gives the same bits
+// whichever of the two kernels a step of its size takes: this thread stands for the virtual threads
+// t, t + 256, t + 512, t + 768.
+template <typename TO, bool CACHED, bool WIDE_ORDER>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
                    const int* __restrict__ rows, int H, TO* __restrict__ out, float* __restrict__ out32) {
@@ -68,6 +72,7 @@ add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __res
     const float* dr = delta ? delta + src : nullptr;
     const bool write_back = dr && !rows;
     float ss = 0.0f;
+    float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (int i0 = threadIdx.x; i0 < H; i0 += NORM_UNROLL * NORM_THREADS) {
         float v[NORM_UNROLL], d[NORM_UNROLL];
 #pragma unroll
@@ -83,11 +88,25 @@ add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __res
                 if (dr) v[k] += d[k];
                 if (write_back) xr[i] = v[k];
                 if (CACHED) row_s[i] = v[k];
-                ss += v[k] * v[k];
+                if (WIDE_ORDER) ss4[k & 3] += v[k] * v[k];
+                else ss += v[k] * v[k];
             }
         }
     }
-    ss = block_sum(ss, scratch);
+    if (WIDE_ORDER) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) ss4[a] = warp_sum(ss4[a]);
+        __syncthreads();
+        if (lane == 0) {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) scratch[warp + (NORM_THREADS / 32) * a] = ss4[a];   // virtual warp w + 8 a
+        }
+        __syncthreads();
+        ss = warp_sum(scratch[lane]);
+    } else {
+        ss = block_sum(ss, scratch);
+    }
     const float scale = 1.0f / sqrtf(ss / (float)H + eps);
     TO* orow = out + (size_t)t * H;
     float* o32 = out32 ? out32 + (size_t)t * H : nullptr;
@@ -116,14 +135,84 @@ add_rmsnorm_kernel(float* x, const float* __restrict__ delta, const float* __res
     }
 }
 
+// Rows of up to NORM_WIDE_THREADS * NORM_UNROLL elements: 1024 threads hold the whole row in registers, so every
+// load of the row, of the update and of the weight is issued before anything is used and the kernel is two trips to
+// memory long (a decode step runs this kernel two or three times a layer with one block per row: its latency, not
+// its bandwidth, is what counts there).  A thread adds its squares in ascending order of the index; the block's
+// tree is fixed by the block size, so a row's result does not depend on the batch.
+constexpr int NORM_WIDE_THREADS = 1024;
+constexpr int NORM_WIDE_ROWS = 128;       // steps of up to this many rows take it
+
+template <typename TO>
+__global__ void __launch_bounds__(NORM_WIDE_THREADS)
+add_rmsnorm_wide_kernel(float* x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
+                        const int* __restrict__ rows, int H, TO* __restrict__ out, float* __restrict__ out32) {
+    __shared__ float scratch[32];
+    // the weight is written by no kernel: it may be on its way before the kernel ahead has finished
+    float ww[NORM_UNROLL];
+#pragma unroll
+    for (int k = 0; k < NORM_UNROLL; ++k) {
+        const int i = threadIdx.x + k * NORM_WIDE_THREADS;
+        ww[k] = (i < H) ? (w ? w[i] : 1.0f) : 0.0f;
+    }
+    pdl_wait();
+    const int t = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[t] : t) * H;
+    float* xr = x + src;
+    const float* dr = delta ? delta + src : nullptr;
+    const bool write_back = dr && !rows;
+    float v[NORM_UNROLL], d[NORM_UNROLL];
+#pragma unroll
+    for (int k = 0; k < NORM_UNROLL; ++k) {
+        const int i = threadIdx.x + k * NORM_WIDE_THREADS;
+        v[k] = (i < H) ? xr[i] : 0.0f;
+        d[k] = (dr && i < H) ? dr[i] : 0.0f;
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NORM_UNROLL; ++k) {
+        const int i = threadIdx.x + k * NORM_WIDE_THREADS;
+        if (i < H) {
+            if (dr) v[k] += d[k];
+            if (write_back) xr[i] = v[k];
+            ss += v[k] * v[k];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)t * H;
+    float* o32 = out32 ? out32 + (size_t)t * H : nullptr;
+#pragma unroll
+    for (int k = 0; k < NORM_UNROLL; ++k) {
+        const int i = threadIdx.x + k * NORM_WIDE_THREADS;
+        if (i < H) {
+            const float y = v[k] * scale * ww[k];
+            orow[i] = from_float<TO>(y);
+            if (o32) o32[i] = y;
+        }
+    }
+}
+
 template <typename TO>
 static int launch_norm(float* x, const float* delta, const float* w, float eps, const int* rows, int T, int H, TO* out,
                        float* out32, cudaStream_t stream) {
+    if (H <= NORM_WIDE_THREADS * NORM_UNROLL) {
+        // few rows: latency counts (2.9 against 3.8 us at one row of 5120); many rows: bandwidth (33 against 49 us at
+        // 2048 rows); the two kernels add in the same order, so the choice does not show in the result
+        if (T <= NORM_WIDE_ROWS) {
+            auto kern = add_rmsnorm_wide_kernel<TO>;
+            SHARPI_LAUNCH_PDL(kern, T, NORM_WIDE_THREADS, 0, stream, x, delta, w, eps, rows, H, out, out32);
+        } else {
+            auto kern = add_rmsnorm_kernel<TO, true, true>;
+            SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, (size_t)H * sizeof(float), stream, x, delta, w, eps, rows, H, out, out32);
+        }
+        return SHARPI_OK;
+    }
     if (H <= NORM_CACHE_FLOATS) {
-        auto kern = add_rmsnorm_kernel<TO, true>;
+        auto kern = add_rmsnorm_kernel<TO, true, false>;
         SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, (size_t)H * sizeof(float), stream, x, delta, w, eps, rows, H, out, out32);
     } else {
-        auto kern = add_rmsnorm_kernel<TO, false>;
+        auto kern = add_rmsnorm_kernel<TO, false, false>;
         SHARPI_LAUNCH_PDL(kern, T, NORM_THREADS, 0, stream, x, delta, w, eps, rows, H, out, out32);
     }
     return SHARPI_OK;

@@ -818,3 +818,40 @@ def test_a_request_crosses_the_edge_of_a_chunk_of_8192(tmp_path_factory, dtype):
             scale = float(ref["long"].abs().max())
             gap = max(float((other[p] - ref["long"][p]).abs().max()) for p in after) / scale
             assert gap > 5 * TOL["bfloat16"], (change, gap)
+
+
+def test_a_part_that_raises_in_mid_step_leaves_a_usable_engine(model_dirs):
+    """A fault made on the host, inside the model: one layer's feed-forward raises once, in the middle of a step
+    whose pages are reserved and whose first layers have run.  Every request of that moment ends with the error,
+    their pages and slots come back, the captured graphs are dropped, and the same engine then generates what the
+    plain implementation generates."""
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams
+    name = "A"
+    cfg, w = plain.load_folder(model_dirs[name])
+    eng = Engine(model_dirs[name], dtype="float32", device="cuda:0",
+                 options=EngineOptions(page_size=8, max_cache_tokens=256, max_batch=3, max_tokens_per_step=32))
+    prompts = [traces.random_tokens(cfg["vocab_size"], n, seed=90 + n) for n in (9, 14, 30, 5)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=10)
+    ffn = eng.model.blocks[2].ffn
+    inner, calls = ffn.forward, {"n": 0}
+
+    def flaky(ctx, h, h32=None):
+        calls["n"] += 1
+        if calls["n"] == 7:                              # some decode step, after graphs were captured
+            raise RuntimeError("injected: this layer's feed-forward failed")
+        return inner(ctx, h, h32)
+
+    ffn.forward = flaky
+    eng.runner.use_graphs = False                        # every step passes through the part above
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.generate(prompts, sp)
+    assert isinstance(eng.last_error, RuntimeError) and eng.stats["failed_steps"] == 1
+    assert not eng.has_unfinished and not eng.cache.requests and not eng._requests
+    assert all(g.pages.held_count == 0 for g in eng.cache.groups) and eng.cache.state_slots.free_count == 3
+    eng.cache.check_invariants()
+    errors = [eng.output(i) for i in list(eng._finished)]
+    assert any(o.finish_reason == "error" and "injected" in o.error for o in errors)
+    ffn.forward = inner
+    eng.runner.use_graphs = True
+    assert eng.generate(prompts, sp) == [plain.generate_greedy(cfg, w, p, 10) for p in prompts]
+    assert eng.runner.graph_replays > 0

@@ -30,7 +30,7 @@ def test_embed_gather(ops, dtype):
     assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
 
 
-@pytest.mark.parametrize("H", [8, 1000, 5120])
+@pytest.mark.parametrize("H", [8, 1000, 5120, 8192, 9000, 20000])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(ops, H, out_dtype):
     T, eps = 37, 1e-5
@@ -53,11 +53,15 @@ def test_add_rmsnorm(ops, H, out_dtype):
     assert torch.equal(x3, x) and torch.allclose(out_rows, ref[rows.long()], rtol=2e-6, atol=1e-6)
 
 
-def test_rmsnorm_rows_do_not_depend_on_the_batch(ops):
-    x, w = rnd(64, 777, seed=4), 1 + 0.1 * rnd(777, seed=5)
+@pytest.mark.parametrize("H", [777, 5120, 8192, 9000])
+def test_rmsnorm_rows_do_not_depend_on_the_batch(ops, H):
+    """Steps of few rows take a kernel built for latency, steps of many rows one built for bandwidth; both add a
+    row's squares in the same order, so a row alone, among 64 and among 300 gives the same bits."""
+    x, w = rnd(300, H, seed=4), 1 + 0.1 * rnd(H, seed=5)
     full, _ = ops.add_rmsnorm(x.clone(), None, w, 1e-6, torch.float32)
+    some, _ = ops.add_rmsnorm(x[:64].clone(), None, w, 1e-6, torch.float32)
     one, _ = ops.add_rmsnorm(x[13:14].clone(), None, w, 1e-6, torch.float32)
-    assert torch.equal(full[13:14], one)
+    assert torch.equal(full[13:14], one) and torch.equal(full[:64], some)
 
 
 def test_swiglu_scales_before_the_nonlinearity(ops):
