@@ -4,10 +4,14 @@
 // page with TMA.  One CTA serves one query head and a tile of up to 128 consecutive rows of one
 // request; a softmax thread owns one row, so row maxima and sums need no shuffles.
 //
-//   warps 0-3  softmax: read S (tcgen05.ld), mask, exp2, row max / sum, write P (bf16, swizzled) to
-//              shared memory; at the end read O, divide by the row sum, store
-//   warp 4     TMA producer: Q once, then K and V blocks of 64 keys through the block table
-//   warp 5     allocates tensor memory, issues the MMAs: S[j] = Q K_j^T, then O += P[j-1] V[j-1]
+//   warps 0-7  softmax, two threads to a query row (warps w and w + 4 share the rows 32 (w % 4) ..): both read the
+//              row's 64 scores of a block for the maximum; each masks, exponentiates, sums and writes P (bf16,
+//              swizzled) for its half of the keys; at the end each reads its half of O's columns, divides by
+//              the row sum, stores.  Eight softmax warps a CTA, sixteen an SM: the kernel is bound by the
+//              latencies inside a softmax warp (load, maximum, exponentials, store, barrier), not by a unit, so
+//              what counts is how many such warps a scheduler can choose from
+//   warp 8     TMA producer: Q once, then K and V blocks of 64 keys through the block table
+//   warp 9     allocates tensor memory, issues the MMAs: S[j] = Q K_j^T, then O += P[j-1] V[j-1]
 //
 // O accumulates in tensor memory over all key blocks.  The exponentials of a row are taken against a
 // reference maximum that is only raised when the row's running maximum has grown by more than 2^8
@@ -34,7 +38,8 @@ using namespace sm100;
 
 constexpr int TQ = 128;        // query rows per CTA (MMA M)
 constexpr int TK = 64;         // keys per block
-constexpr int TC_ATT_THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;
+constexpr int TC_ATT_THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int KV_STAGES = 2;
 
 struct PrefillTcArgs {
@@ -132,11 +137,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(p_full, 128);
+        mbar_init(p_full, SOFTMAX_WARPS * 32);
         mbar_init(pv_done, 1);
         fence_barrier_init();
     }
-    if (warp == 5) {
+    if (warp == SOFTMAX_WARPS + 1) {
         tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
         tmem_relinquish();
     }
@@ -145,7 +150,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == SOFTMAX_WARPS) {
         // ---- TMA producer ----------------------------------------------------------------------
         if (lane == 0) {
             prefetch_tensormap(&q_map);
@@ -177,7 +182,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tma_load_2d(v_s + st * Cfg::KV_BYTES + hf * TK * 128, &kv_map, &v_full[st], hf * 64, row_v);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == SOFTMAX_WARPS + 1) {
         // ---- MMA issuer ------------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t idesc_qk = instr_desc_bf16(TQ, TK);
@@ -217,52 +222,77 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (ok) pv(n_blocks - 1);
         }
     } else {
-        // ---- softmax: thread = query row ---------------------------------------------------------
-        const int r = warp * 32 + lane;
+        // ---- softmax: two threads to a query row ---------------------------------------------------
+        constexpr int HALF = TK / 2;                         // keys of a block per thread
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;
         const int pos_r = p0 + r;
         const int lo_r = visible_lo(pos_r, a.mask_kind, a.mask_span);
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr float RAISE = 8.0f;       // in log2 units: the reference maximum lags by at most this much
         const float scale = a.scale_log2;   // > 0: the maximum of the raw scores is the maximum of the scaled ones
-        float m_ref = -INFINITY, l_run = 0.0f;      // m_ref in log2 units
+        float m_ref = -INFINITY, l_run = 0.0f;      // m_ref in log2 units; l_run: this thread's half of the row sum
         bool ok = true;
 
         for (int j = 0; j < n_blocks; ++j) {
             const int b = j & 1;
             if (!mbar_wait(&s_full[b], (j >> 1) & 1)) { atomicExch(a.status, ERR_S); ok = false; break; }
             tcgen05_fence_after();
-            uint32_t sv[TK];
-            tmem_ld_32_nowait(lane_addr + Cfg::S_COL + b * TK, sv);
-            tmem_ld_32_nowait(lane_addr + Cfg::S_COL + b * TK + 32, sv + 32);
-            tmem_ld_wait();
             const int key0 = (kb_first + j) * TK;
-            if (!(key0 + TK - 1 <= pos_r && key0 >= lo_r)) {        // some keys of the block are hidden from this row
+            const bool hidden = !(key0 + TK - 1 <= pos_r && key0 >= lo_r);   // some keys of the block are hidden from this row
+            // the other half's scores first, for the maximum alone; then this thread's own, which it keeps
+            uint32_t sv[HALF];
+            tmem_ld_32_nowait(lane_addr + Cfg::S_COL + b * TK + (1 - half) * HALF, sv);
+            tmem_ld_wait();
+            if (hidden) {
 #pragma unroll
-                for (int c = 0; c < TK; ++c) {
-                    const int key = key0 + c;
-                    if (!(key <= pos_r && key >= lo_r)) sv[c] = 0xff800000u;    // -inf: its exponential is 0
+                for (int c = 0; c < HALF; ++c) {
+                    const int key = key0 + (1 - half) * HALF + c;
+                    if (!(key <= pos_r && key >= lo_r)) sv[c] = 0xff800000u;    // -inf
                 }
             }
             float m0 = fmax3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
             float m1 = fmax3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
 #pragma unroll
-            for (int c = 6; c + 3 < TK; c += 4) {
+            for (int c = 6; c + 3 < HALF; c += 4) {
                 m0 = fmax3(m0, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
                 m1 = fmax3(m1, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
             }
-            const float m_blk = fmax3(m0, m1, fmaxf(__uint_as_float(sv[TK - 2]), __uint_as_float(sv[TK - 1]))) * scale;
+            const float m_other = fmax3(m0, m1, fmaxf(__uint_as_float(sv[HALF - 2]), __uint_as_float(sv[HALF - 1])));
+            auto load_own = [&]() {
+                tmem_ld_32_nowait(lane_addr + Cfg::S_COL + b * TK + half * HALF, sv);
+                tmem_ld_wait();
+                if (hidden) {
+#pragma unroll
+                    for (int c = 0; c < HALF; ++c) {
+                        const int key = key0 + half * HALF + c;
+                        if (!(key <= pos_r && key >= lo_r)) sv[c] = 0xff800000u;    // -inf: its exponential is 0
+                    }
+                }
+            };
+            load_own();
+            m0 = fmax3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
+            m1 = fmax3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
+#pragma unroll
+            for (int c = 6; c + 3 < HALF; c += 4) {
+                m0 = fmax3(m0, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+                m1 = fmax3(m1, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
+            }
+            const float m_mine = fmax3(m0, m1, fmaxf(__uint_as_float(sv[HALF - 2]), __uint_as_float(sv[HALF - 1])));
+            const float m_blk = fmaxf(m_mine, m_other) * scale;      // the same number in both threads of the row
             // raise the reference maximum only when this block's maximum is far above it; the rows of a warp
-            // share the decision to touch O, each row uses its own factor
+            // share the decision to touch O (and the row's two warps decide alike), each row uses its own factor
             const bool raise = m_blk > m_ref + RAISE;               // also true for the row's first visible block
             if (__any_sync(0xffffffffu, raise)) {
                 const float m_new = fmaxf(m_ref, m_blk);
                 const float factor = (m_ref == -INFINITY) ? 0.0f : exp2f(m_ref - m_new);   // nothing of value in O yet
                 if (j > 0) {
-                    // O holds the sums of blocks 0 .. j-1 once the PV of block j-1 is complete
+                    // O holds the sums of blocks 0 .. j-1 once the PV of block j-1 is complete; this thread
+                    // rescales its half of the row's columns
                     if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(a.status, ERR_O); ok = false; break; }
                     tcgen05_fence_after();
 #pragma unroll
-                    for (int c0 = 0; c0 < D; c0 += 32) {
+                    for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                         uint32_t v[32];
                         tmem_ld_32_nowait(lane_addr + Cfg::O_COL + c0, v);
                         tmem_ld_wait();
@@ -271,6 +301,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         tmem_st_32(lane_addr + Cfg::O_COL + c0, v);
                     }
                     tmem_st_wait();
+                    load_own();          // the scores again: they need not live in registers across the rescaling
                 }
                 l_run *= factor;
                 m_ref = m_new;
@@ -278,11 +309,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // exp2(s * scale - m_ref): one fused multiply-add and one ex2 per score; a hidden score is -inf and
             // gives 0, also for a row that has seen no key yet (its reference stands in as 0)
             const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-            uint32_t packed[TK / 2];
+            uint32_t packed[HALF / 2];
             const uint64_t scale2 = pack2(scale, scale), neg_m2 = pack2(neg_m, neg_m);
             uint64_t l2 = pack2(0.0f, 0.0f);
 #pragma unroll
-            for (int c = 0; c < TK; c += 2) {
+            for (int c = 0; c < HALF; c += 2) {
                 float x0, x1;
                 unpack2(fma2(pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
                 const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
@@ -297,20 +328,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (j >= 1 && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(a.status, ERR_P); ok = false; break; }
             uint8_t* prow = p_s + r * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
+            for (int ch = 0; ch < 4; ++ch)
+                *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (r & 7)) << 4)) =
                     make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
             fence_proxy_async();
             tcgen05_fence_before();
             mbar_arrive(p_full);
         }
         if (ok && !mbar_wait(pv_done, (n_blocks - 1) & 1)) { atomicExch(a.status, ERR_O); ok = false; }
+        // the row sum: the two halves meet in the P buffer, which nothing reads any more (every softmax thread
+        // comes here, whatever its waits said, so the barrier is complete)
+        float* l_s = reinterpret_cast<float*>(p_s);
+        l_s[half * TQ + r] = l_run;
+        named_barrier_all(1, SOFTMAX_WARPS * 32, true);
+        const float l_row = l_s[r] + l_s[TQ + r];          // the same order in both threads
         if (ok) {
             tcgen05_fence_after();
-            const float inv = 1.0f / l_run;
+            const float inv = 1.0f / l_row;
             bf16* dst = a.out + ((size_t)(row0 + r) * a.nq + head) * D;
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld_32_nowait(lane_addr + Cfg::O_COL + c0, v);      // whole-warp operation: all rows take part
                 tmem_ld_wait();
@@ -332,7 +369,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == SOFTMAX_WARPS + 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }

@@ -39,7 +39,7 @@ def expected(model_dirs):
     return out
 
 
-def plain_under_engine_routing(model_dir, reqs, routing, dtype=torch.float64):
+def plain_under_engine_routing(model_dir, reqs, routing, dtype=torch.float64, margin=MARGIN):
     """Plain logits per request with the engine's expert choices imposed; asserts near-ties."""
     cfg, w = plain.load_folder(model_dir, dtype)
     ref, flips = {}, 0
@@ -47,9 +47,21 @@ def plain_under_engine_routing(model_dir, reqs, routing, dtype=torch.float64):
         margins = []
         ref[rid] = plain.forward(cfg, w, toks, forced=routing.get(rid), margins=margins)
         for layer in margins:
-            assert max(layer, default=0.0) < MARGIN, f"request {rid}: an expert choice differs beyond a near-tie"
+            assert max(layer, default=0.0) < margin, f"request {rid}: an expert choice differs beyond a near-tie"
             flips += sum(m > 0 for m in layer)
     return ref, flips
+
+
+def near_tie_margin(model_dir):
+    """What counts as a near-tie of two gate values at a model's own scale.  A gate is the sigmoid of a router
+    logit, whose slope is at most 1/4; the router's input has unit mean square, so its logits are of the size of
+    a router row's norm; and the engine's bfloat16 logits are held to TOL of their scale everywhere else.  So two
+    gates closer than TOL / 4 of a router row's norm are closer than the engine can tell apart.  For the tiny
+    models that is less than MARGIN, which stays their bound; at the large models' width (rows of 5120 weights of
+    0.02: norm 1.43) it is 7e-3, and choices that differ by up to 6e-3 do occur there."""
+    cfg, w = plain.load_folder(model_dir, torch.float32)
+    rows = [float(t.norm(dim=1).mean()) for name, t in w.items() if name.endswith("feed_forward.router.weight")]
+    return max(MARGIN, 0.25 * TOL["bfloat16"] * max(rows, default=0.0))
 
 
 def make_engine(model_dir, dtype, max_tokens, page_size=16):
@@ -139,7 +151,7 @@ def test_layer_widths_of_the_large_models(real_widths, cut):
                     options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8))
     routing = {}
     got = traces.replay(engine, steps, routing)
-    ref, flips = plain_under_engine_routing(folder, reqs, routing, dtype=torch.float32)
+    ref, flips = plain_under_engine_routing(folder, reqs, routing, dtype=torch.float32, margin=near_tie_margin(folder))
     err, where = traces.worst_error(got, ref)
     print(f"real widths {cut}: worst relative error {err:.3e} at {where}; near-tie expert choices: {flips}")
     assert err < TOL["bfloat16"], f"worst error {err:.3e} at {where}"
@@ -726,7 +738,7 @@ def test_layer_widths_of_the_large_models_whole_and_in_portions(real_widths, cut
                     options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8))
     routing = {}
     got = traces.replay(engine, steps, routing)
-    ref, flips = plain_under_engine_routing(folder, reqs, routing, dtype=torch.float32)
+    ref, flips = plain_under_engine_routing(folder, reqs, routing, dtype=torch.float32, margin=near_tie_margin(folder))
     err, where = traces.worst_error(got, ref)
     print(f"real widths {cut}: worst relative error {err:.3e} at {where}; near-tie expert choices: {flips}")
     assert err < TOL["bfloat16"], f"worst error {err:.3e} at {where}"
