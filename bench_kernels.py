@@ -228,7 +228,7 @@ def main(argv=None) -> int:
     global USE_GRAPH
     USE_GRAPH = ns.graph
     if not torch.cuda.is_available():
-        print("microbench needs a CUDA device", file=sys.stderr)
+        print("bench_kernels.py needs a CUDA device", file=sys.stderr)
         return 2
     ns.fn(ns)
     return 0

@@ -63,7 +63,7 @@ def test_attention_planner_cuts_tiles_and_single_rows():
 def test_keys_bucket_of_a_captured_decode_step():
     """A replayed graph's attention launch is sized by the bucket: never below the keys, at most an eighth (or
     256 keys a row) above; a batch that gains a key a row each step changes bucket every 256 steps at most."""
-    from sharpinference_b200.parts.attention import PagedAttentionPlanner as StepRunner
+    from sharpinference_b200.parts.attention import PagedAttentionPlanner as StepRunner    # the bucket is the planner's
     for rows in (1, 3, 8, 64):
         for keys in list(range(rows, 3000, 7)) + [65080, 65536, 65537, 10 ** 6, 2 ** 31 - 5]:
             b = StepRunner.keys_bucket(keys, rows)
