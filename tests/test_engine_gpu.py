@@ -867,3 +867,19 @@ def test_a_part_that_raises_in_mid_step_leaves_a_usable_engine(model_dirs):
     eng.runner.use_graphs = True
     assert eng.generate(prompts, sp) == [plain.generate_greedy(cfg, w, p, 10) for p in prompts]
     assert eng.runner.graph_replays > 0
+
+
+def test_cache_sized_from_free_memory_by_each_groups_needs(model_dirs):
+    """Without max_cache_tokens the pool is sized from the device's free memory: the chunked group for max_batch
+    requests of a chunk plus a step, the global group with the rest."""
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams
+    name = "B"
+    cfg, w = plain.load_folder(model_dirs[name])
+    eng = Engine(model_dirs[name], dtype="bfloat16", device="cuda:0",
+                 options=EngineOptions(page_size=16, max_batch=4, max_tokens_per_step=64, memory_fraction=0.001))
+    groups = {g.spec.kind: g for g in eng.cache.groups}
+    assert groups["chunk"].pages.capacity == 4 * (32 + 64 + 16) // 16
+    assert groups["full"].pages.capacity > 50 * groups["chunk"].pages.capacity
+    prompt = traces.random_tokens(cfg["vocab_size"], 90, seed=12)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=5)
+    same_or_near_tie(cfg, w, prompt, eng.generate([prompt], sp)[0], plain.generate_greedy(cfg, w, prompt, 5), sp)
