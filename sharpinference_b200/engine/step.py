@@ -297,6 +297,7 @@ class StepRunner:
         the static buffers of the others describe requests that are gone)."""
         self._graphs.clear()
         self._graph_seen.clear()
+        self._graph_pool = None          # the pool goes with its last graph; the next capture makes a new one
 
     def reset_after_failure(self) -> None:
         """After a step that raised: no graph is trusted any more, and the kernels' status word and the

@@ -844,12 +844,14 @@ def test_a_part_that_raises_in_mid_step_leaves_a_usable_engine(model_dirs):
                  options=EngineOptions(page_size=8, max_cache_tokens=256, max_batch=3, max_tokens_per_step=32))
     prompts = [traces.random_tokens(cfg["vocab_size"], n, seed=90 + n) for n in (9, 14, 30, 5)]
     sp = SamplingParams(temperature=0.0, max_new_tokens=10)
+    want = [plain.generate_greedy(cfg, w, p, 10) for p in prompts]
+    assert eng.generate(prompts, sp) == want and eng.runner.graph_replays > 0 and eng.runner._graphs
     ffn = eng.model.blocks[2].ffn
     inner, calls = ffn.forward, {"n": 0}
 
     def flaky(ctx, h, h32=None):
         calls["n"] += 1
-        if calls["n"] == 7:                              # some decode step, after graphs were captured
+        if calls["n"] == 7:                              # some decode step
             raise RuntimeError("injected: this layer's feed-forward failed")
         return inner(ctx, h, h32)
 
@@ -857,6 +859,7 @@ def test_a_part_that_raises_in_mid_step_leaves_a_usable_engine(model_dirs):
     eng.runner.use_graphs = False                        # every step passes through the part above
     with pytest.raises(RuntimeError, match="injected"):
         eng.generate(prompts, sp)
+    assert not eng.runner._graphs                        # the graphs captured before the failure are gone
     assert isinstance(eng.last_error, RuntimeError) and eng.stats["failed_steps"] == 1
     assert not eng.has_unfinished and not eng.cache.requests and not eng._requests
     assert all(g.pages.held_count == 0 for g in eng.cache.groups) and eng.cache.state_slots.free_count == 3
@@ -865,8 +868,9 @@ def test_a_part_that_raises_in_mid_step_leaves_a_usable_engine(model_dirs):
     assert any(o.finish_reason == "error" and "injected" in o.error for o in errors)
     ffn.forward = inner
     eng.runner.use_graphs = True
-    assert eng.generate(prompts, sp) == [plain.generate_greedy(cfg, w, p, 10) for p in prompts]
-    assert eng.runner.graph_replays > 0
+    before = eng.runner.graph_replays
+    assert eng.generate(prompts, sp) == want             # captured anew, in a new pool
+    assert eng.runner.graph_replays > before and eng.runner._graphs
 
 
 def test_cache_sized_from_free_memory_by_each_groups_needs(model_dirs):
