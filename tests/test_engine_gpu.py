@@ -887,3 +887,36 @@ def test_cache_sized_from_free_memory_by_each_groups_needs(model_dirs):
     prompt = traces.random_tokens(cfg["vocab_size"], 90, seed=12)
     sp = SamplingParams(temperature=0.0, max_new_tokens=5)
     same_or_near_tie(cfg, w, prompt, eng.generate([prompt], sp)[0], plain.generate_greedy(cfg, w, prompt, 5), sp)
+
+
+def test_captured_graphs_are_evicted_and_captured_again(model_dirs):
+    """Room for two graphs only, while the batch shrinks and grows: graphs are dropped oldest first and captured
+    again when their shape returns; the logits stay those of eager steps."""
+    from sharpinference_b200 import Engine, EngineOptions
+    name = "A"
+    cfg, w = plain.load_folder(model_dirs[name])
+    reqs = {f"e{i}": traces.random_tokens(cfg["vocab_size"], 60, seed=200 + i) for i in range(3)}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:6], "want": []} for r, t in reqs.items()], "end": []}]
+    at, s = {r: 6 for r in reqs}, 0
+    while any(p < 60 for p in at.values()):
+        s += 1
+        live = [r for r in reqs if at[r] < 60 and (s // 4 + int(r[1])) % 3 != 0]      # who decodes changes every 4 steps
+        if not live:
+            continue
+        steps.append({"step": s, "entries": [{"id": r, "tokens": [reqs[r][at[r]]], "want": [0]} for r in live], "end": []})
+        for r in live:
+            at[r] += 1
+    steps[-1]["end"] = list(reqs)
+    outs = {}
+    for graphs in (False, True):
+        eng = Engine(model_dirs[name], dtype="float32", device="cuda:0",
+                     options=EngineOptions(page_size=16, max_cache_tokens=traces.max_tokens(steps), max_batch=4, cuda_graphs=graphs))
+        eng.runner.max_graphs = 2
+        outs[graphs] = traces.replay(eng, steps)
+        if graphs:
+            assert eng.runner.graph_replays > 30 and len(eng.runner._graphs) <= 2
+    for key, row in outs[False].items():
+        assert torch.equal(row, outs[True][key]), key
+    ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    err, where = traces.worst_error(outs[True], ref)
+    assert err < TOL["float32"], (err, where)
