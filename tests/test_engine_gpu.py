@@ -920,3 +920,50 @@ def test_captured_graphs_are_evicted_and_captured_again(model_dirs):
     ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
     err, where = traces.worst_error(outs[True], ref)
     assert err < TOL["float32"], (err, where)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_arrivals_aborts_and_few_pages_through_the_entry_point(model_dirs, seed):
+    """Requests arrive between steps, some are aborted at random moments, greedy and sampled ones side by side, on
+    a cache and a token budget drawn small: after every step no page is lost or held twice, in the end everything
+    is free, every request was reported once, and every greedy request that ran to its length has the plain
+    implementation's tokens (32-bit)."""
+    import random
+    from sharpinference_b200 import Engine, EngineOptions, SamplingParams
+    name = "ABD"[seed]
+    cfg, w = plain.load_folder(model_dirs[name])
+    rng = random.Random(seed)
+    eng = Engine(model_dirs[name], dtype="float32", device="cuda:0",
+                 options=EngineOptions(page_size=8, max_cache_tokens=rng.choice([96, 160]), max_batch=rng.choice([2, 4]),
+                                       max_tokens_per_step=rng.choice([5, 16, 40])))
+    pending = []
+    for i in range(16):
+        sp = SamplingParams(temperature=rng.choice([0.0, 0.0, 0.8]), max_new_tokens=rng.choice([1, 4, 9]),
+                            seed=rng.randrange(1000), top_k=rng.choice([0, 0, 5]))
+        pending.append((traces.random_tokens(cfg["vocab_size"], rng.choice([1, 2, 7, 19, 33, 60]), seed=100 * seed + i), sp))
+    live, done, steps = {}, {}, 0
+    while pending or eng.has_unfinished:
+        if pending and rng.random() < 0.4:
+            p, sp = pending.pop(0)
+            live[eng.add_request(p, sp)] = (p, sp)
+        if live and rng.random() < 0.05:
+            rid = rng.choice(list(live))
+            out = eng.abort(rid) if rid not in done else None
+            if out is not None:
+                done[rid] = out
+        for out in eng.step():
+            assert out.request_id not in done
+            done[out.request_id] = out
+        eng.cache.check_invariants()
+        steps += 1
+        assert steps < 3000
+    assert not eng.cache.requests and all(g.pages.held_count == 0 for g in eng.cache.groups)
+    assert eng.cache.state_slots.free_count == eng.cache.max_requests and set(done) == set(live) and not eng._requests
+    checked = 0
+    for rid, out in done.items():
+        p, sp = live[rid]
+        assert out.finished and out.finish_reason in ("length", "abort", "cache_full")
+        if out.finish_reason == "length" and sp.temperature == 0.0:
+            assert out.tokens == plain.generate_greedy(cfg, w, p, sp.max_new_tokens), (rid, out.preemptions)
+            checked += 1
+    assert checked >= 4
