@@ -967,3 +967,28 @@ def test_random_arrivals_aborts_and_few_pages_through_the_entry_point(model_dirs
             assert out.tokens == plain.generate_greedy(cfg, w, p, sp.max_new_tokens), (rid, out.preemptions)
             checked += 1
     assert checked >= 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(2))
+def test_drawn_schedules_with_long_portions_at_the_large_models_shapes(large_shapes, seed, dtype):
+    """Drawn schedules whose portions run from one token to 700 (around the 128-row attention tiles: 127, 128, 129)
+    beside decoded tokens of other requests, at head size 128 and pages of 64: the tcgen05 attention with partial
+    tiles, the split-KV kernel and every form of the grouped product in the same steps."""
+    from sharpinference_b200 import Engine, EngineOptions
+    folder, reqs = large_shapes
+    steps = traces.drawn(reqs, seed, sizes=(1, 2, 3, 5, 17, 64, 127, 128, 129, 300, 700), want_share=0.2)
+    engine = Engine(folder, dtype=dtype, device="cuda:0",
+                    options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=4))
+    routing = {} if dtype == "bfloat16" else None
+    got = traces.replay(engine, steps, routing)
+    if routing is None:
+        cfg, w = plain.load_folder(folder)
+        ref = {rid: plain.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    else:
+        ref, _ = plain_under_engine_routing(folder, reqs, routing)
+    err, where = traces.worst_error(got, ref)
+    print(f"large shapes, drawn schedule {seed} {dtype}: {len(steps)} steps, worst relative error {err:.3e} at {where}")
+    assert err < TOL[dtype], f"worst error {err:.3e} at {where}"
+    engine.cache.check_invariants()
+    assert all(g.pages.held_count == 0 for g in engine.cache.groups)

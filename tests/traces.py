@@ -86,10 +86,11 @@ def mixed(requests: Dict[str, List[int]], max_live: int = 4, tail: int = 6,
     return steps
 
 
-def drawn(requests: Dict[str, List[int]], seed: int, max_live: int = 4) -> List[dict]:
+def drawn(requests: Dict[str, List[int]], seed: int, max_live: int = 4,
+          sizes: Sequence[int] = (1, 2, 2, 3, 5, 8, 16, 17, 31, 40), want_share: float = 0.6) -> List[dict]:
     """A drawn schedule: up to ``max_live`` requests live; each step every live request either sits out,
-    brings one token, or brings a portion of a drawn size (1 to 40); the wanted places are a drawn subset of
-    the portion's places that always holds its last one."""
+    brings one token, or brings a portion of a size drawn from ``sizes``; the wanted places are a drawn subset
+    of the portion's places that always holds its last one."""
     import random
     r = random.Random(seed)
     waiting = list(requests.items())
@@ -109,8 +110,8 @@ def drawn(requests: Dict[str, List[int]], seed: int, max_live: int = 4) -> List[
             if kind < 0.15 and len(order) > 1:
                 nxt.append((rid, toks, at))
                 continue
-            n = 1 if kind < 0.5 else min(left, r.choice([1, 2, 2, 3, 5, 8, 16, 17, 31, 40]))
-            want = sorted(set(i for i in range(n) if r.random() < 0.6) | {n - 1})
+            n = 1 if kind < 0.5 else min(left, r.choice(list(sizes)))
+            want = sorted(set(i for i in range(n) if r.random() < want_share) | {n - 1})
             entries.append({"id": rid, "tokens": toks[at:at + n], "want": want})
             if at + n == len(toks):
                 ended.append(rid)
