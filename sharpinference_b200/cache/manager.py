@@ -129,6 +129,7 @@ class CacheManager:
         self.requests: Dict[Hashable, RequestCache] = {}
         self.state_slots = FreeList(max_requests)
         self._schedule = list(schedule)
+        self._no_pages: Dict[int, int] = {}
 
         by_spec: Dict[CacheSpec, CacheGroup] = {}
         for index, entry in enumerate(self._schedule):
@@ -151,6 +152,7 @@ class CacheManager:
         for index, entry in enumerate(self._schedule):
             if entry.cache_from is not None:
                 self._entry_group[index] = self._entry_group[entry.cache_from]
+        self._no_pages = dict.fromkeys((g.index for g in self.groups), 0)
 
         if allocate:
             for g in self.groups:
@@ -215,7 +217,8 @@ class CacheManager:
         end = rc.length + n_new
         if rc.length % self.page_size and (end - 1) // self.page_size == (rc.length - 1) // self.page_size:
             # everything falls into the block that holds the last committed position, which has its pages
-            return dict.fromkeys((g.index for g in self.groups), 0)
+            # (most decode steps: one shared answer, which callers only read)
+            return self._no_pages
         need = {}
         blocks_end = (end + self.page_size - 1) // self.page_size
         for g in self.groups:

@@ -218,11 +218,12 @@ class Scheduler:
                 decodes = sorted(decodes, key=lambda r: (r.last_step, len(r.generated), r.admitted_order))[:budget]
             ok = True
             for req in decodes:
-                if self._fits(req, 1, left):
-                    self._take(req, 1, left)
-                else:
+                need = self.cache.pages_needed(req.request_id, 1)
+                if any(k > left[g] for g, k in need.items()):
                     ok = False
                     break
+                for g, k in need.items():
+                    left[g] -= k
             if ok:
                 break
             victim = self.running[-1]
