@@ -250,6 +250,156 @@ static int launch_router_stream(const float* h, const float* wr, int T, int H, i
     return SHARPI_OK;
 }
 
+// Very many tokens, a row that fits shared memory: the block's SMEM_TPB tokens are brought into shared memory once
+// and every pass of EPP router rows (held in registers, as above) runs over them there, so the activations
+// cross into the SM once instead of once per pass (with 16 experts the kernel above reads them four times).
+// The sums are formed exactly as in router_segment_dot.
+constexpr int SMEM_TPB = 8;
+constexpr int SMEM_SHARES = 1;      // warps per segment, each with every SMEM_SHARES-th token: more warps to hide latencies
+constexpr int SMEM_THREADS = ROUTER_SEGMENTS * 32 * SMEM_SHARES;
+
+template <int NI, int EPP>
+__device__ __forceinline__ void router_rows_load(float4 (&b)[EPP][NI], const float* __restrict__ wr, int e0, int E,
+                                                 int H, int begin, int n4, int lane) {
+#pragma unroll
+    for (int ee = 0; ee < EPP; ++ee)
+#pragma unroll
+        for (int k = 0; k < NI; ++k) {
+            const int i = lane + 32 * k;
+            b[ee][k] = (e0 + ee < E && i < n4)
+                           ? __ldg(reinterpret_cast<const float4*>(wr + (size_t)(e0 + ee) * H + begin) + i)
+                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+}
+
+// Sums of NV values over the warp, each formed by the same tree of additions as warp_sum (partner 16, 8, 4, 2,
+// 1 away; a + b is b + a), but halving the number of values a lane carries at each of the first steps instead of
+// carrying all of them through five: 9 shuffles for eight values, not 40.  Lane l ends with the sum of value
+// l >> (5 - log2 NV).
+template <int NV>
+__device__ __forceinline__ float warp_sums_scattered(float (&v)[NV], int lane) {
+    int o = 16;
+#pragma unroll
+    for (int n = NV; n > 1; n >>= 1, o >>= 1) {
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int j = 0; j < n / 2; ++j) {
+            const float mine = upper ? v[n / 2 + j] : v[j];
+            const float theirs = upper ? v[j] : v[n / 2 + j];
+            v[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, o);
+        }
+    }
+#pragma unroll
+    for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+    return v[0];
+}
+
+template <int NI, int EPP>
+__device__ __forceinline__ void router_rows_apply(const float4 (&b)[EPP][NI], const float* h_s, float* seg_s, int e0,
+                                                  int E, int H, int begin, int n4, int first, int n_tok, int warp,
+                                                  int lane) {
+    constexpr int NV = 2 * EPP, OWNERS = 32 / NV;                // two tokens at a time
+    for (int tt = first; tt < n_tok; tt += 2 * SMEM_SHARES) {
+        float v[NV];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int t = min(tt + half * SMEM_SHARES, n_tok - 1);   // an odd last token is computed twice, stored once
+            const float4* a4 = reinterpret_cast<const float4*>(h_s + (size_t)t * H + begin);
+            float4 a[NI];
+#pragma unroll
+            for (int k = 0; k < NI; ++k) {
+                const int i = lane + 32 * k;
+                a[k] = i < n4 ? a4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int ee = 0; ee < EPP; ++ee) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int k = 0; k < NI; ++k) {
+                    if (lane + 32 * k < n4) {                    // a lane adds only the pieces it has, in order
+                        acc = fmaf(a[k].x, b[ee][k].x, acc);
+                        acc = fmaf(a[k].y, b[ee][k].y, acc);
+                        acc = fmaf(a[k].z, b[ee][k].z, acc);
+                        acc = fmaf(a[k].w, b[ee][k].w, acc);
+                    }
+                }
+                v[half * EPP + ee] = acc;
+            }
+        }
+        const float part = warp_sums_scattered<NV>(v, lane);
+        const int which = lane / OWNERS, t = tt + (which / EPP) * SMEM_SHARES, e = e0 + which % EPP;
+        if (lane % OWNERS == 0 && t < n_tok && e < E) seg_s[(warp * SMEM_TPB + t) * E + e] = part;
+    }
+}
+
+template <int NI, int EPP>
+__global__ void __launch_bounds__(SMEM_THREADS)
+router_top1_smem_kernel(const float* __restrict__ h, const float* __restrict__ wr, int T, int H, int E,
+                        int* __restrict__ expert_id, float* __restrict__ expert_weight,
+                        float* __restrict__ logits_out) {
+    extern __shared__ __align__(16) float smem[];
+    float* h_s = smem;                                           // [SMEM_TPB][H]
+    float* seg_s = h_s + (size_t)SMEM_TPB * H;                   // [segments][SMEM_TPB][E]
+    float* r_s = seg_s + ROUTER_SEGMENTS * SMEM_TPB * E;         // [SMEM_TPB][E]
+    const int t0 = blockIdx.x * SMEM_TPB;
+    const int n_tok = min(SMEM_TPB, T - t0);
+    const int warp = (threadIdx.x >> 5) % ROUTER_SEGMENTS, share = (threadIdx.x >> 5) / ROUTER_SEGMENTS;
+    const int lane = threadIdx.x & 31;
+    {
+        // Asynchronous 16-byte copies: all of a thread's pieces are in flight at once, so the tile arrives at the
+        // rate the SM can take it instead of one memory latency per few pieces.  H % 4 == 0 here.
+        const float* src = h + (size_t)t0 * H;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(h_s);
+        const int n = n_tok * (H >> 2);
+        for (int i = threadIdx.x; i < n; i += SMEM_THREADS)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 4 * (size_t)i)
+                         : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const int seg = router_segment_len(H);
+    const int begin = min(H, warp * seg), end = min(H, begin + seg);
+    const int n4 = (end - begin) >> 2;
+    float4 b[EPP][NI];
+    for (int e0 = 0; e0 < E; e0 += EPP) {
+        router_rows_load<NI, EPP>(b, wr, e0, E, H, begin, n4, lane);
+        if (e0 == 0) {                                           // the first router rows are on their way by now
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+        }
+        router_rows_apply<NI, EPP>(b, h_s, seg_s, e0, E, H, begin, n4, share, n_tok, warp, lane);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_tok * E; i += SMEM_THREADS) {
+        float total = 0.0f;
+#pragma unroll
+        for (int sgm = 0; sgm < ROUTER_SEGMENTS; ++sgm) total += seg_s[sgm * SMEM_TPB * E + i];
+        r_s[i] = total;
+    }
+    __syncthreads();
+    if (logits_out)
+        for (int i = threadIdx.x; i < n_tok * E; i += SMEM_THREADS) logits_out[(size_t)t0 * E + i] = r_s[i];
+    if (threadIdx.x < n_tok)
+        router_pick(r_s + threadIdx.x * E, E, expert_id + t0 + threadIdx.x, expert_weight + t0 + threadIdx.x);
+}
+
+static size_t router_smem_bytes(int H, int E) {
+    return ((size_t)SMEM_TPB * H + (size_t)(ROUTER_SEGMENTS + 1) * SMEM_TPB * E) * sizeof(float);
+}
+
+template <int NI>
+static int launch_router_smem(const float* h, const float* wr, int T, int H, int E, int* expert_id,
+                              float* expert_weight, float* logits_out, cudaStream_t stream) {
+    const size_t smem = router_smem_bytes(H, E);
+    constexpr int EPP = NI <= 5 ? 8 : 4;                         // EPP x NI float4 of router rows in registers
+    cudaError_t err = cudaFuncSetAttribute(router_top1_smem_kernel<NI, EPP>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return SHARPI_LAUNCH_FAILED;
+    router_top1_smem_kernel<NI, EPP><<<(T + SMEM_TPB - 1) / SMEM_TPB, SMEM_THREADS, smem, stream>>>(
+        h, wr, T, H, E, expert_id, expert_weight, logits_out);
+    SHARPI_CHECK_LAUNCH();
+    return SHARPI_OK;
+}
+
 // Few tokens: what costs time is the chain of dependent loads of one block walking every expert, so each
 // (token, expert) pair gets a block of its own whose eight warps take one segment each; every load of the
 // step is then in flight at once.  The logits go to `logits`; the block that finishes last for a token (a
@@ -347,7 +497,18 @@ SHARPI_API int sharpi_router_top1(const float* h, const float* wr, int T, int H,
     const bool vec = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(h) & 15) == 0);
     const int pieces = (router_segment_len(H) / 4 + 31) / 32;          // per lane and segment
-    if (T >= 1024 && vec && pieces <= 8 && (size_t)(ROUTER_SEGMENTS + 1) * STREAM_TPB * E * sizeof(float) <= 200 * 1024) {
+    if (T >= 1024 && vec && pieces <= 8 && router_smem_bytes(H, E) <= 200 * 1024) {
+        switch (pieces) {
+            case 1: rc = launch_router_smem<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 2: rc = launch_router_smem<2>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 3: rc = launch_router_smem<3>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 4: rc = launch_router_smem<4>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 5: rc = launch_router_smem<5>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 6: rc = launch_router_smem<6>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            case 7: rc = launch_router_smem<7>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+            default: rc = launch_router_smem<8>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
+        }
+    } else if (T >= 1024 && vec && pieces <= 8 && (size_t)(ROUTER_SEGMENTS + 1) * STREAM_TPB * E * sizeof(float) <= 200 * 1024) {
         switch (pieces) {
             case 1: rc = launch_router_stream<1>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;
             case 2: rc = launch_router_stream<2>(h, wr, T, H, E, expert_id, expert_weight, logits_out, stream); break;

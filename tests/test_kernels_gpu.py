@@ -297,7 +297,8 @@ def test_gemm_nt_grouped_gather_scatter_accumulate(ops, dtype):
 
 # ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("T,H,E", [(1, 77, 5), (50, 5120, 16), (9, 5120, 128), (3, 20000, 7), (1100, 333, 6),
-                                   (1029, 1280, 19), (40, 24, 3), (1030, 5120, 16), (1100, 8192, 5)])
+                                   (1029, 1280, 19), (40, 24, 3), (1030, 5120, 16), (1100, 8192, 5), (2050, 5120, 128),
+                                   (1025, 2048, 7)])
 def test_router_top1(ops, T, H, E):
     h, wr = rnd(T, H, seed=9), rnd(E, H, scale=0.05, seed=10)
     expert, weight, logits = ops.router_top1(h, wr, want_logits=True)
