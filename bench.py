@@ -271,6 +271,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--own-dense-rows", type=int, default=0,
+                    help="EngineOptions.own_dense_rows: dense products of up to this many rows on the engine's own kernel")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--preset", default="scout", choices=["scout", "maverick", "long"],
                     help="scout: 20 Scout-sized layers, batch 8 at context 8192 (the default run); maverick: 4 "
@@ -320,7 +322,8 @@ def main() -> int:
     cache_tokens = max_b * ((ns.context + page - 1) // page * page + page) + ns.prefill_tokens + page
     engine = Engine(model, dtype="bfloat16", device=dev,
                     options=EngineOptions(page_size=page, max_cache_tokens=cache_tokens, max_batch=max_b,
-                                          max_tokens_per_step=max(ns.prefill_tokens, max_b)))
+                                          max_tokens_per_step=max(ns.prefill_tokens, max_b),
+                                          own_dense_rows=ns.own_dense_rows))
     torch.manual_seed(0)                   # the cache content decides the routing of the timed steps: keep it fixed
     for g in engine.cache.groups:          # keys and values as a prefill would have left them: unit-scale numbers
         g.kv.normal_(0.0, 1.0)

@@ -113,7 +113,7 @@ def tc_gemm(ns) -> None:
 
 
 def dense(ns) -> None:
-    """A dense product of a few rows: the grouped tensor-core kernel with one group, or the library.  The weights rotate through enough copies to exceed the L2 cache, as in a model of many layers."""
+    """A dense product of a few rows: the grouped tensor-core kernel with one group, the weight-streaming kernel for up to 16 rows, or the library.  The weights rotate through enough copies to exceed the L2 cache, as in a model of many layers."""
     M, N, K = ns.rows, ns.n, ns.k
     copies = max(2, (300 << 20) // (N * K * 2) + 1)
     ws = [torch.empty(N, K, dtype=torch.bfloat16, device=DEV).normal_(0, 0.02) for _ in range(copies)]
@@ -125,7 +125,9 @@ def dense(ns) -> None:
         w = ws[state["i"] % copies]
         state["i"] += 1
         if ns.impl == "grouped":
-            ops.tc_dense(a, w, swiglu=ns.swiglu, out=None if ns.swiglu else out)
+            ops.tc_dense(a, w, out=out)
+        elif ns.impl == "rows":
+            ops.dense_rows(a, w, swiglu=ns.swiglu, out=None if ns.swiglu else out)
         else:
             y = torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
             if ns.swiglu:
@@ -202,8 +204,8 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--n", type=int, default=7168)
     p.add_argument("--k", type=int, default=5120)
-    p.add_argument("--swiglu", action="store_true")
-    p.add_argument("--impl", choices=["grouped", "library"], default="grouped")
+    p.add_argument("--swiglu", action="store_true", help="SwiGLU after the product (rows: in its epilogue; library: a second kernel)")
+    p.add_argument("--impl", choices=["grouped", "rows", "library"], default="grouped")
     p.set_defaults(fn=dense)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)

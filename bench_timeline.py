@@ -38,7 +38,8 @@ def timeline_run(ns, cfg) -> int:
     model = build_random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02, norm_std=0.0)
     engine = Engine(model, dtype="bfloat16", device=dev,
                     options=EngineOptions(page_size=64, max_cache_tokens=B * (ns.context + 128) + 256 + ns.prefill_tokens, max_batch=B + 1,
-                                          max_tokens_per_step=max(B, 64, ns.prefill_tokens)))
+                                          max_tokens_per_step=max(B, 64, ns.prefill_tokens),
+                                          own_dense_rows=ns.own_dense_rows))
     torch.manual_seed(0)
     for g in engine.cache.groups:
         g.kv.normal_(0.0, 1.0)
@@ -117,6 +118,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--preset", default="scout", choices=["scout", "maverick"])
+    ap.add_argument("--own-dense-rows", type=int, default=0,
+                    help="EngineOptions.own_dense_rows: dense products of up to this many rows on the engine's own kernel")
     ns = ap.parse_args()
     from sharpinference_b200.config import Llama4TextConfig
     base = MAVERICK if ns.preset == "maverick" else SCOUT

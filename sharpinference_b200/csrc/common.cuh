@@ -34,7 +34,9 @@ enum SharpiDtype : int {
 // before it in the stream is still running, so that its launch and set-up overlap that kernel's tail; it
 // must call pdl_wait() before it reads or writes anything that an earlier kernel touches (every such kernel
 // calls it on every path, before any return, so completion of a kernel implies completion of those before
-// it).  Launched the plain way, pdl_wait() does nothing.  sharpi_set_programmatic_launch(0) turns the
+// it).  What an earlier kernel wrote is read with ordinary loads, never with __ldg: a load that is declared to
+// read memory which does not change during the kernel may be moved ahead of the wait by the compiler.
+// Launched the plain way, pdl_wait() does nothing.  sharpi_set_programmatic_launch(0) turns the
 // attribute off for the launches of this library (every kernel library exports its own switch).
 __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
 #pragma unroll
         for (int r = 0; r < MAX_PIECES; ++r) {
             const int i = lane + 32 * r;
-            x[s][r] = (slot0 + s < slots && i < n4) ? __ldg(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            x[s][r] = (slot0 + s < slots && i < n4) ? src[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     }
     const int pos = a.positions[t];

@@ -103,7 +103,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
     float mine = 1.0f;
     if (p.row_scale && lane < count) {
         const int r = r_first + lane;
-        mine = __ldg(p.row_scale + (p.scale_rows ? __ldg(p.scale_rows + r) : r));
+        mine = p.row_scale[p.scale_rows ? p.scale_rows[r] : r];
     }
     float sc[16];
 #pragma unroll
@@ -131,7 +131,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
                 // one group), so a reduction that returns nothing gives the same sum as load, add, store,
                 // without a round trip to memory per element.
                 const int r = r_first + j;
-                float* dst = C + (size_t)(p.out_rows ? __ldg(p.out_rows + r) : r) * p.N + n;
+                float* dst = C + (size_t)(p.out_rows ? p.out_rows[r] : r) * p.N + n;
                 const float gv = scaled ? g[j] * sc[j] : g[j], uv = scaled ? u[j] * sc[j] : u[j];
                 if (p.accumulate) {
                     if (n_ok) atomicAdd(dst, gv);

@@ -44,10 +44,12 @@ class EngineOptions:
     max_batch: int = 64                 # live requests (and state slots)
     max_tokens_per_step: int = 2048     # token budget of one step
     cuda_graphs: bool = True            # capture decode-only steps as CUDA graphs (when the model's parts allow)
-    # Dense bfloat16 products of steps of up to this many rows run on the engine's own tcgen05 weight-streaming
-    # kernel instead of the vendor library (which the reference also uses only for batched projections, its
-    # single-token products being kernels of its own).  0: the library everywhere, which measured faster on
-    # B200 (Scout sizes, batch 8: 947 against 897 tok/s).  The results differ by rounding only.
+    # Dense bfloat16 products of steps of up to this many rows (at most 16) run on the engine's own
+    # weight-streaming kernel instead of the vendor library (which the reference also uses only for batched
+    # projections, its single-token products being kernels of its own).  0: the library everywhere, which is
+    # the faster step on B200 (Scout sizes, 8 layers, batch 1: 614 against 593 tok/s) although the own kernel
+    # is the faster product alone (parts/linear.py has the figures).  The LM head keeps the library either way
+    # (2 GB of weights: 322 against 299 us).  The results differ by rounding only.
     own_dense_rows: int = 0
     # Launch kernels with programmatic stream serialization: a kernel's set-up overlaps the tail of the one
     # before it.  False launches every kernel the plain way.  One switch for the process (the kernel libraries

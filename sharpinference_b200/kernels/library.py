@@ -44,6 +44,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_moe_sort": ("moe", [P, I, I, P, P, P]),
     "sharpi_tc_grouped_gemm": ("tc_gemm", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "sharpi_gather_rows_bf16": ("tc_gemm", [P, P, P, I, I, P]),
+    "sharpi_dense_rows": ("dense_rows", [P, P, P, P, I, I, I, I, P]),
     "sharpi_argmax_rows": ("sampling", [P, I, I, P, P, P]),
     "sharpi_sample_rows_sliced": ("sampling_sliced", [P, I, I, P, P, P, P, P, P, I, I, P, P]),
     "sharpi_apply_penalties": ("sampling", [P, I, P, P, P, P, P, P, I, P]),

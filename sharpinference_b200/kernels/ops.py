@@ -488,13 +488,13 @@ def tc_set_wait_test(limit: int, drop_from: int) -> None:
 _dense_offsets = {}
 
 
-def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Optional[torch.Tensor] = None,
+def tc_dense(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
              accumulate: bool = False) -> torch.Tensor:
-    """A dense product ``a . w^T`` for a few rows (decode) on the grouped tensor-core kernel with one
-    group: the weights stream once through 128-row tiles, K cut over CTAs when the tiles alone would
-    not fill the GPU.  ``swiglu``: ``w`` holds gate rows then up rows and the result is
-    ``silu(g) * u`` in bfloat16; otherwise float32 ``[M, N]``, added into ``out`` with reductions when
-    ``accumulate`` (so that another launch may add into the same rows meanwhile)."""
+    """A dense product ``a . w^T`` for a few rows on the grouped tensor-core kernel with one group: the
+    weights stream once through 128-row tiles, K cut over CTAs when the tiles alone would not fill the GPU.
+    float32 ``[M, N]``, added into ``out`` with reductions when ``accumulate`` (so that another launch may add
+    into the same rows meanwhile).  Alone it is slower than :func:`dense_rows` and the library; its small CTAs
+    run well beside the routed experts' kernels, which is where the mixture part uses it."""
     M = a.shape[0]
     key = (a.device, M)
     offsets = _dense_offsets.get(key)
@@ -502,12 +502,47 @@ def tc_dense(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Opt
         offsets = torch.tensor([0, M], dtype=torch.int32, device=a.device)
         _dense_offsets[key] = offsets
     N = w.shape[0]
-    n_tiles = ((N // 2 if swiglu else N) + 127) // 128
+    n_tiles = (N + 127) // 128
     sms = sm_count(a.device)
     k_split = 1 if n_tiles >= sms else max(1, min(4, (2 * sms + n_tiles - 1) // n_tiles))
     row_tile = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-    return tc_grouped_gemm(a, w.unsqueeze(0), offsets, mode=TC_MODE_SWIGLU if swiglu else TC_MODE_STORE, out=out,
-                           row_tile=row_tile, k_split=k_split, accumulate=accumulate)
+    return tc_grouped_gemm(a, w.unsqueeze(0), offsets, mode=TC_MODE_STORE, out=out, row_tile=row_tile,
+                           k_split=k_split, accumulate=accumulate)
+
+
+DENSE_ROWS_MAX = 16           # rows the weight-streaming dense kernel takes
+
+
+def dense_rows(a: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a . w^T`` for up to 16 bfloat16 rows against a bfloat16 weight ``[N, K]`` that streams in once
+    (``dense_rows.cu``): float32 ``[M, N]`` (plus ``bias``), added into ``out`` with reductions when
+    ``accumulate``, or with ``swiglu`` (``w`` = gate rows then up rows) ``silu(g) * u`` in bfloat16 ``[M, N / 2]``."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"weight is {tuple(w.shape)}, activations have width {K}")
+    if M > DENSE_ROWS_MAX:
+        raise KernelError(f"dense_rows takes up to {DENSE_ROWS_MAX} rows, found {M}")
+    if swiglu and (accumulate or bias is not None):
+        raise KernelError("the SwiGLU epilogue neither accumulates nor takes a bias")
+    if accumulate and out is None:
+        raise KernelError("accumulate needs an output to add to")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if out is None:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device) if swiglu else \
+            torch.empty((M, N), dtype=torch.float32, device=a.device)
+    else:
+        _need(out, "out", torch.bfloat16 if swiglu else torch.float32)
+        if tuple(out.shape) != ((M, N // 2) if swiglu else (M, N)):
+            raise KernelError(f"out is {tuple(out.shape)} for a product of {M} rows and a weight of {N} rows")
+    mode = 2 if swiglu else 1 if accumulate else 0
+    check(kernel("sharpi_dense_rows")(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, mode,
+                                      _stream()), "sharpi_dense_rows")
+    return out
 
 
 def router_top1(h32: torch.Tensor, router_weight: torch.Tensor, *, want_logits: bool = False, sort: bool = False):

@@ -31,8 +31,8 @@ class DenseSwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-        if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h):
-            act = ops.tc_dense(h, self.gate_up.weight, swiglu=True)       # SwiGLU in the product's epilogue
+        if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h) and self.gate_up.bias is None:
+            act = ops.dense_rows(h, self.gate_up.weight, swiglu=True)     # SwiGLU in the product's epilogue
         else:
             act = ops.swiglu(self.gate_up(h), self.act_dtype)
         return self.down(act, out=out, accumulate=accumulate)
@@ -63,12 +63,12 @@ class MoESigmoidTop1(FeedForward):
     graph_safe = True
     # Steps of more rows than this keep the routed gate|up product on the routing's stream (see forward).
     SMALL_STEP_ROWS = 256
-    # Up to this many rows the shared expert's down product runs on our own weight-streaming kernel instead of
-    # the library's: alone the library is a little faster on that shape, but beside the routed gate|up product
-    # the step is not (Scout sizes, 20 layers: batch 1 284 -> 292 tok/s, batch 4 693 -> 702; no difference
-    # from batch 8 on; the shared gate|up product and the attention projections measured slower that way).
-    # Both experts then add into the output with reductions and no longer wait for each other (296 and 715).
-    SHARED_DOWN_OWN_ROWS = 4
+    # Up to this many rows the shared expert's down product adds into the output on the grouped tensor-core
+    # kernel (one group, K cut over CTAs) instead of the library's product and an addition: alone the library is
+    # a little faster on that shape, but beside the routed gate|up product the step is not (Scout sizes, 8
+    # layers: batch 1 614 -> 644 tok/s; no difference from batch 8 on).  Both experts then add into a zeroed
+    # output with reductions and no longer wait for each other.
+    SHARED_DOWN_SPLIT_ADD_ROWS = 4
 
     def __init__(self, *, router: torch.Tensor, experts_gate_up: GroupedLinear, experts_down: GroupedLinear,
                  shared: Optional[DenseSwiGLU], act_dtype: torch.dtype = torch.bfloat16):
@@ -81,8 +81,8 @@ class MoESigmoidTop1(FeedForward):
         self.experts_gate_up, self.experts_down = experts_gate_up, experts_down
         self.shared = shared
         shared_down = getattr(shared, "down", None)
-        if isinstance(shared_down, Linear) and shared_down.stream_rows == 0:
-            shared_down.stream_rows = self.SHARED_DOWN_OWN_ROWS
+        if isinstance(shared_down, Linear) and shared_down.split_add_rows == 0:
+            shared_down.split_add_rows = self.SHARED_DOWN_SPLIT_ADD_ROWS
         self.num_experts = E
         self.act_dtype = act_dtype
         # the tensor-core path takes bfloat16 weights whose inner sizes are multiples of 8 (TMA rows
@@ -104,7 +104,7 @@ class MoESigmoidTop1(FeedForward):
         # of weights keep the memory system busier than one; with priority over the shared expert it measured
         # slower).  Large steps: every product fills the GPU by itself; the routed gate|up product stays on the
         # third stream and takes over the SMs as the shared expert's products drain.
-        # When the shared expert's down product adds with reductions too (few rows, see SHARED_DOWN_OWN_ROWS),
+        # When the shared expert's down product adds with reductions too (few rows, see SHARED_DOWN_SPLIT_ADD_ROWS),
         # both experts add into a zeroed output and the streams need not meet before the end: each element is
         # 0 + a + b in one order or the other, which is the same number.
         tensor_core = self._tensor_core and h.dtype == torch.bfloat16
@@ -113,7 +113,7 @@ class MoESigmoidTop1(FeedForward):
         apart = False
         if self.shared is not None:
             shared_down = getattr(self.shared, "down", None)
-            apart = tensor_core and isinstance(shared_down, Linear) and shared_down.streams(h)
+            apart = tensor_core and isinstance(shared_down, Linear) and shared_down.adds_with_reductions(h)
             make = torch.zeros if apart else torch.empty
             y = make((T, self.experts_down.out_features), dtype=torch.float32, device=h.device)
             side, routed = _side_stream(h.device), _urgent_stream(h.device)

@@ -159,17 +159,19 @@ def test_layer_widths_of_the_large_models(real_widths, cut):
     assert all(g.pages.held_count == 0 for g in engine.cache.groups)
 
 
-def test_dense_products_on_the_engines_own_kernel(large_shapes):
+@pytest.mark.parametrize("rows", [8, 16])
+def test_dense_products_on_the_engines_own_kernel(large_shapes, rows):
     """own_dense_rows: decode-size steps run their dense products (qkv, o, shared expert, dense layers) on the
-    tcgen05 weight-streaming kernel instead of the library; the logits stay within rounding."""
+    weight-streaming kernel up to that many rows (16: its wide form too) instead of the library; the LM head
+    stays on the library; the logits stay within rounding."""
     from sharpinference_b200 import Engine, EngineOptions
     folder, reqs = large_shapes
     reqs = {k: v[:200] for k, v in list(reqs.items())[:3]}
     steps = traces.tail_decode(reqs)
     engine = Engine(folder, dtype="bfloat16", device="cuda:0",
                     options=EngineOptions(page_size=64, max_cache_tokens=traces.max_tokens(steps), max_batch=8,
-                                          own_dense_rows=16))
-    assert all(b.mixer.qkv.stream_rows == 16 and b.ffn.shared.gate_up.stream_rows == 16 for b in engine.model.blocks)
+                                          own_dense_rows=rows))
+    assert all(b.mixer.qkv.stream_rows == rows and b.ffn.shared.gate_up.stream_rows == rows for b in engine.model.blocks)
     assert engine.model.head.stream_rows == 0
     routing = {}
     got = traces.replay(engine, steps, routing)

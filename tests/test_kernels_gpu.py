@@ -553,6 +553,56 @@ def test_tc_grouped_gemm_rows_do_not_depend_on_the_batch(ops):
     assert torch.allclose(cut[0], big[100 + 9], rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 7168, 5120), (8, 5120, 8192), (3, 40, 64), (7, 77, 136), (9, 264, 520),
+                                   (16, 1000, 2048), (1, 8, 8), (5, 202048, 256)])
+def test_dense_rows(ops, M, N, K):
+    """The weight-streaming product of up to 16 rows: store (with and without bias), add-in, and for even N the
+    SwiGLU epilogue; sizes that are no multiples of a tile, a piece of K, or the warps' stride."""
+    a = rnd(M, K, dtype=torch.bfloat16, seed=M + K)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=N)
+    ref = a.double().cpu() @ w.double().cpu().T
+    atol = 1e-4 * float(ref.abs().max()) + 1e-6
+    out = ops.dense_rows(a, w)
+    assert out.dtype == torch.float32 and torch.allclose(out.double().cpu(), ref, rtol=1e-4, atol=atol)
+    bias = rnd(N, seed=3)
+    out_b = ops.dense_rows(a, w, bias=bias)
+    assert torch.allclose(out_b.double().cpu(), ref + bias.double().cpu(), rtol=1e-4, atol=atol)
+    base = rnd(M, N, seed=4)
+    acc = base.clone()
+    ops.dense_rows(a, w, out=acc, accumulate=True)
+    assert torch.allclose(acc.double().cpu(), base.double().cpu() + ref, rtol=1e-4, atol=atol)
+    if N % 2 == 0:
+        act = ops.dense_rows(a, w, swiglu=True)
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        want = g / (1 + torch.exp(-g)) * u
+        assert act.dtype == torch.bfloat16 and act.shape == (M, N // 2)
+        assert torch.allclose(act.double().cpu(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) + 1e-6)
+
+
+def test_dense_rows_do_not_depend_on_the_batch(ops):
+    """A row gives the same bits alone, among eight and among sixteen rows, at any place in the batch."""
+    N, K = 520, 1288
+    a = rnd(16, K, dtype=torch.bfloat16, seed=5)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=6)
+    all16 = ops.dense_rows(a, w)
+    first8 = ops.dense_rows(a[:8].contiguous(), w)
+    one = ops.dense_rows(a[11:12].contiguous(), w)
+    assert torch.equal(all16[:8], first8) and torch.equal(all16[11:12], one)
+    act16 = ops.dense_rows(a, w, swiglu=True)
+    act1 = ops.dense_rows(a[5:6].contiguous(), w, swiglu=True)
+    assert torch.equal(act16[5:6], act1)
+
+
+def test_dense_rows_refuses_what_it_does_not_take(ops):
+    w = rnd(64, 128, dtype=torch.bfloat16, seed=1)
+    with pytest.raises(Exception, match="16 rows"):
+        ops.dense_rows(rnd(17, 128, dtype=torch.bfloat16, seed=2), w)
+    with pytest.raises(Exception):
+        ops.dense_rows(rnd(2, 132, dtype=torch.bfloat16, seed=2), rnd(64, 132, dtype=torch.bfloat16, seed=1))   # K % 8
+    with pytest.raises(Exception, match="width"):
+        ops.dense_rows(rnd(2, 64, dtype=torch.bfloat16, seed=2), w)
+
+
 @pytest.mark.parametrize("k_split", [2, 4, 7])
 def test_tc_grouped_gemm_k_split(ops, k_split):
     """Few rows: K is cut over several CTAs per tile; the last of them adds the parts and applies the epilogue."""

@@ -170,7 +170,8 @@ def test_unknown_part_kind_names_the_known_ones():
 
 
 def test_linear_on_the_weight_streaming_kernel():
-    """The dense products of a decode step can run on the tcgen05 kernel (one group, K cut over CTAs)."""
+    """The dense products of a decode step run on the weight-streaming kernel, SwiGLU in the gate|up product's
+    epilogue; with stream_rows = 0 on the library's, to the same numbers within rounding."""
     from sharpinference_b200.parts import DenseSwiGLU, Linear
     H, I, T = 128, 200, 5
     g, u, dn = rnd(I, H, scale=0.1, seed=1), rnd(I, H, scale=0.1, seed=2), rnd(H, I, scale=0.1, seed=3)
@@ -185,21 +186,24 @@ def test_linear_on_the_weight_streaming_kernel():
     ref = plain.dense_ffn(h.double(), g.double(), u.double(), dn.double())
     assert float((out - ref).abs().max()) / float(ref.abs().max()) < 1e-2
     lib = DenseSwiGLU(gate_up=Linear(gate_up.weight), down=Linear(down.weight), act_dtype=torch.bfloat16)
+    assert not lib.gate_up.streams(hb) and not gate_up.streams(rnd(17, H).to(torch.bfloat16).to(DEV))
     assert float((lib.forward(None, hb).double().cpu() - out).abs().max()) / float(ref.abs().max()) < 1e-2
 
 
 def test_linear_adds_into_its_output():
-    """accumulate: the product is added to what the output holds, on the weight-streaming kernel (with
-    reductions) and on the library's (product, then an addition); a dense SwiGLU passes it on to its down product."""
+    """accumulate: the product is added to what the output holds, on the weight-streaming kernel or the grouped
+    kernel with K cut over CTAs (both with reductions) and on the library's (product, then an addition); a dense
+    SwiGLU passes it on to its down product."""
     from sharpinference_b200.parts import DenseSwiGLU, Linear
     H, I, T = 136, 200, 3
     w = rnd(H, I, scale=0.1, seed=5).to(torch.bfloat16).to(DEV)
     a = rnd(T, I, seed=6).to(torch.bfloat16).to(DEV)
     base = rnd(T, H, seed=7).to(DEV)
     want = base.double().cpu() + a.double().cpu() @ w.double().cpu().T
-    for stream_rows in (0, 8):
-        lin = Linear(w, stream_rows=stream_rows)
+    for stream_rows, split_add_rows in ((0, 0), (8, 0), (0, 4), (8, 4), (0, 2)):
+        lin = Linear(w, stream_rows=stream_rows, split_add_rows=split_add_rows)
         assert lin.streams(a) == (stream_rows > 0)
+        assert lin.adds_with_reductions(a) == (stream_rows > 0 or split_add_rows >= T)
         out = base.clone()
         assert lin(a, out=out, accumulate=True) is out
         assert torch.allclose(out.double().cpu(), want, rtol=1e-4, atol=1e-3)
@@ -222,7 +226,8 @@ def test_linear_with_a_bias(dtype):
     want = a.double() @ w.double().T + b.double()
     for stream_rows in (0, 16):
         lin = Linear(w.to(dtype).to(DEV), bias=b.to(DEV), stream_rows=stream_rows)
-        assert not lin.streams(a.to(dtype).to(DEV))                   # a biased product stays off the streaming kernel
+        # the weight-streaming kernel adds the bias in its epilogue
+        assert lin.streams(a.to(dtype).to(DEV)) == (dtype == torch.bfloat16 and stream_rows > 0)
         assert torch.allclose(lin(a.to(dtype).to(DEV)).double().cpu(), want, rtol=1e-4, atol=1e-3)
     with pytest.raises(ValueError, match="bias"):
         Linear(w.to(DEV), bias=b[:5].to(DEV))
