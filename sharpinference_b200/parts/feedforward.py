@@ -129,7 +129,8 @@ class MoESigmoidTop1(FeedForward):
         act = None
         with torch.cuda.stream(routed if routed is not None else main):
             expert, weight, _, offsets, sorted_rows = ops.router_top1(h32, self.router, sort=True)
-            h_sorted = ops.gather_rows_bf16(h, sorted_rows) if tensor_core else None
+            # one row is its own sorted order: nothing to gather
+            h_sorted = (h if T == 1 else ops.gather_rows_bf16(h, sorted_rows)) if tensor_core else None
             if tensor_core and T > self.SMALL_STEP_ROWS:
                 act = ops.tc_grouped_gemm(h_sorted, self.experts_gate_up.weight, offsets, mode=ops.TC_MODE_SWIGLU,
                                           row_scale=weight, scale_rows=sorted_rows)
