@@ -137,6 +137,23 @@ def dense(ns) -> None:
           f"weights {N * K * 2 / ms / 1e6:.0f} GB/s")
 
 
+def router(ns) -> None:
+    """Router logits, sigmoid and top-1 for a prompt portion's tokens (fp32), each call on another copy of the
+    activations so that they come from memory as after the norm kernel of a long step."""
+    T, H, E = ns.tokens, ns.hidden, ns.experts
+    copies = max(2, (300 << 20) // (T * H * 4) + 1)
+    hs = [torch.randn(T, H, device=DEV) for _ in range(copies)]
+    wr = torch.randn(E, H, device=DEV) * 0.05
+    state = {"i": 0}
+
+    def fn():
+        ops.router_top1(hs[state["i"] % copies], wr)
+        state["i"] += 1
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"router_top1 tokens={T} hidden={H} experts={E}: {ms * 1e3:.1f} us, "
+          f"{(T * H * 4 + E * H * 4) / ms / 1e6:.0f} GB/s of activations and router rows read once")
+
+
 def _cache(batch: int, context: int, nkv: int, d: int, ps: int):
     blocks = (context + ps - 1) // ps
     pages = batch * blocks
@@ -207,6 +224,11 @@ def main(argv=None) -> int:
     p.add_argument("--swiglu", action="store_true", help="SwiGLU after the product (rows: in its epilogue; library: a second kernel)")
     p.add_argument("--impl", choices=["grouped", "rows", "library"], default="grouped")
     p.set_defaults(fn=dense)
+    p = sub.add_parser("router")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=5120)
+    p.add_argument("--experts", type=int, default=16)
+    p.set_defaults(fn=router)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
