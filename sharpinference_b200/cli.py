@@ -6,7 +6,10 @@ Kept with the same spelling, meaning and default: ``-m|--model`` (here a model f
 ``-p|--prompt``, ``-f|--file``, ``-n|--n-predict`` (512), ``--temp`` (0.7; 0 = greedy), ``--top-k``
 (40), ``--top-p`` (0.95), ``--min-p`` (0.05), ``-s|--seed`` (-1 = random), ``-c|--ctx-size``,
 ``--repeat-penalty`` (1.1), ``--repeat-last-n`` (256), ``--frequency-penalty``, ``--presence-penalty``,
-``--verbose-prompt``, ``--no-display-prompt``.  There is no tokenizer in this engine (random-weight
+``--verbose-prompt``, ``--no-display-prompt``, ``--device`` (an index or a name such as CUDA0; one GPU, and
+no CPU), ``--min-batch-blas`` (the smallest step whose dense products go to the library's GEMM: below it the
+engine's own weight-streaming kernel runs them, as the reference's matvec kernels do below its threshold,
+src/SharpInference.Cli/RunCommand.cs:179-182; here 0 means the library at every size).  There is no tokenizer in this engine (random-weight
 models have no vocabulary), so a prompt is a list of token ids: ``-p "5 17 3"`` or ``--tokens
 5,17,3``; several prompts are separated by ``;`` and are served as one continuous batch.  Added:
 ``--dtype``, ``--random-weights SEED`` with ``--config`` (writes a model folder first),
@@ -62,11 +65,30 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens-per-step", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-cache-tokens", type=int, default=None)
+    ap.add_argument("--device", default=None,
+                    help="GPU to run on: an index (0, 1, ...) or a name (CUDA0, cuda:1); default: cuda:0.  One device "
+                         "only; 'none' (CPU) is refused: the engine has no CPU path")
+    ap.add_argument("--min-batch-blas", type=int, default=0,
+                    help="smallest step (rows) whose dense products go to the library's GEMM; smaller steps run them on "
+                         "the engine's own weight-streaming kernel (at most 17: that kernel takes up to 16 rows).  "
+                         "0 (default): the library at every size, which is the faster step on B200")
     ap.add_argument("--json", action="store_true", help="print the result as one JSON object")
     ap.add_argument("--trace-layers", action="store_true",
                     help="after every step print, per layer, the L2 norm of the last row's residual and the expert "
                          "it was routed to (steps then run eagerly); for finding the first layer that differs")
     return ap
+
+
+def parse_device(text):
+    """``--device`` in the reference's spellings (src/SharpInference.Cli/RunCommand.cs:99-102: an index, or a name
+    such as CUDA0) and torch's; None for anything else, 'none' (CPU) included."""
+    if text is None or text == "" or text.lower() == "auto":
+        return "cuda:0"
+    t = text.strip().lower()
+    for prefix in ("cuda:", "cuda", ""):
+        if t.startswith(prefix) and t[len(prefix):].isdigit():
+            return f"cuda:{int(t[len(prefix):])}"
+    return None
 
 
 def main(argv=None) -> int:
@@ -99,9 +121,14 @@ def main(argv=None) -> int:
     cache_tokens = ns.max_cache_tokens
     if cache_tokens is None and ns.ctx_size > 0:
         cache_tokens = ns.ctx_size * ns.max_batch
-    engine = Engine(model_dir, dtype=ns.dtype, options=EngineOptions(
+    device = parse_device(ns.device)
+    if device is None:
+        print(f"sharpi-cli: --device {ns.device!r}: expected an index, CUDA<n> or cuda:<n> (the engine has no CPU path)",
+              file=sys.stderr)
+        return 2
+    engine = Engine(model_dir, dtype=ns.dtype, device=device, options=EngineOptions(
         page_size=ns.page_size, max_cache_tokens=cache_tokens, max_batch=ns.max_batch,
-        max_tokens_per_step=ns.max_tokens_per_step))
+        max_tokens_per_step=ns.max_tokens_per_step, own_dense_rows=max(0, min(ns.min_batch_blas, 17) - 1)))
     params = [SamplingParams(temperature=ns.temp, top_k=ns.top_k, top_p=ns.top_p, min_p=ns.min_p,
                              repetition_penalty=ns.repeat_penalty, penalty_last_n=ns.repeat_last_n,
                              frequency_penalty=ns.frequency_penalty, presence_penalty=ns.presence_penalty,

@@ -154,3 +154,10 @@ def test_command_line_keeps_the_reference_option_names():
     assert (defaults.n_predict, defaults.temp, defaults.top_k, defaults.top_p, defaults.min_p, defaults.seed) == \
         (512, 0.7, 40, 0.95, 0.05, -1)
     assert parse_prompts("5 17 3; 9,9") == [[5, 17, 3], [9, 9]]
+    # --device in the reference's spellings (an index, a name) and torch's; --min-batch-blas as there
+    from sharpinference_b200.cli import parse_device
+    assert [parse_device(t) for t in (None, "auto", "0", "1", "CUDA0", "cuda:2", "cuda3")] == \
+        ["cuda:0", "cuda:0", "cuda:0", "cuda:1", "cuda:0", "cuda:2", "cuda:3"]
+    assert parse_device("none") is None and parse_device("Vulkan1") is None and parse_device("gpu") is None
+    assert defaults.min_batch_blas == 0 and defaults.device is None
+    assert build_parser().parse_args(["--min-batch-blas", "9", "--device", "CUDA0"]).min_batch_blas == 9

@@ -426,8 +426,8 @@ def test_command_line_generates(model_dirs, tmp_path):
     cfg_path = tmp_path / "config.json"
     cfg_path.write_text(json.dumps(TINY_B))
     proc = subprocess.run([cli, "--random-weights", "3", "--config", str(cfg_path), "--tokens", "1,2,3", "-n", "4",
-                           "--temp", "0.8", "-s", "9", "--max-cache-tokens", "128"], capture_output=True, text=True,
-                          timeout=600)
+                           "--temp", "0.8", "-s", "9", "--max-cache-tokens", "128", "--device", "CUDA0",
+                           "--min-batch-blas", "9"], capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr
     assert len(proc.stdout.strip().splitlines()[-1].split("|")[-1].split()) == 4
     # --trace-layers: a line per step and layer, with the expert where the layer is a mixture (layers 1, 3, 5 of B)
