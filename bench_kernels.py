@@ -154,6 +154,58 @@ def router(ns) -> None:
           f"{(T * H * 4 + E * H * 4) / ms / 1e6:.0f} GB/s of activations and router rows read once")
 
 
+def elementwise(ns) -> None:
+    """The memory-bound kernels between the products of a prompt step, each call on another copy of its inputs
+    (copies that exceed L2 together), with the bytes each has to move."""
+    T, H, I = ns.tokens, ns.hidden, ns.inter
+    nq, nkv, d, ps = ns.heads, ns.kv_heads, ns.head_dim, ns.page_size
+    state = {"i": 0}
+
+    def rotate(items):
+        def pick():
+            state["i"] += 1
+            return items[state["i"] % len(items)]
+        return pick
+
+    if ns.op == "add_rmsnorm":
+        copies = max(2, (300 << 20) // (T * H * 8) + 1)
+        xs = rotate([(torch.randn(T, H, device=DEV), torch.randn(T, H, device=DEV)) for _ in range(copies)])
+        w = torch.ones(H, device=DEV)
+        nbytes = T * H * (4 + 4 + 4 + 2 + (4 if ns.fp32_copy else 0))
+
+        def fn():
+            x, delta = xs()
+            ops.add_rmsnorm(x, delta, w, 1e-5, torch.bfloat16, want_fp32=ns.fp32_copy)
+    elif ns.op == "swiglu":
+        copies = max(2, (300 << 20) // (T * 2 * I * 4) + 1)
+        gus = rotate([torch.randn(T, 2 * I, device=DEV) for _ in range(copies)])
+        nbytes = T * I * (8 + 2)
+        fn = lambda: ops.swiglu(gus(), torch.bfloat16)
+    elif ns.op == "gather":
+        copies = max(2, (300 << 20) // (T * H * 2) + 1)
+        hs = rotate([torch.randn(T, H, device=DEV).to(torch.bfloat16) for _ in range(copies)])
+        rows = torch.randperm(T, device=DEV).to(torch.int32)
+        nbytes = T * H * 4
+        fn = lambda: ops.gather_rows_bf16(hs(), rows)
+    else:   # qkv_post: rotation, L2 norm, q store, keys and values into pages
+        width = (nq + 2 * nkv) * d
+        copies = max(2, (300 << 20) // (T * width * 4) + 1)
+        qkvs = rotate([torch.randn(T, width, device=DEV) for _ in range(copies)])
+        pages = (T + ps - 1) // ps
+        kv = torch.zeros(pages, 2, nkv, ps, d, dtype=torch.bfloat16, device=DEV)
+        table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+        positions = torch.arange(T, dtype=torch.int32, device=DEV)
+        row_req = torch.zeros(T, dtype=torch.int32, device=DEV)
+        inv_freq = (500000.0 ** (-torch.arange(0, d, 2, device=DEV, dtype=torch.float32) / d)).contiguous()
+        q = torch.empty(T, nq, d, dtype=torch.bfloat16, device=DEV)
+        nbytes = T * width * 4 + T * width * 2
+        fn = lambda: ops.qkv_post(qkvs(), positions, row_req, table, inv_freq, q, kv, nq=nq, nkv=nkv, d=d, page_size=ps,
+                                  pairing=ops.ROPE_INTERLEAVED, l2_eps=1e-5, temp_attn_scale=0.0, temp_floor_scale=0.0,
+                                  write_kv=True)
+    ms = _time(fn, max(ns.iters, 8))
+    print(f"{ns.op} tokens={T}: {ms * 1e3:.1f} us, {nbytes / 1e6:.0f} MB -> {nbytes / ms / 1e6:.0f} GB/s")
+
+
 def _cache(batch: int, context: int, nkv: int, d: int, ps: int):
     blocks = (context + ps - 1) // ps
     pages = batch * blocks
@@ -224,6 +276,17 @@ def main(argv=None) -> int:
     p.add_argument("--swiglu", action="store_true", help="SwiGLU after the product (rows: in its epilogue; library: a second kernel)")
     p.add_argument("--impl", choices=["grouped", "rows", "library"], default="grouped")
     p.set_defaults(fn=dense)
+    p = sub.add_parser("elementwise")
+    p.add_argument("--op", choices=["add_rmsnorm", "swiglu", "gather", "qkv_post"], default="add_rmsnorm")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=5120)
+    p.add_argument("--inter", type=int, default=8192)
+    p.add_argument("--heads", type=int, default=40)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--page-size", type=int, default=64)
+    p.add_argument("--fp32-copy", action="store_true", help="add_rmsnorm: also write the unrounded copy (as before a router)")
+    p.set_defaults(fn=elementwise)
     p = sub.add_parser("router")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--hidden", type=int, default=5120)
