@@ -44,9 +44,10 @@ __device__ __forceinline__ uint4 load_stream(const uint4* p) {
     return v;
 }
 
-// Activations are the output of the kernel before this one, and this kernel is running before that one has
-// ended: they are read with an ordinary load that stays behind the wait (a load marked as reading memory that
-// never changes, as __ldg is, may be moved ahead of it by the compiler: it was, and read the last step's values).
+// Activations are the output of the kernel before this one, and where this kernel is started early it is running
+// before that one has ended: they are read with an ordinary load that stays behind the wait (a load marked as
+// reading memory that never changes, as __ldg is, may be moved ahead of it by the compiler: it was, and read the
+// last step's values).
 __device__ __forceinline__ uint4 load_after_wait(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
